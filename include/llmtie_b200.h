@@ -1,0 +1,266 @@
+/*
+ * llmtie_b200 - the attention hot path of llmtie-rs as precompiled sm_100a
+ * kernels behind a C ABI.
+ *
+ * This library stands where `llmtie_cuda::Gpu` (crates/llmtie-cuda/src/device.rs)
+ * stands for attention, RoPE and the KV cache: it replaces the NVRTC module
+ * loader (`Gpu::open`, device.rs:737-842) with kernels compiled ahead of
+ * time, and the cache allocator policy of the model crates with
+ * `llmtie_kv_*`. Every entry point below names the reference method it
+ * replaces. Conventions, all taken from the reference:
+ *
+ *   - device buffers are raw device pointers plus their length in ELEMENTS,
+ *     so memory owned by the caller's allocator (cudarc in the reference) can
+ *     be passed straight through and every range is checked on the host
+ *     before anything is launched (error.rs:140-277);
+ *   - f16 travels as uint16_t bit patterns;
+ *   - offsets are element offsets into a buffer, never sub-slices, because
+ *     projections may alias one allocation (device.rs:2909-2913);
+ *   - all work is asynchronous on the handle's own non-blocking stream and
+ *     stream-ordered; nothing here synchronises the host except
+ *     llmtie_synchronize, llmtie_download and llmtie_kprof_report;
+ *   - a call that is refused returns a non-zero status, launches nothing and
+ *     leaves a message for llmtie_last_error() (thread-local).
+ *
+ * There is no CPU fallback: without a usable device llmtie_open fails with
+ * LLMTIE_ERR_NO_DEVICE and nothing else can be called.
+ */
+#ifndef LLMTIE_B200_H
+#define LLMTIE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct llmtie_gpu llmtie_gpu;
+typedef struct llmtie_decode_scratch llmtie_decode_scratch;
+typedef int32_t llmtie_status;
+
+/* Status codes: one per `CudaError` variant the path can raise
+ * (crates/llmtie-cuda/src/error.rs). */
+enum {
+    LLMTIE_OK = 0,
+    LLMTIE_ERR_NO_DEVICE = 1,             /* CudaError::NoDevice */
+    LLMTIE_ERR_DRIVER = 2,                /* CudaError::Driver */
+    LLMTIE_ERR_SLICE_OVERRUN = 3,         /* CudaError::SliceOverrun */
+    LLMTIE_ERR_CACHE_OVERRUN = 4,         /* CudaError::CacheOverrun */
+    LLMTIE_ERR_ODD_CACHE_CAPACITY = 5,    /* CudaError::OddCacheCapacity */
+    LLMTIE_ERR_ODD_HEAD_DIM = 6,          /* CudaError::OddHeadDim */
+    LLMTIE_ERR_UNSUPPORTED_ATTENTION = 7, /* CudaError::UnsupportedAttention */
+    LLMTIE_ERR_RAGGED_BLOCK = 8,          /* CudaError::RaggedBlock */
+    LLMTIE_ERR_MISALIGNED = 9,            /* CudaError::Misaligned */
+    LLMTIE_ERR_MISSING_KERNEL = 10,       /* CudaError::MissingKernel */
+    LLMTIE_ERR_TIMEOUT = 11,              /* a bounded device wait ran out */
+    LLMTIE_ERR_INVALID = 12               /* null handle, negative size */
+};
+
+/* ---- device handle ------------------------------------------------------ */
+
+/* Gpu::open (device.rs:737-842): binds the device, creates the handle's
+ * non-blocking stream and checks that the device is an sm_100 part. */
+llmtie_status llmtie_open(int32_t ordinal, llmtie_gpu **out);
+/* The same, adopting a stream the caller owns (a cudaStream_t). */
+llmtie_status llmtie_open_on_stream(int32_t ordinal, void *stream, llmtie_gpu **out);
+void llmtie_close(llmtie_gpu *g);
+/* Message of the last refused or failed call on this thread. */
+const char *llmtie_last_error(void);
+/* The handle's cudaStream_t. */
+void *llmtie_stream(llmtie_gpu *g);
+int32_t llmtie_ordinal(llmtie_gpu *g);
+/* Gpu::synchronize (device.rs:1433-1440). Also surfaces LLMTIE_ERR_TIMEOUT if
+ * a kernel's bounded wait gave up since the last call. */
+llmtie_status llmtie_synchronize(llmtie_gpu *g);
+
+/* Gpu::uninit / zeros / zeros_f16 (device.rs:937-983): stream-ordered. */
+llmtie_status llmtie_alloc(llmtie_gpu *g, size_t bytes, void **dptr);
+llmtie_status llmtie_zeros(llmtie_gpu *g, size_t bytes, void **dptr);
+llmtie_status llmtie_free(llmtie_gpu *g, void *dptr);
+/* Gpu::upload / download (device.rs:898-935): host <-> device on the stream;
+ * download waits for the stream. */
+llmtie_status llmtie_upload(llmtie_gpu *g, void *dst, const void *src, size_t bytes);
+llmtie_status llmtie_download(llmtie_gpu *g, void *dst, const void *src, size_t bytes);
+/* Gpu::upload_f16 (device.rs:1422-1431): f32 on the device -> f16 bits, RNE. */
+llmtie_status llmtie_round_f16(llmtie_gpu *g, const float *src, uint16_t *dst, size_t n);
+
+/* ---- KV-cache allocator -------------------------------------------------- */
+
+/* The growth policy of crates/llmtie-chat/src/model.rs:714-747 and
+ * crates/llmtie-translate/src/model.rs:662-694: the capacity to allocate when
+ * a cache of `cap` must hold past + n positions (0 = it already does).
+ * want = min(max(next_pow2(past + n + (n > 1 ? 256 : 0)), 256),
+ *            max(max_positions, past + n)). */
+size_t llmtie_kv_want_capacity(size_t cap, size_t past, size_t n, size_t max_positions);
+/* zeros_f16(want * kv_dim) twice (chat/model.rs:722-731): zeroed K
+ * [kv_heads][cap][hd] and V [kv_heads][hd][cap]. cap must be even. */
+llmtie_status llmtie_kv_alloc_f16(llmtie_gpu *g, size_t kv_heads, size_t head_dim,
+                                  size_t cap, uint16_t **k, uint16_t **v);
+/* Gpu::cache_grow_f16 / cache_grow (device.rs:3086-3212): re-stride `live`
+ * positions from a cache of old_cap into one of new_cap. */
+llmtie_status llmtie_cache_grow_f16(llmtie_gpu *g, const uint16_t *src, size_t src_len,
+                                    uint16_t *dst, size_t dst_len, size_t kv_heads,
+                                    size_t head_dim, size_t old_cap, size_t new_cap,
+                                    size_t live, int32_t transposed);
+llmtie_status llmtie_cache_grow(llmtie_gpu *g, const float *src, size_t src_len,
+                                float *dst, size_t dst_len, size_t kv_heads,
+                                size_t head_dim, size_t old_cap, size_t new_cap,
+                                size_t live, int32_t transposed);
+/* Gpu::cache_append_f16 / cache_append (device.rs:2849-2901, :3013-3078):
+ * src [n][kv_heads*head_dim] f32 at src_off -> cache positions past..past+n. */
+llmtie_status llmtie_cache_append_f16(llmtie_gpu *g, const float *src, size_t src_len,
+                                      size_t src_off, uint16_t *dst, size_t dst_len,
+                                      size_t n, size_t kv_heads, size_t head_dim,
+                                      size_t cap, size_t past, int32_t transposed);
+llmtie_status llmtie_cache_append(llmtie_gpu *g, const float *src, size_t src_len,
+                                  size_t src_off, float *dst, size_t dst_len, size_t n,
+                                  size_t kv_heads, size_t head_dim, size_t cap,
+                                  size_t past, int32_t transposed);
+
+/* ---- RoPE ----------------------------------------------------------------- */
+
+/* Gpu::rope / rope_scaled (device.rs:5410-5471): NeoX/halves RoPE in place on
+ * x[off .. off + t*heads*head_dim]; freq_div is NULL or head_dim/2 floats. */
+llmtie_status llmtie_rope_scaled(llmtie_gpu *g, float *x, size_t x_len, size_t off,
+                                 const float *freq_div, size_t t, size_t heads,
+                                 size_t head_dim, float theta, size_t first);
+/* Gpu::rope_cache_f16 (device.rs:2915-3000): one decoded position. q is
+ * rotated in place; rotated k and v go to the f16 caches at `pos`; the
+ * projection buffers for k and v are not written. q, k and v may be offsets
+ * into one allocation. */
+llmtie_status llmtie_rope_cache_f16(llmtie_gpu *g, float *q, size_t q_len, size_t q_off,
+                                    const float *k, size_t k_len, size_t k_off,
+                                    const float *v, size_t v_len, size_t v_off,
+                                    const float *freq_div, size_t heads, size_t kv_heads,
+                                    size_t head_dim, float theta, size_t pos,
+                                    uint16_t *kc, size_t kc_len, uint16_t *vc,
+                                    size_t vc_len, size_t cap);
+
+/* ---- prefill / encoder attention ------------------------------------------- */
+
+/* Gpu::supports_flash (device.rs:5697-5699). */
+int32_t llmtie_supports_flash(size_t head_dim, size_t heads, size_t kv_heads);
+/* Gpu::flash_attn_f16 (device.rs:5754-5799): q f32 [tq][heads*hd] (already
+ * rotated), K f16 [kv][cap][hd], V f16 [kv][hd][cap] holding past+tq
+ * positions; out f32 [tq][heads*hd]. head_dim 128 only, cap even. */
+llmtie_status llmtie_flash_attn_f16(llmtie_gpu *g, const float *q, size_t q_len,
+                                    const uint16_t *k, size_t k_len, const uint16_t *v,
+                                    size_t v_len, float *out, size_t out_len, size_t tq,
+                                    size_t past, size_t heads, size_t kv_heads,
+                                    size_t head_dim, size_t cap, float scale,
+                                    int32_t causal);
+/* Gpu::flash_attn (device.rs:5702-5745): the same off f32 caches, head_dim 64
+ * or 128; K and V are rounded to f16 on their way into the products. */
+llmtie_status llmtie_flash_attn(llmtie_gpu *g, const float *q, size_t q_len,
+                                const float *k, size_t k_len, const float *v,
+                                size_t v_len, float *out, size_t out_len, size_t tq,
+                                size_t past, size_t heads, size_t kv_heads,
+                                size_t head_dim, size_t cap, float scale, int32_t causal);
+/* Gpu::flash_attn_rows (device.rs:5812-5865): the Whisper encoder. qkv f32
+ * [t][3*heads*hd] (q | k | v column blocks), non-causal, scale on q before it
+ * is rounded, context returned f16 [t][heads*hd]. head_dim 64 only.
+ * `work` is NULL (the call allocates and frees its own staging buffers on the
+ * stream) or a buffer of llmtie_flash_rows_work_bytes(t, heads, head_dim). */
+llmtie_status llmtie_flash_attn_rows(llmtie_gpu *g, const float *qkv, size_t qkv_len,
+                                     uint16_t *out, size_t out_len, size_t t,
+                                     size_t heads, size_t head_dim, float scale,
+                                     void *work, size_t work_bytes);
+size_t llmtie_flash_rows_work_bytes(size_t t, size_t heads, size_t head_dim);
+
+/* ---- decode attention ------------------------------------------------------- */
+
+/* DecodeScratch (device.rs:166-233, :6332-6359): the split-KV workspace a
+ * caller keeps per cache. It grows inside the attention call when a longer
+ * context needs more partials; its counters rest at zero between calls. */
+llmtie_status llmtie_decode_scratch_new(llmtie_gpu *g, llmtie_decode_scratch **out);
+void llmtie_decode_scratch_free(llmtie_gpu *g, llmtie_decode_scratch *s);
+
+/* Gpu::attn_decode_f16 / attn_decode_f16_q_row without the int8 twin
+ * (device.rs:5949-6038, :6224-6413): one query position, q f32 [heads*hd] at
+ * q_off with a group's rows adjacent, f16 caches holding tk <= cap positions,
+ * out f32 [heads*hd] at out_off (out_off % 32 == 0). scale_q puts the scale
+ * on q; otherwise on the scores. head_dim 64 or 128; heads/kv_heads at most 4
+ * at 128 and 8 at 64, as the reference's instantiations. */
+llmtie_status llmtie_attn_decode_f16(llmtie_gpu *g, const float *q, size_t q_len,
+                                     size_t q_off, const uint16_t *k, size_t k_len,
+                                     const uint16_t *v, size_t v_len, size_t heads,
+                                     size_t kv_heads, size_t head_dim, size_t tk,
+                                     size_t cap, float scale, int32_t scale_q,
+                                     llmtie_decode_scratch *scratch, float *out,
+                                     size_t out_len, size_t out_off);
+/* Gpu::attn_decode (device.rs:6132-6168): the same off f32 caches, head_dim 64
+ * (the Whisper decoder's self-attention). */
+llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_t q_len, size_t q_off,
+                                 const float *k, size_t k_len, const float *v,
+                                 size_t v_len, size_t heads, size_t kv_heads,
+                                 size_t head_dim, size_t tk, size_t cap, float scale,
+                                 int32_t scale_q, llmtie_decode_scratch *scratch,
+                                 float *out, size_t out_len, size_t out_off);
+
+/* ---- batched and sharded entries (supersets; the reference loops) ------------ */
+
+/* What crates/llmtie-translate/src/model.rs:824-859 does as a loop of
+ * single-sequence launches, in one launch: `batch` sequences, each with its
+ * own f16 caches, live length and capacity. q and out are f32
+ * [batch][heads*hd]. k_ptrs, v_ptrs, tk and cap are HOST arrays of `batch`.
+ * If `partial` is non-zero, out is instead [batch][heads][hd+2]: the
+ * un-normalised context, the maximum score and the sum of exponentials
+ * (kernels.rs:5791-5799), for llmtie_lse_merge. */
+llmtie_status llmtie_decode_batched(llmtie_gpu *g, const float *q, size_t q_len,
+                                    const uint16_t *const *k_ptrs,
+                                    const uint16_t *const *v_ptrs, const int32_t *tk,
+                                    const int32_t *cap, size_t batch, size_t heads,
+                                    size_t kv_heads, size_t head_dim, float scale,
+                                    int32_t scale_q, llmtie_decode_scratch *scratch,
+                                    float *out, size_t out_len, int32_t partial);
+/* The merge of ad_publish_merge (kernels.rs:5836-5879) over `parts` triples
+ * laid out [parts][rows][hd+2], e.g. an all-gather of each GPU's
+ * llmtie_decode_batched(partial=1) output; out f32 [rows][hd]. */
+llmtie_status llmtie_lse_merge(llmtie_gpu *g, const float *parts_buf, size_t parts_len,
+                               size_t parts, size_t rows, size_t head_dim, float *out,
+                               size_t out_len);
+/* AsrModel::attend (crates/llmtie-asr/src/model.rs:573-641) fused: n query
+ * rows (q f32 [n][heads*hd], scale applied to q) over f16 cross caches
+ * K [heads][cap][hd], V [heads][hd][cap] with tk live keys, non-causal;
+ * out f32 [n][heads*hd]. */
+llmtie_status llmtie_cross_attn(llmtie_gpu *g, const float *q, size_t q_len,
+                                const uint16_t *k, size_t k_len, const uint16_t *v,
+                                size_t v_len, size_t n, size_t heads, size_t head_dim,
+                                size_t tk, size_t cap, float scale,
+                                llmtie_decode_scratch *scratch, float *out,
+                                size_t out_len);
+/* ChatModel::run's prefill of one layer (crates/llmtie-chat/src/model.rs:
+ * 848-889, :967-980) for `batch` packed ragged sequences in one call: RoPE on
+ * q and k, the new K/V written into each sequence's f16 cache at past[b], and
+ * causal attention. q f32 [total][heads*hd] (rotated in place), k and v f32
+ * [total][kv_heads*hd] (unrotated), cu_seqlens HOST int32 [batch+1],
+ * past/cap/k_ptrs/v_ptrs HOST arrays; out f32 [total][heads*hd]. */
+llmtie_status llmtie_prefill_varlen(llmtie_gpu *g, float *q, size_t q_len, const float *k,
+                                    size_t k_len, const float *v, size_t v_len,
+                                    const int32_t *cu_seqlens, size_t batch,
+                                    uint16_t *const *k_ptrs, uint16_t *const *v_ptrs,
+                                    const int32_t *past, const int32_t *cap,
+                                    const float *freq_div, size_t heads, size_t kv_heads,
+                                    size_t head_dim, float theta, float scale, float *out,
+                                    size_t out_len);
+
+/* ---- profiling ---------------------------------------------------------------- */
+
+/* kprof (device.rs:1490-1565): with it on, every launch is bracketed by
+ * events and charged to its kernel's name. The report is "name count ms"
+ * lines; returns the bytes needed. */
+void llmtie_kprof_enable(llmtie_gpu *g, int32_t on);
+void llmtie_kprof_reset(llmtie_gpu *g);
+size_t llmtie_kprof_report(llmtie_gpu *g, char *buf, size_t cap);
+/* Gpu::kernel_resources (device.rs:1458-1465): registers per thread, local
+ * bytes per thread, static shared bytes. */
+llmtie_status llmtie_kernel_resources(const char *name, int32_t *regs, int32_t *local_bytes,
+                                      int32_t *shared_bytes);
+/* Kernels launched through this handle since it was opened. */
+uint64_t llmtie_launch_count(llmtie_gpu *g);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

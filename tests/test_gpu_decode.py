@@ -1,0 +1,192 @@
+"""Decode attention through the C ABI against the CPU oracle.
+
+The cases, salts and the 2e-5-of-full-scale bound are those of the
+reference's `the_fused_decode_attention_matches_the_chain`
+(crates/llmtie-cuda/tests/kernels.rs:2782-2932).
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.helpers import assert_close_to, assert_parity, normal_f16, poison_f16_bits
+
+pytestmark = pytest.mark.gpu
+
+# (heads, kv_heads, hd, tk, cap, f16 cache, scale on the query)
+CASES = [
+    (8, 2, 128, 1, 256, True, False),
+    (8, 2, 128, 63, 256, True, False),
+    (8, 2, 128, 64, 256, True, False),
+    (8, 2, 128, 65, 256, True, False),
+    (8, 2, 128, 200, 256, True, False),
+    (8, 2, 128, 256, 256, True, False),
+    (4, 4, 128, 130, 512, True, False),
+    (6, 6, 64, 1500, 1500, True, True),
+    (6, 6, 64, 1499, 1500, True, True),
+    (6, 6, 64, 37, 448, False, True),
+    (6, 6, 64, 129, 448, False, True),
+    (6, 6, 64, 448, 448, False, True),
+    (4, 2, 128, 16500, 16512, True, False),
+    (32, 8, 128, 4096, 4096, True, False),
+    (32, 8, 128, 8192, 8192, True, False),
+    (32, 8, 128, 7777, 8192, True, False),
+    (40, 40, 128, 1500, 1536, True, False),
+    (20, 20, 64, 1500, 1500, True, True),
+    (8, 8, 64, 5000, 5056, False, True),
+]
+
+
+@pytest.mark.parametrize("i,case", list(enumerate(CASES)))
+def test_fused_decode_matches_the_chain(gpu, i, case):
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, kv, hd, tk, cap, half, scale_q = case
+    salt = 300 + 3 * i
+    q = O.seq(heads * hd, salt)
+    k0 = O.seq(kv * cap * hd, salt + 1)
+    v0 = O.seq(kv * hd * cap, salt + 2)
+    scale = 0.11
+    scratch = DecodeScratch()
+    dq = gpu.upload(q)
+    name = f"attn_decode heads {heads} kv {kv} hd {hd} tk {tk} f16 {half}"
+    if half:
+        k, v = O.through_f16(k0), O.through_f16(v0)
+        want = O.decode_f32(q, k, v, heads, kv, hd, tk, cap, scale, scale_q)
+        dk, dv = gpu.upload_f16(k0), gpu.upload_f16(v0)
+        first = gpu.attn_decode_f16(dq, dk, dv, heads, kv, hd, tk, cap, scale, scale_q, scratch)
+        again = gpu.attn_decode_f16(dq, dk, dv, heads, kv, hd, tk, cap, scale, scale_q, scratch)
+    else:
+        want = O.decode_f32(q, k0, v0, heads, kv, hd, tk, cap, scale, scale_q)
+        dk, dv = gpu.upload(k0), gpu.upload(v0)
+        first = gpu.attn_decode(dq, dk, dv, heads, kv, hd, tk, cap, scale, scale_q, scratch)
+        again = gpu.attn_decode(dq, dk, dv, heads, kv, hd, tk, cap, scale, scale_q, scratch)
+    a, b = gpu.download(first), gpu.download(again)
+    # twice through one scratch: a counter left dirty would merge early or never
+    assert np.array_equal(a, b), f"{name}: not reproducible through one scratch"
+    assert_close_to(name, want, a, 2e-5)
+    if half:
+        tight = O.decode_f64(q, O.round_f16(k0), O.round_f16(v0), heads, kv, hd, 0, tk, cap,
+                             scale, scale_q)
+        assert_close_to(name + " (f64 oracle)", tight, a, 2e-5)
+
+
+def test_decode_refusals(gpu):
+    """The shapes it refuses, by name rather than by wrong answer
+    (crates/llmtie-cuda/tests/kernels.rs:2910-2932)."""
+    from ttsxabe_b200 import CacheOverrun, DecodeScratch, UnsupportedAttention
+
+    scratch = DecodeScratch()
+    dq = gpu.upload(O.seq(8 * 128, 1))
+    dk = gpu.upload_f16(O.seq(2 * 256 * 128, 2))
+    with pytest.raises(UnsupportedAttention):   # a head width it is not instantiated at
+        gpu.attn_decode_f16(dq, dk, dk, 8, 2, 96, 10, 256, 1.0, False, scratch)
+    with pytest.raises(CacheOverrun):           # more keys than the cache holds
+        gpu.attn_decode_f16(dq, dk, dk, 8, 2, 128, 257, 256, 1.0, False, scratch)
+    with pytest.raises(CacheOverrun):           # no keys at all
+        gpu.attn_decode_f16(dq, dk, dk, 8, 2, 128, 0, 256, 1.0, False, scratch)
+    with pytest.raises(UnsupportedAttention):   # a group wider than the kernel carries
+        gpu.attn_decode_f16(dq, dk, dk, 10, 2, 128, 10, 256, 1.0, False, scratch)
+
+
+def test_row_variant_equals_single(gpu):
+    """`attn_decode_f16_q_row` writes row `row` of a shared output and reads q
+    at an offset; same kernel, same bits (kernels.rs tests :3339-3440)."""
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, kv, hd, tk, cap = 32, 8, 128, 777, 1024
+    rows = 3
+    scratch = DecodeScratch()
+    qs = O.seq(rows * heads * hd, 11)
+    dq_all = gpu.upload(qs)
+    dk = gpu.upload_f16(O.seq(kv * cap * hd, 12))
+    dv = gpu.upload_f16(O.seq(kv * cap * hd, 13))
+    out = gpu.zeros(rows * heads * hd)
+    for r in range(rows):
+        gpu.attn_decode_f16_row(dq_all, r * heads * hd, dk, dv, heads, kv, hd, tk, cap, 0.09,
+                                False, scratch, out, r)
+    got = gpu.download(out).reshape(rows, -1)
+    for r in range(rows):
+        dq = gpu.upload(qs[r * heads * hd:(r + 1) * heads * hd])
+        single = gpu.download(
+            gpu.attn_decode_f16(dq, dk, dv, heads, kv, hd, tk, cap, 0.09, False, scratch))
+        assert np.array_equal(single, got[r])
+
+
+@pytest.mark.parametrize("batch", [1, 16])
+def test_config3_batched_decode(gpu, batch):
+    """BASELINE config 3: one query per sequence, context seeded uniform in
+    [2048, 4096], 32 Q / 8 KV heads, hd 128, f16 cache and N(0,1) query, RoPE
+    on the query at position = context length; bar max-abs 2e-3, rel-L2 1e-3."""
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, kv, hd = 32, 8, 128
+    rng = np.random.default_rng(3000 + batch)
+    tks = rng.integers(2048, 4097, size=batch)
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    scratch = DecodeScratch()
+    ks, vs, caps, wants, qs = [], [], [], [], []
+    for b in range(batch):
+        tk = int(tks[b])
+        cap = 4096
+        q = normal_f16(rng, heads * hd)
+        q = O.rope(q, 1, heads, hd, 10000.0, tk)
+        kb = O.round_f16(normal_f16(rng, kv * cap * hd))
+        vb = O.round_f16(normal_f16(rng, kv * hd * cap))
+        # what lies past the live keys must not matter: poison it
+        kb = poison_f16_bits(kb, kv, tk, hd, cap, False)
+        vb = poison_f16_bits(vb, kv, tk, hd, cap, True)
+        wants.append(O.decode_f64(q, kb, vb, heads, kv, hd, 0, tk, cap, scale, False))
+        ks.append(gpu.upload_u16(kb))
+        vs.append(gpu.upload_u16(vb))
+        caps.append(cap)
+        qs.append(q)
+    dq = gpu.upload(np.concatenate(qs))
+    out = gpu.decode_batched(dq, ks, vs, tks, caps, heads, kv, hd, scale, False, scratch)
+    got = gpu.download(out).reshape(batch, -1)
+    for b in range(batch):
+        assert_parity(f"config 3 batch {batch} seq {b} tk {tks[b]}", wants[b], got[b])
+        # the reference's loop of single-sequence calls gives the same bits
+    single = gpu.download(gpu.attn_decode_f16(gpu.upload(qs[0]), ks[0], vs[0], heads, kv, hd,
+                                              int(tks[0]), caps[0], scale, False, scratch))
+    assert_parity("single vs oracle", wants[0], single)
+
+
+def test_partial_triples_merge_to_the_whole(gpu):
+    """Splitting the keys over `parts` caches, taking un-normalised
+    (o, m, l) from each and merging equals decoding the whole cache: the
+    algebra the multi-GPU path rests on (kernels.rs:5836-5879)."""
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, kv, hd, parts, per = 32, 8, 128, 4, 1024
+    rng = np.random.default_rng(77)
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, heads * hd)
+    kv_all = normal_f16(rng, kv * parts * per * hd).reshape(kv, parts * per, hd)
+    vv_all = normal_f16(rng, kv * parts * per * hd).reshape(kv, parts * per, hd)
+    scratch = DecodeScratch()
+    dq = gpu.upload(q)
+    bufs = []
+    for p in range(parts):
+        kc = np.ascontiguousarray(kv_all[:, p * per:(p + 1) * per, :])
+        vc = np.ascontiguousarray(vv_all[:, p * per:(p + 1) * per, :].transpose(0, 2, 1))
+        dk, dv = gpu.upload_u16(O.round_f16(kc)), gpu.upload_u16(O.round_f16(vc))
+        part = gpu.decode_batched(dq, [dk], [dv], [per], [per], heads, kv, hd, scale, False,
+                                  scratch, partial=True)
+        trip = gpu.download(part).reshape(heads, hd + 2)
+        _, o_un, m, l = O.decode_f64(q, O.round_f16(kc), O.round_f16(vc), heads, kv, hd, 0, per,
+                                     per, scale, False, triple=True)
+        assert_close_to("partial m", m, trip[:, hd], 1e-5)
+        assert_close_to("partial l", l, trip[:, hd + 1], 1e-4)
+        assert_close_to("partial o", o_un, trip[:, :hd].reshape(-1), 1e-4)
+        bufs.append(part)
+    import torch
+
+    with torch.cuda.stream(gpu.stream):
+        gathered = torch.cat(bufs)
+    merged = gpu.download(gpu.lse_merge(gathered, parts, heads, hd))
+    kc = np.ascontiguousarray(kv_all)
+    vc = np.ascontiguousarray(vv_all.transpose(0, 2, 1))
+    want = O.decode_f64(q, O.round_f16(kc), O.round_f16(vc), heads, kv, hd, 0, parts * per,
+                        parts * per, scale, False)
+    assert_parity("merged partials", want, merged)
+    assert_close_to("merged partials", want, merged, 2e-5)

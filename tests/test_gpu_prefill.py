@@ -1,0 +1,203 @@
+"""Fused prefill / encoder attention through the C ABI against the oracle.
+
+Shapes, salts, the peaked softmax (q x 100) and the tolerance are those of the
+reference's `fused_attention_sized` (crates/llmtie-cuda/tests/kernels.rs:
+2249-2439); the BASELINE configs add the N(0,1) cases at the 2e-3 / 1e-3 bar.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.helpers import (assert_parity, assert_prefill_tolerance, lay_caches, normal_f16,
+                           prefill_spread)
+
+pytestmark = pytest.mark.gpu
+
+# (heads, kv_heads, hd, causal, tq, past, cap, f16 cache)
+SIZED = [
+    (4, 2, 128, True, 70, 33, 160, False),
+    (4, 4, 64, False, 70, 33, 160, False),
+    (4, 2, 64, False, 70, 33, 160, False),
+    (4, 4, 128, True, 70, 33, 160, False),
+    (4, 4, 64, True, 70, 33, 160, False),
+    (4, 2, 64, True, 70, 33, 160, False),
+    (8, 2, 128, True, 150, 0, 256, True),
+    (8, 1, 128, True, 90, 17, 128, True),
+    (4, 4, 128, True, 200, 40, 256, True),
+    (4, 2, 128, True, 130, 5, 138, True),
+    (4, 4, 64, False, 300, 0, 300, False),
+]
+
+
+@pytest.mark.parametrize("case", SIZED)
+def test_fused_attention_sized(gpu, case):
+    heads, kv, hd, causal, tq, past, cap, half = case
+    tk = past + tq
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = O.seq(tq * heads * hd, 71) * np.float32(100.0)
+    kc, vc = lay_caches(O.seq(kv * tk * hd, 72), O.seq(kv * tk * hd, 73), kv, tk, hd, cap)
+    dq = gpu.upload(q)
+    if half:
+        out = gpu.flash_attn_f16(dq, gpu.upload_f16(kc), gpu.upload_f16(vc), tq, past, heads, kv,
+                                 hd, cap, scale, causal)
+    else:
+        out = gpu.flash_attn(dq, gpu.upload(kc), gpu.upload(vc), tq, past, heads, kv, hd, cap,
+                             scale, causal)
+    got = gpu.download(out)
+    want, spread = prefill_spread(q, kc, vc, tq, past, heads, kv, hd, cap, scale, causal)
+    # the numpy restatement and the C oracle are the same function
+    c_want = O.prefill(q, kc, vc, tq, past, heads, kv, hd, cap, scale, causal)
+    assert np.abs(c_want - want).max() < 1e-5
+    assert_prefill_tolerance(str(case), want, spread, got)
+
+
+def test_prefill_refusals(gpu):
+    from ttsxabe_b200 import (CacheOverrun, OddCacheCapacity, SliceOverrun,
+                              UnsupportedAttention)
+
+    dq = gpu.upload(O.seq(16 * 8 * 128, 1))
+    dk = gpu.upload_f16(O.seq(2 * 256 * 128, 2))
+    with pytest.raises(UnsupportedAttention):
+        gpu.flash_attn_f16(dq, dk, dk, 16, 0, 8, 2, 64, 256, 1.0, True)   # f16 cache: 128 only
+    with pytest.raises(UnsupportedAttention):
+        gpu.flash_attn_f16(dq, dk, dk, 16, 0, 8, 3, 128, 256, 1.0, True)
+    with pytest.raises(OddCacheCapacity):
+        gpu.flash_attn_f16(dq, dk, dk, 16, 0, 8, 2, 128, 255, 1.0, True)
+    with pytest.raises(CacheOverrun):
+        gpu.flash_attn_f16(dq, dk, dk, 16, 250, 8, 2, 128, 256, 1.0, True)
+    with pytest.raises(SliceOverrun):
+        gpu.flash_attn_f16(dq, dk, dk, 17, 0, 8, 2, 128, 256, 1.0, True)
+    assert gpu.supports_flash(128, 32, 8) and gpu.supports_flash(64, 20, 20)
+    assert not gpu.supports_flash(96, 8, 2) and not gpu.supports_flash(128, 10, 4)
+
+
+def test_config1_single_layer_prefill(gpu):
+    """BASELINE config 1: batch 1, seq 128, 32 Q / 8 KV heads, hd 128, Q/K/V
+    fp16 N(0,1), NeoX RoPE theta 10000 on Q and K, scale 1/sqrt(128), fp32
+    output [128, 32, 128]."""
+    heads, kv, hd, n = 32, 8, 128, 128
+    rng = np.random.default_rng(1)
+    q = normal_f16(rng, n * heads * hd)
+    k = normal_f16(rng, n * kv * hd)
+    v = normal_f16(rng, n * kv * hd)
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    cap = 256
+    # oracle: f32 RoPE on the f16-rounded values, rotated K rounded into the cache
+    qr = O.rope(q, n, heads, hd, 10000.0, 0)
+    kr = O.rope(k, n, kv, hd, 10000.0, 0)
+    kc = np.zeros(kv * cap * hd, np.uint16)
+    vc = np.zeros(kv * cap * hd, np.uint16)
+    O.cache_append_f16(kr, kc, n, kv, hd, cap, 0, False)
+    O.cache_append_f16(v, vc, n, kv, hd, cap, 0, True)
+    want = O.prefill(qr, kc, vc, n, 0, heads, kv, hd, cap, scale, True)
+
+    # the reference's chain: rope q, rope k, append k, append v^T, flash_attn_f16
+    dq, dk, dv = gpu.upload(q), gpu.upload(k), gpu.upload(v)
+    gpu.rope(dq, 0, n, heads, hd, 10000.0, 0)
+    gpu.rope(dk, 0, n, kv, hd, 10000.0, 0)
+    dkc, dvc = gpu.zeros_f16(kv * cap * hd), gpu.zeros_f16(kv * cap * hd)
+    gpu.cache_append_f16(dk, 0, dkc, n, kv, hd, cap, 0, False)
+    gpu.cache_append_f16(dv, 0, dvc, n, kv, hd, cap, 0, True)
+    out = gpu.flash_attn_f16(dq, dkc, dvc, n, 0, heads, kv, hd, cap, scale, True)
+    got = gpu.download(out)
+    assert got.shape == (n * heads * hd,)
+    assert_parity("config 1", want, got)
+    assert np.array_equal(gpu.download_u16(dvc), vc)
+
+    # the fused varlen entry gives the same answer and the same cache
+    dq2 = gpu.upload(q)
+    kc2, vc2 = gpu.zeros_f16(kv * cap * hd), gpu.zeros_f16(kv * cap * hd)
+    out2 = gpu.prefill_varlen(dq2, gpu.upload(k), gpu.upload(v), [0, n], [kc2], [vc2], [0],
+                              [cap], None, heads, kv, hd, 10000.0, scale)
+    assert_parity("config 1 (varlen entry)", want, gpu.download(out2))
+    assert np.array_equal(gpu.download_u16(kc2), gpu.download_u16(dkc))
+    assert np.array_equal(gpu.download_u16(vc2), vc)
+
+
+def test_config2_ragged_batched_prefill(gpu):
+    """BASELINE config 2: 8 ragged sequences, lengths seeded uniform in
+    [256, 512], packed with cu_seqlens, 32 Q / 8 KV heads, hd 128, RoPE theta
+    10000, the new K/V written into the fp16 KV cache."""
+    heads, kv, hd, batch = 32, 8, 128, 8
+    rng = np.random.default_rng(2)
+    lens = rng.integers(256, 513, size=batch)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    total = int(cu[-1])
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, total * heads * hd)
+    k = normal_f16(rng, total * kv * hd)
+    v = normal_f16(rng, total * kv * hd)
+    cap = 512
+    dq = gpu.upload(q)
+    kcs = [gpu.zeros_f16(kv * cap * hd) for _ in range(batch)]
+    vcs = [gpu.zeros_f16(kv * cap * hd) for _ in range(batch)]
+    out = gpu.prefill_varlen(dq, gpu.upload(k), gpu.upload(v), cu, kcs, vcs, [0] * batch,
+                             [cap] * batch, None, heads, kv, hd, 10000.0, scale)
+    got = gpu.download(out).reshape(total, heads * hd)
+    for b in range(batch):
+        n, r0 = int(lens[b]), int(cu[b])
+        qb = q.reshape(total, -1)[r0:r0 + n].reshape(-1)
+        kb = k.reshape(total, -1)[r0:r0 + n].reshape(-1)
+        vb = v.reshape(total, -1)[r0:r0 + n].reshape(-1)
+        qr = O.rope(qb, n, heads, hd, 10000.0, 0)
+        kr = O.rope(kb, n, kv, hd, 10000.0, 0)
+        kc = np.zeros(kv * cap * hd, np.uint16)
+        vc = np.zeros(kv * cap * hd, np.uint16)
+        O.cache_append_f16(kr, kc, n, kv, hd, cap, 0, False)
+        O.cache_append_f16(vb, vc, n, kv, hd, cap, 0, True)
+        want = O.prefill(qr, kc, vc, n, 0, heads, kv, hd, cap, scale, True, fast=True)
+        assert_parity(f"config 2 sequence {b} ({n} tokens)", want, got[r0:r0 + n].reshape(-1))
+        assert np.array_equal(gpu.download_u16(vcs[b]), vc)
+        # rotated keys: the device's sincosf and the host's differ in the last bit
+        dk = O.widen_f16(gpu.download_u16(kcs[b]))
+        assert np.abs(dk - O.widen_f16(kc)).max() <= 4e-3
+    # one sequence against the f64 oracle as well
+    n = int(lens[0])
+    qr = O.rope(q.reshape(total, -1)[:n].reshape(-1), n, heads, hd, 10000.0, 0)
+    want64 = O.prefill(qr, gpu.download_u16(kcs[0]), gpu.download_u16(vcs[0]), n, 0, heads, kv,
+                       hd, cap, scale, True)
+    assert_parity("config 2 sequence 0 (f64 oracle)", want64, got[:n].reshape(-1))
+
+
+def test_whisper_encoder_rows(gpu):
+    """BASELINE config 4, encoder: non-causal self-attention over 1500 frames,
+    20 heads, hd 64, scale 1/8 on q, context f16 [t, d] from one [t, 3d]
+    product (crates/llmtie-cuda/src/device.rs:5812-5865)."""
+    heads, hd, t = 20, 64, 1500
+    d = heads * hd
+    rng = np.random.default_rng(4)
+    qkv = normal_f16(rng, t * 3 * d).reshape(t, 3 * d)
+    out = gpu.flash_attn_rows(gpu.upload(qkv), t, heads, hd, 0.125)
+    got = O.widen_f16(gpu.download_u16(out))
+    kc, vc = lay_caches(qkv[:, d:2 * d].reshape(t, heads, hd).transpose(1, 0, 2),
+                        qkv[:, 2 * d:].reshape(t, heads, hd).transpose(1, 0, 2), heads, t, hd, t)
+    want = O.prefill(np.ascontiguousarray(qkv[:, :d]), kc, vc, t, 0, heads, heads, hd, t, 0.125,
+                     False, scale_q=True, fast=True)
+    # the context is returned rounded to f16: half an ulp of f16 on top of the bar
+    assert np.abs(want - got).max() <= 2e-3 + 2.0 ** -11 * np.abs(want).max()
+    assert np.linalg.norm(want - got) / np.linalg.norm(want) <= 1e-3 + 2.0 ** -11
+
+
+@pytest.mark.parametrize("n", [1, 2, 5, 8, 16, 32])
+def test_whisper_cross_attention(gpu, n):
+    """BASELINE config 4, decoder cross-attention: 1 to 32 query tokens over
+    the 1500-frame encoder K/V, 20 heads, hd 64, scale 1/8 on q."""
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, hd, tk = 20, 64, 1500
+    rng = np.random.default_rng(40 + n)
+    q = normal_f16(rng, n * heads * hd)
+    kc = O.round_f16(normal_f16(rng, heads * tk * hd))
+    vc = O.round_f16(normal_f16(rng, heads * hd * tk))
+    scratch = DecodeScratch()
+    out = gpu.cross_attn(gpu.upload(q), gpu.upload_u16(kc), gpu.upload_u16(vc), n, heads, hd, tk,
+                         tk, 0.125, scratch)
+    got = gpu.download(out)
+    want = O.prefill(q, kc, vc, n, 0, heads, heads, hd, tk, 0.125, False, scale_q=True, tk=tk)
+    assert_parity(f"cross attention n={n}", want, got)
+    if n == 1:
+        # one row is the reference's attn_decode_f16 call with scale_q
+        dec = gpu.download(gpu.attn_decode_f16(gpu.upload(q), gpu.upload_u16(kc),
+                                               gpu.upload_u16(vc), heads, heads, hd, tk, tk,
+                                               0.125, True, scratch))
+        assert np.array_equal(dec, got)

@@ -1,0 +1,1136 @@
+// The C ABI of llmtie_b200: the handle, host-side refusals and the dispatch
+// to the kernels. Every range is checked here, before anything is launched,
+// and refused by name, as `llmtie_cuda::Gpu` does
+// (crates/llmtie-cuda/src/device.rs, error.rs:140-277).
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+llmtie_status driver_fail(const char *what, cudaError_t e)
+{
+    return llmtie_fail(LLMTIE_ERR_DRIVER, "%s: %s", what, cudaGetErrorString(e));
+}
+
+size_t next_pow2(size_t x)
+{
+    size_t p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+bool fits_i32(size_t x) { return x <= 0x7fffffffu; }
+
+}  // namespace
+
+static std::map<std::string, const void *> &kernel_table()
+{
+    static std::map<std::string, const void *> t;
+    return t;
+}
+
+KernelReg::KernelReg(const char *name, const void *fn) { kernel_table()[name] = fn; }
+
+const void *llmtie_kernel_symbol(const char *name)
+{
+    const auto it = kernel_table().find(name);
+    return it == kernel_table().end() ? nullptr : it->second;
+}
+
+llmtie_status llmtie_fail(llmtie_status code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+extern "C" const char *llmtie_last_error(void) { return g_err; }
+
+LaunchScope::LaunchScope(llmtie_gpu *g_, const char *name_) : g(g_), name(name_)
+{
+    if (g->kprof) cudaEventRecord(g->ev0, g->stream);
+}
+
+llmtie_status LaunchScope::done()
+{
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return driver_fail(name, e);
+    g->launches++;
+    if (g->kprof) {
+        cudaEventRecord(g->ev1, g->stream);
+        cudaEventSynchronize(g->ev1);
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, g->ev0, g->ev1);
+        KprofEntry &en = g->prof[name];
+        en.count++;
+        en.ms += ms;
+    }
+    return LLMTIE_OK;
+}
+
+#define NEED_HANDLE(g)                                                          \
+    do {                                                                        \
+        if (!(g)) return llmtie_fail(LLMTIE_ERR_INVALID, "null device handle"); \
+        cudaSetDevice((g)->ordinal);                                            \
+    } while (0)
+
+// ---- handle ---------------------------------------------------------------
+
+static llmtie_status open_impl(int32_t ordinal, void *stream, bool adopt, llmtie_gpu **out)
+{
+    if (!out) return llmtie_fail(LLMTIE_ERR_INVALID, "null output handle");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return llmtie_fail(LLMTIE_ERR_NO_DEVICE, "no usable CUDA device: %s",
+                           e != cudaSuccess ? cudaGetErrorString(e) : "no device present");
+    }
+    if (ordinal < 0 || ordinal >= count) {
+        return llmtie_fail(LLMTIE_ERR_NO_DEVICE, "no usable CUDA device: ordinal %d of %d",
+                           ordinal, count);
+    }
+    e = cudaSetDevice(ordinal);
+    if (e != cudaSuccess) {
+        return llmtie_fail(LLMTIE_ERR_NO_DEVICE, "no usable CUDA device: %s",
+                           cudaGetErrorString(e));
+    }
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, ordinal);
+    if (e != cudaSuccess) return driver_fail("reading device properties", e);
+    if (prop.major != 10) {
+        // The kernels are compiled for sm_100a only; there is nothing to fall
+        // back to, so a different part is "kernel not in the module".
+        return llmtie_fail(LLMTIE_ERR_MISSING_KERNEL,
+                           "kernels are built for sm_100a, device %d is sm_%d%d", ordinal,
+                           prop.major, prop.minor);
+    }
+    llmtie_gpu *g = new (std::nothrow) llmtie_gpu();
+    if (!g) return llmtie_fail(LLMTIE_ERR_DRIVER, "allocating the handle");
+    g->ordinal = ordinal;
+    g->sm_count = prop.multiProcessorCount;
+    if (adopt) {
+        g->stream = (cudaStream_t)stream;
+        g->owns_stream = false;
+    } else {
+        e = cudaStreamCreateWithFlags(&g->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            delete g;
+            return driver_fail("creating the stream", e);
+        }
+        g->owns_stream = true;
+    }
+    cudaEventCreate(&g->ev0);
+    cudaEventCreate(&g->ev1);
+    // Keep freed blocks in the pool rather than returning them to the
+    // driver between calls (device.rs:769-781).
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, ordinal) == cudaSuccess) {
+        uint64_t keep = UINT64_MAX;
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    e = cudaMalloc(&g->timeout_flag, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(g->timeout_flag, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        llmtie_close(g);
+        return driver_fail("allocating the status word", e);
+    }
+    *out = g;
+    return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_open(int32_t ordinal, llmtie_gpu **out)
+{
+    return open_impl(ordinal, nullptr, false, out);
+}
+
+extern "C" llmtie_status llmtie_open_on_stream(int32_t ordinal, void *stream, llmtie_gpu **out)
+{
+    return open_impl(ordinal, stream, true, out);
+}
+
+extern "C" void llmtie_close(llmtie_gpu *g)
+{
+    if (!g) return;
+    cudaSetDevice(g->ordinal);
+    if (g->stream) cudaStreamSynchronize(g->stream);
+    if (g->timeout_flag) cudaFree(g->timeout_flag);
+    if (g->ev0) cudaEventDestroy(g->ev0);
+    if (g->ev1) cudaEventDestroy(g->ev1);
+    if (g->owns_stream && g->stream) cudaStreamDestroy(g->stream);
+    delete g;
+}
+
+extern "C" void *llmtie_stream(llmtie_gpu *g) { return g ? (void *)g->stream : nullptr; }
+extern "C" int32_t llmtie_ordinal(llmtie_gpu *g) { return g ? g->ordinal : -1; }
+
+extern "C" llmtie_status llmtie_synchronize(llmtie_gpu *g)
+{
+    NEED_HANDLE(g);
+    const cudaError_t e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) return driver_fail("synchronizing", e);
+    int flag = 0;
+    cudaMemcpy(&flag, g->timeout_flag, sizeof(int), cudaMemcpyDeviceToHost);
+    if (flag != 0) {
+        cudaMemset(g->timeout_flag, 0, sizeof(int));
+        return llmtie_fail(LLMTIE_ERR_TIMEOUT, "a bounded device wait gave up (site %d)", flag);
+    }
+    return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_alloc(llmtie_gpu *g, size_t bytes, void **dptr)
+{
+    NEED_HANDLE(g);
+    if (!dptr) return llmtie_fail(LLMTIE_ERR_INVALID, "null output pointer");
+    cudaSetDevice(g->ordinal);
+    const cudaError_t e = cudaMallocAsync(dptr, bytes ? bytes : 1, g->stream);
+    if (e != cudaSuccess) return driver_fail("allocating", e);
+    return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_zeros(llmtie_gpu *g, size_t bytes, void **dptr)
+{
+    const llmtie_status s = llmtie_alloc(g, bytes, dptr);
+    if (s != LLMTIE_OK) return s;
+    const cudaError_t e = cudaMemsetAsync(*dptr, 0, bytes ? bytes : 1, g->stream);
+    if (e != cudaSuccess) return driver_fail("zeroing", e);
+    return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_free(llmtie_gpu *g, void *dptr)
+{
+    NEED_HANDLE(g);
+    if (!dptr) return LLMTIE_OK;
+    const cudaError_t e = cudaFreeAsync(dptr, g->stream);
+    if (e != cudaSuccess) return driver_fail("freeing", e);
+    return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_upload(llmtie_gpu *g, void *dst, const void *src, size_t bytes)
+{
+    NEED_HANDLE(g);
+    const cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g->stream);
+    if (e != cudaSuccess) return driver_fail("uploading", e);
+    return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_download(llmtie_gpu *g, void *dst, const void *src, size_t bytes)
+{
+    NEED_HANDLE(g);
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
+    if (e != cudaSuccess) return driver_fail("downloading", e);
+    return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_round_f16(llmtie_gpu *g, const float *src, uint16_t *dst,
+                                          size_t n)
+{
+    NEED_HANDLE(g);
+    LaunchScope ls(g, "round_f16");
+    launch_round_f16(g->stream, src, dst, n);
+    return ls.done();
+}
+
+// ---- KV-cache allocator ------------------------------------------------------
+
+extern "C" size_t llmtie_kv_want_capacity(size_t cap, size_t past, size_t n,
+                                          size_t max_positions)
+{
+    if (cap >= past + n) return 0;
+    const size_t reserve = n > 1 ? 256 : 0;
+    size_t want = std::max<size_t>(next_pow2(past + n + reserve), 256);
+    want = std::min(want, std::max(max_positions, past + n));
+    return want;
+}
+
+extern "C" llmtie_status llmtie_kv_alloc_f16(llmtie_gpu *g, size_t kv_heads, size_t head_dim,
+                                             size_t cap, uint16_t **k, uint16_t **v)
+{
+    NEED_HANDLE(g);
+    if (!k || !v) return llmtie_fail(LLMTIE_ERR_INVALID, "null output pointer");
+    if (cap % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    const size_t bytes = kv_heads * head_dim * cap * sizeof(uint16_t);
+    llmtie_status s = llmtie_zeros(g, bytes, (void **)k);
+    if (s != LLMTIE_OK) return s;
+    s = llmtie_zeros(g, bytes, (void **)v);
+    if (s != LLMTIE_OK) {
+        llmtie_free(g, *k);
+        *k = nullptr;
+    }
+    return s;
+}
+
+static llmtie_status grow_impl(llmtie_gpu *g, const void *src, size_t src_len, void *dst,
+                               size_t dst_len, size_t kv_heads, size_t hd, size_t old_cap,
+                               size_t new_cap, size_t live, bool transposed, int esize,
+                               const char *name)
+{
+    NEED_HANDLE(g);
+    if (live > old_cap || new_cap < old_cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu",
+                           std::max(live, old_cap), std::min(new_cap, old_cap));
+    }
+    const size_t rows = transposed ? kv_heads * hd : kv_heads;
+    const size_t len = transposed ? live : live * hd;
+    const size_t ss = transposed ? old_cap : old_cap * hd;
+    const size_t ds = transposed ? new_cap : new_cap * hd;
+    if (rows * ss > src_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           rows * ss, src_len);
+    }
+    if (rows * ds > dst_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           rows * ds, dst_len);
+    }
+    if (rows * len == 0) return LLMTIE_OK;
+    LaunchScope ls(g, name);
+    launch_cache_grow(g->stream, src, dst, (long long)rows, (long long)len, (long long)ss,
+                      (long long)ds, esize);
+    return ls.done();
+}
+
+extern "C" llmtie_status llmtie_cache_grow_f16(llmtie_gpu *g, const uint16_t *src,
+                                               size_t src_len, uint16_t *dst, size_t dst_len,
+                                               size_t kv_heads, size_t head_dim, size_t old_cap,
+                                               size_t new_cap, size_t live, int32_t transposed)
+{
+    return grow_impl(g, src, src_len, dst, dst_len, kv_heads, head_dim, old_cap, new_cap, live,
+                     transposed != 0, 2, "cache_grow_f16");
+}
+
+extern "C" llmtie_status llmtie_cache_grow(llmtie_gpu *g, const float *src, size_t src_len,
+                                           float *dst, size_t dst_len, size_t kv_heads,
+                                           size_t head_dim, size_t old_cap, size_t new_cap,
+                                           size_t live, int32_t transposed)
+{
+    return grow_impl(g, src, src_len, dst, dst_len, kv_heads, head_dim, old_cap, new_cap, live,
+                     transposed != 0, 4, "cache_grow");
+}
+
+static llmtie_status append_impl(llmtie_gpu *g, const float *src, size_t src_len,
+                                 size_t src_off, void *dst, size_t dst_len, size_t n,
+                                 size_t kv_heads, size_t hd, size_t cap, size_t past,
+                                 bool transposed, bool f16)
+{
+    NEED_HANDLE(g);
+    if (past + n > cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", past + n, cap);
+    }
+    if (f16 && cap % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    const size_t total = n * kv_heads * hd;
+    if (src_off + total > src_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           src_off + total, src_len);
+    }
+    if (kv_heads * hd * cap > dst_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           kv_heads * hd * cap, dst_len);
+    }
+    if (!fits_i32(cap) || !fits_i32(n) || !fits_i32(kv_heads * hd)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "cache geometry does not fit 32 bits");
+    }
+    if (total == 0) return LLMTIE_OK;
+    const char *name = f16 ? (transposed ? "cache_append_t_f16" : "cache_append_f16")
+                           : (transposed ? "cache_append_t" : "cache_append");
+    LaunchScope ls(g, name);
+    launch_cache_append(g->stream, src, (long long)src_off, dst, (int)n, (int)kv_heads, (int)hd,
+                        (int)cap, (int)past, transposed, f16);
+    return ls.done();
+}
+
+extern "C" llmtie_status llmtie_cache_append_f16(llmtie_gpu *g, const float *src,
+                                                 size_t src_len, size_t src_off, uint16_t *dst,
+                                                 size_t dst_len, size_t n, size_t kv_heads,
+                                                 size_t head_dim, size_t cap, size_t past,
+                                                 int32_t transposed)
+{
+    return append_impl(g, src, src_len, src_off, dst, dst_len, n, kv_heads, head_dim, cap, past,
+                       transposed != 0, true);
+}
+
+extern "C" llmtie_status llmtie_cache_append(llmtie_gpu *g, const float *src, size_t src_len,
+                                             size_t src_off, float *dst, size_t dst_len,
+                                             size_t n, size_t kv_heads, size_t head_dim,
+                                             size_t cap, size_t past, int32_t transposed)
+{
+    return append_impl(g, src, src_len, src_off, dst, dst_len, n, kv_heads, head_dim, cap, past,
+                       transposed != 0, false);
+}
+
+// ---- RoPE ---------------------------------------------------------------------
+
+extern "C" llmtie_status llmtie_rope_scaled(llmtie_gpu *g, float *x, size_t x_len, size_t off,
+                                            const float *freq_div, size_t t, size_t heads,
+                                            size_t head_dim, float theta, size_t first)
+{
+    NEED_HANDLE(g);
+    if (head_dim % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_HEAD_DIM, "a rotary head of odd width %zu", head_dim);
+    }
+    if (off + t * heads * head_dim > x_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           off + t * heads * head_dim, x_len);
+    }
+    if (!fits_i32(t) || !fits_i32(heads * head_dim) || !fits_i32(first + t)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "rope geometry does not fit 32 bits");
+    }
+    if (t * heads * head_dim == 0) return LLMTIE_OK;
+    LaunchScope ls(g, "rope");
+    launch_rope(g->stream, x, (long long)off, freq_div, (int)t, (int)heads, (int)head_dim, theta,
+                (int)first);
+    return ls.done();
+}
+
+extern "C" llmtie_status llmtie_rope_cache_f16(llmtie_gpu *g, float *q, size_t q_len,
+                                               size_t q_off, const float *k, size_t k_len,
+                                               size_t k_off, const float *v, size_t v_len,
+                                               size_t v_off, const float *freq_div, size_t heads,
+                                               size_t kv_heads, size_t head_dim, float theta,
+                                               size_t pos, uint16_t *kc, size_t kc_len,
+                                               uint16_t *vc, size_t vc_len, size_t cap)
+{
+    NEED_HANDLE(g);
+    if (pos >= cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", pos + 1, cap);
+    }
+    if (cap % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    if (head_dim % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_HEAD_DIM, "a rotary head of odd width %zu", head_dim);
+    }
+    const size_t spans[3][3] = {{q_off, heads * head_dim, q_len},
+                                {k_off, kv_heads * head_dim, k_len},
+                                {v_off, kv_heads * head_dim, v_len}};
+    for (const auto &s : spans) {
+        if (s[0] + s[1] > s[2]) {
+            return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                               s[0] + s[1], s[2]);
+        }
+    }
+    const size_t want = cap * kv_heads * head_dim;
+    if (kc_len < want || vc_len < want) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", want,
+                           std::min(kc_len, vc_len));
+    }
+    if (!fits_i32(cap) || !fits_i32(heads * head_dim)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "cache geometry does not fit 32 bits");
+    }
+    LaunchScope ls(g, "rope_cache_f16");
+    launch_rope_cache_f16(g->stream, q, (long long)q_off, k, (long long)k_off, v,
+                          (long long)v_off, freq_div, (int)heads, (int)kv_heads, (int)head_dim,
+                          theta, (int)pos, kc, vc, (int)cap);
+    return ls.done();
+}
+
+// ---- prefill / encoder attention -----------------------------------------------
+
+extern "C" int32_t llmtie_supports_flash(size_t head_dim, size_t heads, size_t kv_heads)
+{
+    return (head_dim == 64 || head_dim == 128) && heads % std::max<size_t>(kv_heads, 1) == 0;
+}
+
+static llmtie_status unsupported(size_t hd, size_t heads, size_t kv)
+{
+    return llmtie_fail(LLMTIE_ERR_UNSUPPORTED_ATTENTION,
+                       "fused attention wants head_dim 64 or 128 and heads a multiple of "
+                       "kv_heads, got head_dim %zu, %zu heads over %zu",
+                       hd, heads, kv);
+}
+
+static llmtie_status misaligned(const char *what, const void *p, size_t align)
+{
+    return llmtie_fail(LLMTIE_ERR_MISALIGNED, "%s starts at %zu, which is not a multiple of %zu",
+                       what, (size_t)(uintptr_t)p, align);
+}
+
+// One sequence through the general kernel.
+static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q, size_t q_len,
+                                const void *k, size_t k_len, const void *v, size_t v_len,
+                                void *out, size_t out_len, size_t tq, size_t past, size_t heads,
+                                size_t kv_heads, size_t hd, size_t cap, float scale, bool causal,
+                                bool kv_f32)
+{
+    NEED_HANDLE(g);
+    if (kv_heads == 0 || heads % kv_heads != 0) return unsupported(hd, heads, kv_heads);
+    if (past + tq > cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", past + tq, cap);
+    }
+    if (tq * heads * hd > q_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           tq * heads * hd, q_len);
+    }
+    if (tq * heads * hd > out_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           tq * heads * hd, out_len);
+    }
+    const size_t need = kv_heads * cap * hd;
+    if (k_len < need || v_len < need) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", need,
+                           std::min(k_len, v_len));
+    }
+    if (((uintptr_t)q & 15u) != 0) return misaligned("the query", q, 16);
+    if (((uintptr_t)k & 15u) != 0) return misaligned("the key cache", k, 16);
+    if (((uintptr_t)out & 7u) != 0) return misaligned("the output", out, 8);
+    if (!fits_i32(cap) || !fits_i32(tq) || !fits_i32(heads * hd)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "attention geometry does not fit 32 bits");
+    }
+    if (tq == 0) return LLMTIE_OK;
+    PrefillParams p;
+    memset(&p, 0, sizeof(p));
+    p.nseq = 1;
+    p.seq[0].k = k;
+    p.seq[0].v = v;
+    p.seq[0].row0 = 0;
+    p.seq[0].tq = (int)tq;
+    p.seq[0].past = (int)past;
+    p.seq[0].cap = (int)cap;
+    p.seq[0].tk = (int)(past + tq);
+    p.q = q;
+    p.q_stride = (long long)(heads * hd);
+    p.out = out;
+    p.out_stride = (long long)(heads * hd);
+    p.heads = (int)heads;
+    p.kv_heads = (int)kv_heads;
+    p.causal = causal ? 1 : 0;
+    p.kv_f32 = kv_f32 ? 1 : 0;
+    p.out_f16 = 0;
+    p.q_scale = 1.0f;
+    p.sl2 = scale * kLog2e;
+    LaunchScope ls(g, name);
+    const cudaError_t e = launch_prefill_mma(g->stream, p, (int)hd);
+    if (e != cudaSuccess) return driver_fail(name, e);
+    return ls.done();
+}
+
+extern "C" llmtie_status llmtie_flash_attn_f16(llmtie_gpu *g, const float *q, size_t q_len,
+                                               const uint16_t *k, size_t k_len,
+                                               const uint16_t *v, size_t v_len, float *out,
+                                               size_t out_len, size_t tq, size_t past,
+                                               size_t heads, size_t kv_heads, size_t head_dim,
+                                               size_t cap, float scale, int32_t causal)
+{
+    if (head_dim != 128) return unsupported(head_dim, heads, kv_heads);
+    if (cap % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    return flash_impl(g, "flash_attn_h", q, q_len, k, k_len, v, v_len, out, out_len, tq, past,
+                      heads, kv_heads, head_dim, cap, scale, causal != 0, false);
+}
+
+extern "C" llmtie_status llmtie_flash_attn(llmtie_gpu *g, const float *q, size_t q_len,
+                                           const float *k, size_t k_len, const float *v,
+                                           size_t v_len, float *out, size_t out_len, size_t tq,
+                                           size_t past, size_t heads, size_t kv_heads,
+                                           size_t head_dim, size_t cap, float scale,
+                                           int32_t causal)
+{
+    if (head_dim != 64 && head_dim != 128) return unsupported(head_dim, heads, kv_heads);
+    return flash_impl(g, head_dim == 128 ? "flash_attn" : "flash_attn_64", q, q_len, k, k_len, v,
+                      v_len, out, out_len, tq, past, heads, kv_heads, head_dim, cap, scale,
+                      causal != 0, true);
+}
+
+static size_t rows_pad(size_t t) { return (t + 127) / 128 * 128; }
+
+extern "C" size_t llmtie_flash_rows_work_bytes(size_t t, size_t heads, size_t head_dim)
+{
+    return 2 * heads * rows_pad(t) * head_dim * sizeof(uint16_t);
+}
+
+extern "C" llmtie_status llmtie_flash_attn_rows(llmtie_gpu *g, const float *qkv, size_t qkv_len,
+                                                uint16_t *out, size_t out_len, size_t t,
+                                                size_t heads, size_t head_dim, float scale,
+                                                void *work, size_t work_bytes)
+{
+    NEED_HANDLE(g);
+    if (head_dim != 64) return unsupported(head_dim, heads, heads);
+    const size_t d = heads * head_dim;
+    if (qkv_len < t * 3 * d) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           t * 3 * d, qkv_len);
+    }
+    if (out_len < t * d) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", t * d,
+                           out_len);
+    }
+    if (((uintptr_t)qkv & 15u) != 0) return misaligned("the stacked product", qkv, 16);
+    if (((uintptr_t)out & 3u) != 0) return misaligned("the output", out, 4);
+    if (!fits_i32(t) || !fits_i32(3 * d)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "attention geometry does not fit 32 bits");
+    }
+    if (t == 0 || heads == 0) return LLMTIE_OK;
+    const size_t need = llmtie_flash_rows_work_bytes(t, heads, head_dim);
+    void *own = nullptr;
+    if (work) {
+        if (work_bytes < need) {
+            return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                               need, work_bytes);
+        }
+        if (((uintptr_t)work & 15u) != 0) return misaligned("the work buffer", work, 16);
+    } else {
+        const llmtie_status s = llmtie_alloc(g, need, &own);
+        if (s != LLMTIE_OK) return s;
+        work = own;
+    }
+    const size_t tp = rows_pad(t);
+    uint16_t *ks = (uint16_t *)work;
+    uint16_t *vs = ks + heads * tp * head_dim;
+    llmtie_status st;
+    {
+        LaunchScope ls(g, "rows_stage");
+        launch_rows_stage(g->stream, qkv, ks, vs, (int)t, (int)tp, (int)heads, (int)head_dim);
+        st = ls.done();
+    }
+    if (st == LLMTIE_OK) {
+        PrefillParams p;
+        memset(&p, 0, sizeof(p));
+        p.nseq = 1;
+        p.seq[0].k = ks;
+        p.seq[0].v = vs;
+        p.seq[0].tq = (int)t;
+        p.seq[0].cap = (int)tp;
+        p.seq[0].tk = (int)t;
+        p.q = qkv;
+        p.q_stride = (long long)(3 * d);
+        p.out = out;
+        p.out_stride = (long long)d;
+        p.heads = (int)heads;
+        p.kv_heads = (int)heads;
+        p.causal = 0;
+        p.kv_f32 = 0;
+        p.out_f16 = 1;
+        p.q_scale = scale;   // on q before it is rounded, as the encoder does
+        p.sl2 = kLog2e;
+        LaunchScope ls(g, "flash_attn_64_rows");
+        const cudaError_t e = launch_prefill_mma(g->stream, p, 64);
+        st = (e != cudaSuccess) ? driver_fail("flash_attn_64_rows", e) : ls.done();
+    }
+    if (own) llmtie_free(g, own);
+    return st;
+}
+
+// ---- decode attention -----------------------------------------------------------
+
+extern "C" llmtie_status llmtie_decode_scratch_new(llmtie_gpu *g, llmtie_decode_scratch **out)
+{
+    NEED_HANDLE(g);
+    if (!out) return llmtie_fail(LLMTIE_ERR_INVALID, "null output pointer");
+    *out = new (std::nothrow) llmtie_decode_scratch();
+    if (!*out) return llmtie_fail(LLMTIE_ERR_DRIVER, "allocating the scratch");
+    return LLMTIE_OK;
+}
+
+extern "C" void llmtie_decode_scratch_free(llmtie_gpu *g, llmtie_decode_scratch *s)
+{
+    if (!s) return;
+    if (g) {
+        if (s->part) cudaFreeAsync(s->part, g->stream);
+        if (s->ctr) cudaFreeAsync(s->ctr, g->stream);
+    }
+    delete s;
+}
+
+// Grows the scratch to hold `pairs` heads of `splits` partials. Stream-ordered,
+// so a kernel still reading the old buffers is not disturbed; counters are
+// zero when allocated and every launch leaves them at zero.
+static llmtie_status scratch_reserve(llmtie_gpu *g, llmtie_decode_scratch *s, size_t pairs,
+                                     size_t splits, size_t hd)
+{
+    const size_t floats = pairs * splits * 8 * (hd + 2);
+    if (floats > s->part_floats) {
+        if (s->part) cudaFreeAsync(s->part, g->stream);
+        s->part = nullptr;
+        s->part_floats = 0;
+        const size_t want = next_pow2(floats);
+        const cudaError_t e = cudaMallocAsync((void **)&s->part, want * sizeof(float), g->stream);
+        if (e != cudaSuccess) return driver_fail("allocating", e);
+        s->part_floats = want;
+    }
+    if (pairs > s->ctr_words) {
+        if (s->ctr) cudaFreeAsync(s->ctr, g->stream);
+        s->ctr = nullptr;
+        s->ctr_words = 0;
+        const size_t want = next_pow2(pairs);
+        cudaError_t e = cudaMallocAsync((void **)&s->ctr, want * sizeof(unsigned), g->stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(s->ctr, 0, want * sizeof(unsigned), g->stream);
+        if (e != cudaSuccess) return driver_fail("allocating", e);
+        s->ctr_words = want;
+    }
+    return LLMTIE_OK;
+}
+
+// Picks the span of keys a block takes so that one wave of blocks covers the
+// whole launch: every block is resident at once and they finish together.
+static void decode_plan(llmtie_gpu *g, DecodeParams &p, int hd)
+{
+    const int slots = decode_resident_blocks(hd, g->sm_count);
+    long long units = 0;   // 128-key units over every (sequence, kv head, row chunk)
+    int max_tk = 0;
+    for (int b = 0; b < p.nseq; b++) {
+        units += (long long)((p.seq[b].tk + 127) / 128) * p.kv_heads * p.row_chunks;
+        max_tk = std::max(max_tk, p.seq[b].tk);
+    }
+    const long long per = std::max<long long>(1, (units + slots - 1) / slots);
+    p.span = (int)(per * 128);
+    p.max_splits = (max_tk + p.span - 1) / p.span;
+}
+
+static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams &p, int hd,
+                                   llmtie_decode_scratch *scratch)
+{
+    decode_plan(g, p, hd);
+    const size_t pairs = (size_t)p.nseq * p.row_chunks * p.kv_heads;
+    const llmtie_status s = scratch_reserve(g, scratch, pairs, (size_t)p.max_splits, (size_t)hd);
+    if (s != LLMTIE_OK) return s;
+    p.part = scratch->part;
+    p.ctr = scratch->ctr;
+    LaunchScope ls(g, name);
+    const cudaError_t e = launch_decode_f16(g->stream, p, hd);
+    if (e != cudaSuccess) return driver_fail(name, e);
+    return ls.done();
+}
+
+extern "C" llmtie_status llmtie_attn_decode_f16(llmtie_gpu *g, const float *q, size_t q_len,
+                                                size_t q_off, const uint16_t *k, size_t k_len,
+                                                const uint16_t *v, size_t v_len, size_t heads,
+                                                size_t kv_heads, size_t head_dim, size_t tk,
+                                                size_t cap, float scale, int32_t scale_q,
+                                                llmtie_decode_scratch *scratch, float *out,
+                                                size_t out_len, size_t out_off)
+{
+    NEED_HANDLE(g);
+    if (!scratch) return llmtie_fail(LLMTIE_ERR_INVALID, "null decode scratch");
+    if (cap % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    if (head_dim != 64 && head_dim != 128) return unsupported(head_dim, heads, kv_heads);
+    // The widest query group the reference's instantiations carry: four at
+    // 128, eight at 64 (device.rs:6043-6049, :6245-6252).
+    const size_t gmax = head_dim == 128 ? 4 : 8;
+    if (kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > gmax) {
+        return unsupported(head_dim, heads, kv_heads);
+    }
+    if (tk == 0 || tk > cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", tk, cap);
+    }
+    if ((cap * 2) % 8 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    const size_t need = kv_heads * cap * head_dim;
+    if (k_len < need || v_len < need) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", need,
+                           std::min(k_len, v_len));
+    }
+    const size_t n = heads * head_dim;
+    if (q_len < q_off + n) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           q_off + n, q_len);
+    }
+    if (out_len < out_off + n) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           out_off + n, out_len);
+    }
+    if (out_off % 32 != 0) {
+        return llmtie_fail(LLMTIE_ERR_RAGGED_BLOCK,
+                           "a row of %zu does not divide into blocks of 32", out_off);
+    }
+    if (((uintptr_t)k & 15u) != 0) return misaligned("the key cache", k, 16);
+    if (((uintptr_t)v & 7u) != 0) return misaligned("the value cache", v, 8);
+    if (!fits_i32(cap)) return llmtie_fail(LLMTIE_ERR_INVALID, "capacity does not fit 32 bits");
+    const size_t group = heads / kv_heads;
+    DecodeParams p;
+    memset(&p, 0, sizeof(p));
+    p.nseq = 1;
+    p.seq[0].k = k;
+    p.seq[0].v = v;
+    p.seq[0].tk = (int)tk;
+    p.seq[0].cap = (int)cap;
+    p.q = q + q_off;
+    p.q_kv = (long long)(group * head_dim);
+    p.q_row = (long long)head_dim;
+    p.out = out + out_off;
+    p.out_kv = (long long)(group * head_dim);
+    p.out_row = (long long)head_dim;
+    p.rows = (int)group;
+    p.row_chunks = 1;
+    p.kv_heads = (int)kv_heads;
+    p.partial = 0;
+    p.q_scale = scale_q ? scale : 1.0f;
+    p.sl2 = (scale_q ? 1.0f : scale) * kLog2e;
+    return decode_launch(g, head_dim == 128 ? "attn_decode_h128" : "attn_decode_h64", p,
+                         (int)head_dim, scratch);
+}
+
+extern "C" llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_t q_len,
+                                            size_t q_off, const float *k, size_t k_len,
+                                            const float *v, size_t v_len, size_t heads,
+                                            size_t kv_heads, size_t head_dim, size_t tk,
+                                            size_t cap, float scale, int32_t scale_q,
+                                            llmtie_decode_scratch *scratch, float *out,
+                                            size_t out_len, size_t out_off)
+{
+    NEED_HANDLE(g);
+    (void)scratch;   // the f32 cache is a few hundred keys: one block a head, no partials
+    if (head_dim != 64) return unsupported(head_dim, heads, kv_heads);
+    if (kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > 8) {
+        return unsupported(head_dim, heads, kv_heads);
+    }
+    if (tk == 0 || tk > cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", tk, cap);
+    }
+    if ((cap * 4) % 8 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    const size_t need = kv_heads * cap * head_dim;
+    if (k_len < need || v_len < need) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", need,
+                           std::min(k_len, v_len));
+    }
+    const size_t n = heads * head_dim;
+    if (q_len < q_off + n) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           q_off + n, q_len);
+    }
+    if (out_len < out_off + n) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           out_off + n, out_len);
+    }
+    if (out_off % 32 != 0) {
+        return llmtie_fail(LLMTIE_ERR_RAGGED_BLOCK,
+                           "a row of %zu does not divide into blocks of 32", out_off);
+    }
+    if (!fits_i32(cap)) return llmtie_fail(LLMTIE_ERR_INVALID, "capacity does not fit 32 bits");
+    LaunchScope ls(g, "attn_decode_f64");
+    launch_decode_f32(g->stream, q, (long long)q_off, k, v, out, (long long)out_off, (int)heads,
+                      (int)kv_heads, (int)head_dim, (int)tk, (int)cap, scale_q ? scale : 1.0f,
+                      scale_q ? 1.0f : scale);
+    return ls.done();
+}
+
+extern "C" llmtie_status llmtie_decode_batched(llmtie_gpu *g, const float *q, size_t q_len,
+                                               const uint16_t *const *k_ptrs,
+                                               const uint16_t *const *v_ptrs, const int32_t *tk,
+                                               const int32_t *cap, size_t batch, size_t heads,
+                                               size_t kv_heads, size_t head_dim, float scale,
+                                               int32_t scale_q, llmtie_decode_scratch *scratch,
+                                               float *out, size_t out_len, int32_t partial)
+{
+    NEED_HANDLE(g);
+    if (!scratch) return llmtie_fail(LLMTIE_ERR_INVALID, "null decode scratch");
+    if (!k_ptrs || !v_ptrs || !tk || !cap) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "null sequence table");
+    }
+    if (head_dim != 64 && head_dim != 128) return unsupported(head_dim, heads, kv_heads);
+    if (kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > 8) {
+        return unsupported(head_dim, heads, kv_heads);
+    }
+    const size_t n = heads * head_dim;
+    const size_t on = partial ? heads * (head_dim + 2) : n;
+    if (q_len < batch * n) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           batch * n, q_len);
+    }
+    if (out_len < batch * on) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           batch * on, out_len);
+    }
+    for (size_t b = 0; b < batch; b++) {
+        if (cap[b] <= 0 || cap[b] % 4 != 0) {
+            return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                               "an f16 cache with an odd capacity of %d", cap[b]);
+        }
+        if (tk[b] <= 0 || tk[b] > cap[b]) {
+            return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                               "appending at %d to a cache with room for %d", tk[b], cap[b]);
+        }
+        if (((uintptr_t)k_ptrs[b] & 15u) != 0) return misaligned("a key cache", k_ptrs[b], 16);
+        if (((uintptr_t)v_ptrs[b] & 7u) != 0) return misaligned("a value cache", v_ptrs[b], 8);
+    }
+    const size_t group = heads / kv_heads;
+    const size_t ostride = partial ? head_dim + 2 : head_dim;
+    for (size_t b0 = 0; b0 < batch; b0 += LLMTIE_DECODE_MAX_SEQ) {
+        const size_t nb = std::min<size_t>(LLMTIE_DECODE_MAX_SEQ, batch - b0);
+        DecodeParams p;
+        memset(&p, 0, sizeof(p));
+        p.nseq = (int)nb;
+        for (size_t b = 0; b < nb; b++) {
+            p.seq[b].k = k_ptrs[b0 + b];
+            p.seq[b].v = v_ptrs[b0 + b];
+            p.seq[b].tk = tk[b0 + b];
+            p.seq[b].cap = cap[b0 + b];
+        }
+        p.q = q + b0 * n;
+        p.q_seq = (long long)n;
+        p.q_kv = (long long)(group * head_dim);
+        p.q_row = (long long)head_dim;
+        p.out = out + b0 * on;
+        p.out_seq = (long long)on;
+        p.out_kv = (long long)(group * ostride);
+        p.out_row = (long long)ostride;
+        p.rows = (int)group;
+        p.row_chunks = 1;
+        p.kv_heads = (int)kv_heads;
+        p.partial = partial ? 1 : 0;
+        p.q_scale = scale_q ? scale : 1.0f;
+        p.sl2 = (scale_q ? 1.0f : scale) * kLog2e;
+        const llmtie_status s = decode_launch(
+            g, head_dim == 128 ? "attn_decode_h128" : "attn_decode_h64", p, (int)head_dim,
+            scratch);
+        if (s != LLMTIE_OK) return s;
+    }
+    return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_lse_merge(llmtie_gpu *g, const float *parts_buf,
+                                          size_t parts_len, size_t parts, size_t rows,
+                                          size_t head_dim, float *out, size_t out_len)
+{
+    NEED_HANDLE(g);
+    if (parts_len < parts * rows * (head_dim + 2)) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           parts * rows * (head_dim + 2), parts_len);
+    }
+    if (out_len < rows * head_dim) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           rows * head_dim, out_len);
+    }
+    if (head_dim == 0 || head_dim > 1024) return unsupported(head_dim, rows, rows);
+    if (parts == 0 || rows == 0) return LLMTIE_OK;
+    LaunchScope ls(g, "lse_merge");
+    launch_lse_merge(g->stream, parts_buf, (int)parts, (int)rows, (int)head_dim, out);
+    return ls.done();
+}
+
+extern "C" llmtie_status llmtie_cross_attn(llmtie_gpu *g, const float *q, size_t q_len,
+                                           const uint16_t *k, size_t k_len, const uint16_t *v,
+                                           size_t v_len, size_t n, size_t heads, size_t head_dim,
+                                           size_t tk, size_t cap, float scale,
+                                           llmtie_decode_scratch *scratch, float *out,
+                                           size_t out_len)
+{
+    NEED_HANDLE(g);
+    if (!scratch) return llmtie_fail(LLMTIE_ERR_INVALID, "null decode scratch");
+    if (head_dim != 64 && head_dim != 128) return unsupported(head_dim, heads, heads);
+    if (heads == 0) return unsupported(head_dim, heads, heads);
+    if (tk == 0 || tk > cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", tk, cap);
+    }
+    if (cap % 4 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    const size_t need = heads * cap * head_dim;
+    if (k_len < need || v_len < need) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", need,
+                           std::min(k_len, v_len));
+    }
+    const size_t d = heads * head_dim;
+    if (q_len < n * d || out_len < n * d) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", n * d,
+                           std::min(q_len, out_len));
+    }
+    if (((uintptr_t)k & 15u) != 0) return misaligned("the key cache", k, 16);
+    if (((uintptr_t)v & 7u) != 0) return misaligned("the value cache", v, 8);
+    if (!fits_i32(cap) || !fits_i32(n * d)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "attention geometry does not fit 32 bits");
+    }
+    if (n == 0) return LLMTIE_OK;
+    // The query rows of one head share its keys exactly as a GQA group's
+    // heads do, so they ride the decode kernel eight rows a block.
+    DecodeParams p;
+    memset(&p, 0, sizeof(p));
+    p.nseq = 1;
+    p.seq[0].k = k;
+    p.seq[0].v = v;
+    p.seq[0].tk = (int)tk;
+    p.seq[0].cap = (int)cap;
+    p.q = q;
+    p.q_kv = (long long)head_dim;
+    p.q_row = (long long)d;
+    p.out = out;
+    p.out_kv = (long long)head_dim;
+    p.out_row = (long long)d;
+    p.rows = (int)n;
+    p.row_chunks = (int)((n + 7) / 8);
+    p.kv_heads = (int)heads;
+    p.partial = 0;
+    p.q_scale = scale;
+    p.sl2 = kLog2e;
+    return decode_launch(g, head_dim == 128 ? "cross_attn_h128" : "cross_attn_h64", p,
+                         (int)head_dim, scratch);
+}
+
+extern "C" llmtie_status llmtie_prefill_varlen(
+    llmtie_gpu *g, float *q, size_t q_len, const float *k, size_t k_len, const float *v,
+    size_t v_len, const int32_t *cu_seqlens, size_t batch, uint16_t *const *k_ptrs,
+    uint16_t *const *v_ptrs, const int32_t *past, const int32_t *cap, const float *freq_div,
+    size_t heads, size_t kv_heads, size_t head_dim, float theta, float scale, float *out,
+    size_t out_len)
+{
+    NEED_HANDLE(g);
+    if (!cu_seqlens || !k_ptrs || !v_ptrs || !past || !cap) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "null sequence table");
+    }
+    if (head_dim != 128) return unsupported(head_dim, heads, kv_heads);
+    if (kv_heads == 0 || heads % kv_heads != 0) return unsupported(head_dim, heads, kv_heads);
+    if (batch == 0) return LLMTIE_OK;
+    const size_t total = (size_t)cu_seqlens[batch];
+    if (q_len < total * heads * head_dim || out_len < total * heads * head_dim) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           total * heads * head_dim, std::min(q_len, out_len));
+    }
+    if (k_len < total * kv_heads * head_dim || v_len < total * kv_heads * head_dim) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           total * kv_heads * head_dim, std::min(k_len, v_len));
+    }
+    if (((uintptr_t)q & 15u) != 0) return misaligned("the query", q, 16);
+    if (((uintptr_t)out & 7u) != 0) return misaligned("the output", out, 8);
+    for (size_t b = 0; b < batch; b++) {
+        const int n = cu_seqlens[b + 1] - cu_seqlens[b];
+        if (n < 0) return llmtie_fail(LLMTIE_ERR_INVALID, "cu_seqlens is not ascending");
+        if (cap[b] % 2 != 0) {
+            return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                               "an f16 cache with an odd capacity of %d", cap[b]);
+        }
+        if (past[b] < 0 || past[b] + n > cap[b]) {
+            return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                               "appending at %d to a cache with room for %d", past[b] + n,
+                               cap[b]);
+        }
+        if (((uintptr_t)k_ptrs[b] & 15u) != 0) return misaligned("a key cache", k_ptrs[b], 16);
+    }
+    for (size_t b0 = 0; b0 < batch; b0 += LLMTIE_PREFILL_MAX_SEQ) {
+        const size_t nb = std::min<size_t>(LLMTIE_PREFILL_MAX_SEQ, batch - b0);
+        VarlenParams vp;
+        PrefillParams pp;
+        memset(&vp, 0, sizeof(vp));
+        memset(&pp, 0, sizeof(pp));
+        const int base = cu_seqlens[b0];
+        vp.nseq = pp.nseq = (int)nb;
+        for (size_t b = 0; b < nb; b++) {
+            const int row0 = cu_seqlens[b0 + b] - base;
+            const int n = cu_seqlens[b0 + b + 1] - cu_seqlens[b0 + b];
+            vp.seq[b] = {k_ptrs[b0 + b], v_ptrs[b0 + b], row0, n, past[b0 + b], cap[b0 + b]};
+            pp.seq[b].k = k_ptrs[b0 + b];
+            pp.seq[b].v = v_ptrs[b0 + b];
+            pp.seq[b].row0 = row0;
+            pp.seq[b].tq = n;
+            pp.seq[b].past = past[b0 + b];
+            pp.seq[b].cap = cap[b0 + b];
+            pp.seq[b].tk = past[b0 + b] + n;
+        }
+        vp.total = cu_seqlens[b0 + nb] - base;
+        vp.q = q + (size_t)base * heads * head_dim;
+        vp.k = k + (size_t)base * kv_heads * head_dim;
+        vp.v = v + (size_t)base * kv_heads * head_dim;
+        vp.freq_div = freq_div;
+        vp.heads = (int)heads;
+        vp.kv_heads = (int)kv_heads;
+        vp.hd = (int)head_dim;
+        vp.theta = theta;
+        {
+            LaunchScope ls(g, "varlen_rope_append");
+            launch_varlen_rope_append(g->stream, vp);
+            g->launches++;   // two kernels in that launcher
+            const llmtie_status s = ls.done();
+            if (s != LLMTIE_OK) return s;
+        }
+        pp.q = vp.q;
+        pp.q_stride = (long long)(heads * head_dim);
+        pp.out = out + (size_t)base * heads * head_dim;
+        pp.out_stride = (long long)(heads * head_dim);
+        pp.heads = (int)heads;
+        pp.kv_heads = (int)kv_heads;
+        pp.causal = 1;
+        pp.q_scale = 1.0f;
+        pp.sl2 = scale * kLog2e;
+        LaunchScope ls(g, "flash_attn_h");
+        const cudaError_t e = launch_prefill_mma(g->stream, pp, (int)head_dim);
+        if (e != cudaSuccess) return driver_fail("flash_attn_h", e);
+        const llmtie_status s = ls.done();
+        if (s != LLMTIE_OK) return s;
+    }
+    return LLMTIE_OK;
+}
+
+// ---- profiling -------------------------------------------------------------------
+
+extern "C" void llmtie_kprof_enable(llmtie_gpu *g, int32_t on)
+{
+    if (g) g->kprof = on != 0;
+}
+
+extern "C" void llmtie_kprof_reset(llmtie_gpu *g)
+{
+    if (g) g->prof.clear();
+}
+
+extern "C" size_t llmtie_kprof_report(llmtie_gpu *g, char *buf, size_t cap)
+{
+    if (!g) return 0;
+    std::string s;
+    for (const auto &kv : g->prof) {
+        char line[256];
+        snprintf(line, sizeof(line), "%s %llu %.6f\n", kv.first.c_str(),
+                 (unsigned long long)kv.second.count, kv.second.ms);
+        s += line;
+    }
+    if (buf && cap > 0) {
+        const size_t n = std::min(cap - 1, s.size());
+        memcpy(buf, s.data(), n);
+        buf[n] = 0;
+    }
+    return s.size() + 1;
+}
+
+extern "C" llmtie_status llmtie_kernel_resources(const char *name, int32_t *regs,
+                                                 int32_t *local_bytes, int32_t *shared_bytes)
+{
+    const void *fn = name ? llmtie_kernel_symbol(name) : nullptr;
+    if (!fn) {
+        return llmtie_fail(LLMTIE_ERR_MISSING_KERNEL, "kernel %s is not in the module",
+                           name ? name : "(null)");
+    }
+    cudaFuncAttributes a;
+    const cudaError_t e = cudaFuncGetAttributes(&a, fn);
+    if (e != cudaSuccess) return driver_fail("reading kernel attributes", e);
+    if (regs) *regs = a.numRegs;
+    if (local_bytes) *local_bytes = (int32_t)a.localSizeBytes;
+    if (shared_bytes) *shared_bytes = (int32_t)a.sharedSizeBytes;
+    return LLMTIE_OK;
+}
+
+extern "C" uint64_t llmtie_launch_count(llmtie_gpu *g) { return g ? g->launches : 0; }

@@ -1,0 +1,168 @@
+// Shared declarations for the llmtie_b200 library: the device handle, the
+// launch bookkeeping every entry point goes through, and the host-callable
+// launchers each kernel file exports to the C ABI in abi.cu.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/llmtie_b200.h"
+
+struct KprofEntry {
+    uint64_t count = 0;
+    double ms = 0.0;
+};
+
+struct llmtie_gpu {
+    int ordinal = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 0;
+    uint64_t launches = 0;
+    bool kprof = false;
+    std::map<std::string, KprofEntry> prof;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    // One word the kernels' bounded waits set when they give up.
+    int *timeout_flag = nullptr;
+};
+
+struct llmtie_decode_scratch {
+    float *part = nullptr;     // [pairs][splits][8][hd + 2]
+    unsigned *ctr = nullptr;   // [pairs], zero at rest
+    size_t part_floats = 0;
+    size_t ctr_words = 0;
+};
+
+// Sets the thread's error message and returns `code`.
+llmtie_status llmtie_fail(llmtie_status code, const char *fmt, ...);
+
+// Brackets one launch: counts it, and under kprof times it with events and
+// charges it to `name` (what `launched()` does in the reference's device.rs).
+struct LaunchScope {
+    llmtie_gpu *g;
+    const char *name;
+    LaunchScope(llmtie_gpu *g_, const char *name_);
+    // Checks the launch; returns LLMTIE_OK or a driver error.
+    llmtie_status done();
+};
+
+// ---- launchers (defined beside their kernels) --------------------------------
+
+// rope_cache.cu
+void launch_rope(cudaStream_t st, float *x, long long off, const float *freq_div, int t,
+                 int heads, int hd, float theta, int first);
+void launch_rope_cache_f16(cudaStream_t st, float *q, long long q_off, const float *k,
+                           long long k_off, const float *v, long long v_off,
+                           const float *freq_div, int heads, int kv_heads, int hd,
+                           float theta, int pos, uint16_t *kc, uint16_t *vc, int cap);
+void launch_cache_append(cudaStream_t st, const float *src, long long src_off, void *dst,
+                         int n, int kv_heads, int hd, int cap, int past, bool transposed,
+                         bool f16);
+void launch_cache_grow(cudaStream_t st, const void *src, void *dst, long long rows,
+                       long long len, long long src_stride, long long dst_stride, int esize);
+void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n);
+// Whisper encoder staging: qkv f32 [t][3*heads*64] -> K f16 [heads][tp][64],
+// V f16 [heads][64][tp] (tp = padded t), zero padded.
+void launch_rows_stage(cudaStream_t st, const float *qkv, uint16_t *k, uint16_t *v, int t,
+                       int tp, int heads, int hd);
+
+// decode.cu
+#define LLMTIE_DECODE_MAX_SEQ 32
+struct DecodeSeq {
+    const uint16_t *k;
+    const uint16_t *v;
+    int tk;
+    int cap;
+};
+struct DecodeParams {
+    DecodeSeq seq[LLMTIE_DECODE_MAX_SEQ];
+    const float *q;        // row r of (sequence b, kv head kh, row chunk rc) at
+    long long q_seq;       //   q + b*q_seq + kh*q_kv + (rc*8 + r)*q_row
+    long long q_kv;
+    long long q_row;
+    float *out;            // same addressing with its own strides
+    long long out_seq;
+    long long out_kv;
+    long long out_row;
+    float *part;           // partials [pair][split][8][hd + 2]
+    unsigned *ctr;         // arrival counters [pair]
+    int rows;              // query rows per kv head (all chunks together)
+    int row_chunks;        // ceil(rows / 8)
+    int kv_heads;
+    int nseq;
+    int span;              // keys per block of the grid, a multiple of 128
+    int max_splits;        // grid.x
+    int partial;           // write (o, m, l) un-normalised, row stride hd + 2
+    float q_scale;         // scale when it goes on q, else 1
+    float sl2;             // (scale on the scores, else 1) * log2(e)
+};
+// hd is 64 or 128. Returns the cudaError of the launch.
+cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd);
+// How many blocks of the decode kernel fit the device at once.
+int decode_resident_blocks(int hd, int sm_count);
+void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
+                       const float *v, float *out, long long out_off, int heads, int kv_heads,
+                       int hd, int tk, int cap, float q_scale, float s_scale);
+void launch_lse_merge(cudaStream_t st, const float *parts_buf, int parts, int rows, int hd,
+                      float *out);
+
+// prefill_mma.cu
+#define LLMTIE_PREFILL_MAX_SEQ 32
+struct PrefillSeq {
+    const void *k;         // [kv][cap][hd], f16 bits or f32
+    const void *v;         // [kv][hd][cap]
+    int row0;              // first row of this sequence in q and out
+    int tq;                // query rows
+    int past;              // positions already in the cache before them
+    int cap;
+    int tk;                // keys visible when not causal
+    int pad_;
+};
+struct PrefillParams {
+    PrefillSeq seq[LLMTIE_PREFILL_MAX_SEQ];
+    int nseq;
+    const float *q;        // row r, head h at q + r*q_stride + h*hd
+    long long q_stride;
+    void *out;             // f32 or f16, row stride out_stride
+    long long out_stride;
+    int heads, kv_heads;
+    int causal;
+    int kv_f32;            // caches are f32 (rounded to f16 on load)
+    int out_f16;
+    float q_scale;         // scale when it goes on q before rounding, else 1
+    float sl2;             // (scale on the scores, else 1) * log2(e)
+};
+cudaError_t launch_prefill_mma(cudaStream_t st, const PrefillParams &p, int hd);
+
+// rope_cache.cu: packed ragged sequences, RoPE on q (in place) and k (into
+// the f16 K caches), v transposed into the f16 V caches.
+struct VarlenSeq {
+    uint16_t *k;
+    uint16_t *v;
+    int row0, n, past, cap;
+};
+struct VarlenParams {
+    VarlenSeq seq[LLMTIE_PREFILL_MAX_SEQ];
+    int nseq;
+    int total;             // rows over all sequences
+    float *q;              // [total][heads*hd], rotated in place
+    const float *k;        // [total][kv_heads*hd]
+    const float *v;
+    const float *freq_div;
+    int heads, kv_heads, hd;
+    float theta;
+};
+void launch_varlen_rope_append(cudaStream_t st, const VarlenParams &p);
+
+// Name -> kernel table behind llmtie_kernel_resources: each kernel file
+// registers its entries from a static initialiser.
+const void *llmtie_kernel_symbol(const char *name);
+struct KernelReg {
+    KernelReg(const char *name, const void *fn);
+};
+

@@ -1,0 +1,491 @@
+// Single-query (decode) attention off the f16 KV cache, split over the keys.
+//
+// What the kernel computes is the reference's decode arithmetic
+// (crates/llmtie-cuda/src/kernels.rs:5976-6164, :6334-6505): f32 query, f16
+// keys and values, scores and probabilities kept at f32 precision, one
+// partial (o, m, l) per block of keys and a log-sum-exp merge by the last
+// block to arrive (kernels.rs:5779-5903).
+//
+// How it computes it is built for a bandwidth-bound B200: the kernel is a
+// stream of 128-bit loads that land directly in tensor-core fragment
+// registers, with no shared-memory staging and no block-wide barrier in the
+// key loop. A warp owns 32 consecutive keys at a time and up to eight query
+// rows that share them (the query heads of one GQA group). Both products run
+// on mma.m16n8k16 with f32 accumulation; f32 precision of the query and of
+// the probabilities is kept by splitting each into an f16 head and an f16
+// remainder, which ride in the two halves of the 16-row A operand, so the
+// split costs no extra instruction:
+//
+//   rows 0..7  of A : hi(x) = f16(x)          rows 8..15 : lo(x) = f16(x - hi(x))
+//   C rows r and r+8 summed in the same thread = x . k to ~2^-22.
+//
+// The cache layouts make both B operands K-major as they lie in memory: a
+// key row [hd] for q.K^T and a value row of the transposed cache [cap] for
+// P.V. The contraction index of an MMA is a dummy, so it is permuted to let
+// each thread fetch 16 contiguous bytes per fragment pair:
+//
+//   q.K^T: thread (g = lane/4, c = lane%4) loads 8 halves of key n(g) at
+//          hd offset 32 i + 8 c and feeds them to two MMAs; the query
+//          fragment is built once with the same permutation.
+//   P.V  : the same thread loads 8 consecutive keys 8 c .. 8 c + 7 of value
+//          row d = 8 j + g; score tile (mm, h) is given the keys
+//          8 (n/2) + 4 mm + 2 h + n%2 so that its accumulator registers are
+//          exactly the A fragment the value product wants.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+__device__ __forceinline__ void ldg128(uint32_t (&r)[4], const void *p)
+{
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+        : "l"(p));
+}
+
+__device__ __forceinline__ void ldg64(uint32_t &r0, uint32_t &r1, const void *p)
+{
+    asm("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "l"(p));
+}
+
+__device__ __forceinline__ float ldcg(const float *p)
+{
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float ex2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// f16 head and f16 remainder of a pair of floats, packed low half first.
+__device__ __forceinline__ void split_pair(float x0, float x1, uint32_t &hi, uint32_t &lo)
+{
+    const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
+    const __half l0 = __float2half_rn(x0 - __half2float(h0));
+    const __half l1 = __float2half_rn(x1 - __half2float(h1));
+    hi = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+    lo = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+}
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kRows = 8;   // query rows a block carries
+
+template <int HD, bool V16>
+__global__ void __launch_bounds__(kThreads, 3)
+decode_f16_kernel(const __grid_constant__ DecodeParams p)
+{
+    constexpr int KI = HD / 32;
+    constexpr int NT = HD / 8;
+    constexpr float kLn2 = 0.6931471805599453f;
+
+    __shared__ float sm_o[kWarps][kRows][HD];
+    __shared__ float sm_m[kWarps][kRows];
+    __shared__ float sm_l[kWarps][kRows];
+    __shared__ float sm_M[kRows];
+    __shared__ int sm_last;
+
+    const int split = blockIdx.x;
+    const int kh = blockIdx.y;
+    const int b = blockIdx.z / p.row_chunks;
+    const int rc = blockIdx.z % p.row_chunks;
+    const uint16_t *kbase = p.seq[b].k;
+    const uint16_t *vbase = p.seq[b].v;
+    const int tk = p.seq[b].tk;
+    const int cap = p.seq[b].cap;
+    const int nsplit = (tk + p.span - 1) / p.span;
+    if (split >= nsplit) return;
+    const int k_begin = split * p.span;
+    const int k_end = min(tk, k_begin + p.span);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int g = lane >> 2;
+    const int c = lane & 3;
+    const int rows_here = min(kRows, p.rows - rc * kRows);
+
+    // The query fragments, permuted as the key loads are, split hi / lo.
+    uint32_t qa[KI][2][4];
+    {
+        const float *qrow = p.q + (long long)b * p.q_seq + (long long)kh * p.q_kv +
+                            (long long)(rc * kRows + g) * p.q_row;
+        const bool live = g < rows_here;
+#pragma unroll
+        for (int i = 0; i < KI; i++) {
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int at = 32 * i + 8 * c + 4 * u;
+                float x[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) x[e] = live ? qrow[at + e] * p.q_scale : 0.0f;
+                split_pair(x[0], x[1], qa[i][u][0], qa[i][u][1]);
+                split_pair(x[2], x[3], qa[i][u][2], qa[i][u][3]);
+            }
+        }
+    }
+
+    float m = -CUDART_INF_F;   // running maximum, in log2 units
+    float l = 0.0f;            // this thread's share of the running sum
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    }
+
+    for (int blk = k_begin + warp * 32; blk < k_end; blk += kWarps * 32) {
+        // ---- scores: four 8-key tiles ------------------------------------
+        float t[2][2][2];
+#pragma unroll
+        for (int mm = 0; mm < 2; mm++) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int key = blk + 8 * (g >> 1) + 4 * mm + 2 * h + (g & 1);
+                const uint16_t *krow = kbase + ((size_t)kh * cap + key) * HD + 8 * c;
+                const bool live = key < k_end;
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int i = 0; i < KI; i++) {
+                    uint32_t r[4] = {0u, 0u, 0u, 0u};
+                    if (live) ldg128(r, krow + 32 * i);
+                    mma16816(acc, qa[i][0][0], qa[i][0][1], qa[i][0][2], qa[i][0][3], r[0], r[1]);
+                    mma16816(acc, qa[i][1][0], qa[i][1][1], qa[i][1][2], qa[i][1][3], r[2], r[3]);
+                }
+                // this thread's two columns are keys blk + 8c + 4mm + 2h + {0, 1}
+                const int k0 = blk + 8 * c + 4 * mm + 2 * h;
+                t[mm][h][0] = (k0 < k_end) ? (acc[0] + acc[2]) * p.sl2 : -CUDART_INF_F;
+                t[mm][h][1] = (k0 + 1 < k_end) ? (acc[1] + acc[3]) * p.sl2 : -CUDART_INF_F;
+            }
+        }
+
+        // ---- online softmax over the block --------------------------------
+        float bm = -CUDART_INF_F;
+#pragma unroll
+        for (int mm = 0; mm < 2; mm++) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                bm = fmaxf(bm, fmaxf(t[mm][h][0], t[mm][h][1]));
+            }
+        }
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+        const float m_new = fmaxf(m, bm);
+        if (__any_sync(0xffffffffu, m_new > m)) {
+            const float alpha = ex2(m - m_new);   // 0 on the first block
+            l *= alpha;
+#pragma unroll
+            for (int j = 0; j < NT; j++) {
+                o[j][0] *= alpha;
+                o[j][1] *= alpha;
+                o[j][2] *= alpha;
+                o[j][3] *= alpha;
+            }
+        }
+        m = m_new;
+        uint32_t pa[2][4];
+#pragma unroll
+        for (int mm = 0; mm < 2; mm++) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const float p0 = ex2(t[mm][h][0] - m);
+                const float p1 = ex2(t[mm][h][1] - m);
+                l += p0 + p1;
+                split_pair(p0, p1, pa[mm][2 * h], pa[mm][2 * h + 1]);
+            }
+        }
+
+        // ---- context: HD/8 tiles of 8 value rows --------------------------
+        const int g0 = blk + 8 * c;       // this thread's first key
+        const int nlive = k_end - g0;     // keys of its eight that exist
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+            const uint16_t *vrow = vbase + ((size_t)kh * HD + 8 * j + g) * cap + g0;
+            uint32_t r[4] = {0u, 0u, 0u, 0u};
+            if (V16) {
+                if (nlive > 0) ldg128(r, vrow);
+            } else {
+                if (nlive > 0) ldg64(r[0], r[1], vrow);
+                if (nlive > 4) ldg64(r[2], r[3], vrow + 4);
+            }
+            if (nlive < 8) {
+                // Capacity past the live keys may hold anything, and 0 * NaN
+                // is NaN: clear what lies beyond.
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    if (nlive <= 2 * i) {
+                        r[i] = 0u;
+                    } else if (nlive == 2 * i + 1) {
+                        r[i] &= 0x0000ffffu;
+                    }
+                }
+            }
+            mma16816(o[j], pa[0][0], pa[0][1], pa[0][2], pa[0][3], r[0], r[1]);
+            mma16816(o[j], pa[1][0], pa[1][1], pa[1][2], pa[1][3], r[2], r[3]);
+        }
+    }
+
+    // ---- the block's four warps merge through shared memory -----------------
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (c == 0) {
+        sm_m[warp][g] = m;
+        sm_l[warp][g] = l;
+    }
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        sm_o[warp][g][8 * j + 2 * c] = o[j][0] + o[j][2];
+        sm_o[warp][g][8 * j + 2 * c + 1] = o[j][1] + o[j][3];
+    }
+    __syncthreads();
+
+    const int pair = (b * p.row_chunks + rc) * p.kv_heads + kh;
+    float *part = p.part + ((size_t)pair * p.max_splits + split) * kRows * (HD + 2);
+    float *orow0 = p.out + (long long)b * p.out_seq + (long long)kh * p.out_kv +
+                   (long long)(rc * kRows) * p.out_row;
+    for (int idx = tid; idx < rows_here * HD; idx += kThreads) {
+        const int row = idx / HD, d = idx % HD;
+        float M = sm_m[0][row];
+#pragma unroll
+        for (int w = 1; w < kWarps; w++) M = fmaxf(M, sm_m[w][row]);
+        float O = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) {
+            const float mw = sm_m[w][row];
+            const float f = (mw == -CUDART_INF_F) ? 0.0f : ex2(mw - M);
+            O += f * sm_o[w][row][d];
+            L += f * sm_l[w][row];
+        }
+        if (nsplit == 1) {
+            float *orow = orow0 + (long long)row * p.out_row;
+            if (p.partial) {
+                orow[d] = O;
+                if (d == 0) {
+                    orow[HD] = M * kLn2;
+                    orow[HD + 1] = L;
+                }
+            } else {
+                orow[d] = L > 0.0f ? O / L : 0.0f;
+            }
+        } else {
+            float *pr = part + row * (HD + 2);
+            pr[d] = O;
+            if (d == 0) {
+                pr[HD] = M;
+                pr[HD + 1] = L;
+            }
+        }
+    }
+    if (nsplit == 1) return;
+
+    // ---- the last block of this head to arrive merges every partial ---------
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(p.ctr + pair, 1u);
+        sm_last = (prev == (unsigned)(nsplit - 1));
+    }
+    __syncthreads();
+    if (!sm_last) return;
+    __threadfence();
+    const float *all = p.part + (size_t)pair * p.max_splits * kRows * (HD + 2);
+    if (tid < rows_here) {
+        float M = -CUDART_INF_F;
+        for (int i = 0; i < nsplit; i++) {
+            M = fmaxf(M, ldcg(all + ((size_t)i * kRows + tid) * (HD + 2) + HD));
+        }
+        sm_M[tid] = M;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows_here * HD; idx += kThreads) {
+        const int row = idx / HD, d = idx % HD;
+        const float M = sm_M[row];
+        float O = 0.0f, L = 0.0f;
+        for (int i = 0; i < nsplit; i++) {
+            const float *pr = all + ((size_t)i * kRows + row) * (HD + 2);
+            const float mi = ldcg(pr + HD);
+            const float f = (mi == -CUDART_INF_F) ? 0.0f : ex2(mi - M);
+            O += f * ldcg(pr + d);
+            L += f * ldcg(pr + HD + 1);
+        }
+        float *orow = orow0 + (long long)row * p.out_row;
+        if (p.partial) {
+            orow[d] = O;
+            if (d == 0) {
+                orow[HD] = M * kLn2;
+                orow[HD + 1] = L;
+            }
+        } else {
+            orow[d] = L > 0.0f ? O / L : 0.0f;
+        }
+    }
+    if (tid == 0) p.ctr[pair] = 0u;   // at rest again for the next call
+}
+
+// Decode off an f32 cache (the Whisper decoder's self-attention: 64-wide
+// heads, at most a few hundred keys). One block a query head; plain f32 FMA
+// as the reference's `attn_decode_f64` entry keeps it.
+template <int HD>
+__global__ void __launch_bounds__(256)
+decode_f32_kernel(const float *__restrict__ q, long long q_off, const float *__restrict__ k,
+                  const float *__restrict__ v, float *__restrict__ out, long long out_off,
+                  int group, int tk, int cap, float q_scale, float s_scale)
+{
+    constexpr int CH = 256;
+    __shared__ float sq[HD];
+    __shared__ float sp[CH];
+    __shared__ float red[8];
+    __shared__ float so[4][HD];
+    const int head = blockIdx.x;
+    const int kh = head / group;
+    const int tid = threadIdx.x;
+    if (tid < HD) sq[tid] = q[q_off + (long long)head * HD + tid] * q_scale;
+    __syncthreads();
+    const int d = tid % HD;      // output channel this thread accumulates
+    const int part = tid / HD;   // over keys part, part + 4, ... of a chunk
+    float m = -CUDART_INF_F, l = 0.0f, acc = 0.0f;
+    for (int c0 = 0; c0 < tk; c0 += CH) {
+        const int key = c0 + tid;
+        float s = -CUDART_INF_F;
+        if (key < tk) {
+            const float *kr = k + ((size_t)kh * cap + key) * HD;
+            float dot = 0.0f;
+#pragma unroll 8
+            for (int e = 0; e < HD; e++) dot += sq[e] * kr[e];
+            s = dot * s_scale;
+        }
+        // block maximum
+        float bm = s;
+        for (int w = 16; w > 0; w >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, w));
+        if ((tid & 31) == 0) red[tid >> 5] = bm;
+        __syncthreads();
+        bm = red[0];
+        for (int w = 1; w < 8; w++) bm = fmaxf(bm, red[w]);
+        const float m_new = fmaxf(m, bm);
+        const float alpha = (m == -CUDART_INF_F) ? 0.0f : __expf(m - m_new);
+        const float pv = (key < tk) ? __expf(s - m_new) : 0.0f;
+        sp[tid] = pv;
+        __syncthreads();
+        float bs = pv;
+        for (int w = 16; w > 0; w >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, w);
+        if ((tid & 31) == 0) red[tid >> 5] = bs;
+        __syncthreads();
+        bs = 0.0f;
+        for (int w = 0; w < 8; w++) bs += red[w];
+        l = l * alpha + bs;
+        m = m_new;
+        acc *= alpha;
+        const int n = min(CH, tk - c0);
+        const float *vr = v + ((size_t)kh * HD + d) * cap + c0;
+        for (int e = part; e < n; e += 256 / HD) acc += sp[e] * vr[e];
+        __syncthreads();
+    }
+    so[part][d] = acc;
+    __syncthreads();
+    if (tid < HD) {
+        float a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 256 / HD; w++) a += so[w][tid];
+        out[out_off + (long long)head * HD + tid] = l > 0.0f ? a / l : 0.0f;
+    }
+}
+
+// out[row] = sum_i o_i exp(m_i - M) / sum_i l_i exp(m_i - M) over `parts`
+// triples laid out [parts][rows][hd + 2].
+__global__ void lse_merge_kernel(const float *__restrict__ buf, int parts, int rows, int hd,
+                                 float *__restrict__ out)
+{
+    const int row = blockIdx.x;
+    const int stride = hd + 2;
+    float M = -CUDART_INF_F;
+    for (int i = 0; i < parts; i++) {
+        M = fmaxf(M, buf[((size_t)i * rows + row) * stride + hd]);
+    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float O = 0.0f, L = 0.0f;
+        for (int i = 0; i < parts; i++) {
+            const float *pr = buf + ((size_t)i * rows + row) * stride;
+            const float mi = pr[hd];
+            const float f = (mi == -CUDART_INF_F) ? 0.0f : __expf(mi - M);
+            O += f * pr[d];
+            L += f * pr[hd + 1];
+        }
+        out[(size_t)row * hd + d] = L > 0.0f ? O / L : 0.0f;
+    }
+}
+
+const KernelReg reg_d128("attn_decode_h128", (const void *)decode_f16_kernel<128, true>);
+const KernelReg reg_d128u("attn_decode_h128_unaligned", (const void *)decode_f16_kernel<128, false>);
+const KernelReg reg_d64("attn_decode_h64", (const void *)decode_f16_kernel<64, true>);
+const KernelReg reg_d64u("attn_decode_h64_unaligned", (const void *)decode_f16_kernel<64, false>);
+const KernelReg reg_df32("attn_decode_f64", (const void *)decode_f32_kernel<64>);
+const KernelReg reg_merge("lse_merge", (const void *)lse_merge_kernel);
+
+}  // namespace
+
+cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd)
+{
+    const dim3 grid(p.max_splits, p.kv_heads, p.nseq * p.row_chunks);
+    bool v16 = true;
+    for (int b = 0; b < p.nseq; b++) {
+        if (p.seq[b].cap % 8 != 0 || ((uintptr_t)p.seq[b].v & 15u) != 0) v16 = false;
+    }
+    if (hd == 128) {
+        if (v16) {
+            decode_f16_kernel<128, true><<<grid, kThreads, 0, st>>>(p);
+        } else {
+            decode_f16_kernel<128, false><<<grid, kThreads, 0, st>>>(p);
+        }
+    } else {
+        if (v16) {
+            decode_f16_kernel<64, true><<<grid, kThreads, 0, st>>>(p);
+        } else {
+            decode_f16_kernel<64, false><<<grid, kThreads, 0, st>>>(p);
+        }
+    }
+    return cudaGetLastError();
+}
+
+int decode_resident_blocks(int hd, int sm_count)
+{
+    int per_sm = 0;
+    cudaError_t e;
+    if (hd == 128) {
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_f16_kernel<128, true>,
+                                                          kThreads, 0);
+    } else {
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_f16_kernel<64, true>,
+                                                          kThreads, 0);
+    }
+    if (e != cudaSuccess || per_sm < 1) per_sm = 1;
+    return per_sm * sm_count;
+}
+
+void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
+                       const float *v, float *out, long long out_off, int heads, int kv_heads,
+                       int hd, int tk, int cap, float q_scale, float s_scale)
+{
+    (void)hd;   // 64: the only width the f32 cache is decoded at
+    decode_f32_kernel<64><<<heads, 256, 0, st>>>(q, q_off, k, v, out, out_off, heads / kv_heads,
+                                                tk, cap, q_scale, s_scale);
+}
+
+void launch_lse_merge(cudaStream_t st, const float *parts_buf, int parts, int rows, int hd,
+                      float *out)
+{
+    lse_merge_kernel<<<rows, hd, 0, st>>>(parts_buf, parts, rows, hd, out);
+}

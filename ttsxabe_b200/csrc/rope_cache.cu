@@ -1,0 +1,360 @@
+// RoPE and the KV-cache movers: the element-wise kernels either side of
+// attention. Arithmetic follows the reference's kernels exactly where a bit
+// could differ: accurate powf / sincosf in f32 for the rotation
+// (crates/llmtie-cuda/src/kernels.rs:4915-4959) and round-to-nearest-even
+// into the f16 caches (kernels.rs:5287-5317).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint16_t f16_bits(float x)
+{
+    return __half_as_ushort(__float2half_rn(x));
+}
+
+// The rotation of one pair, with the roundings spelled out so that every
+// kernel that rotates produces the same bits whatever the compiler would have
+// contracted: the fused decode-step and ragged-prefill kernels are held to
+// bit equality with rope followed by an append.
+__device__ __forceinline__ void rotate(float a, float b, float cs, float sn, float &lo, float &hi)
+{
+    lo = __fmaf_rn(a, cs, -__fmul_rn(b, sn));
+    hi = __fmaf_rn(b, cs, __fmul_rn(a, sn));
+}
+
+// The angle of pair j at position pos: f32 throughout, accurate powf.
+__device__ __forceinline__ void pair_sincos(float theta, int j, int hd, const float *freq_div,
+                                            int pos, float &sn, float &cs)
+{
+    float inv = powf(theta, __fdiv_rn(__fmul_rn(-2.0f, (float)j), (float)hd));
+    if (freq_div) inv = __fdiv_rn(inv, freq_div[j]);
+    sincosf(__fmul_rn((float)pos, inv), &sn, &cs);
+}
+
+// One thread per rotating pair (j, j + hd/2).
+__global__ void rope_kernel(float *__restrict__ x, long long off,
+                            const float *__restrict__ freq_div, int t, int heads, int hd,
+                            float theta, int first)
+{
+    const int half = hd >> 1;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)t * heads * half) return;
+    const int j = (int)(i % half);
+    const int h = (int)((i / half) % heads);
+    const int p = (int)(i / ((long long)half * heads));
+    float sn, cs;
+    pair_sincos(theta, j, hd, freq_div, first + p, sn, cs);
+    const size_t base = (size_t)off + ((size_t)p * heads + h) * hd + j;
+    float lo, hi;
+    rotate(x[base], x[base + half], cs, sn, lo, hi);
+    x[base] = lo;
+    x[base + half] = hi;
+}
+
+// One decoded position: q rotated in place, rotated k and plain v into the
+// f16 caches at `pos`. q, k and v may alias one allocation, so no restrict.
+__global__ void rope_cache_f16_kernel(float *q, long long q_off, const float *k,
+                                      long long k_off, const float *v, long long v_off,
+                                      const float *__restrict__ freq_div, int heads,
+                                      int kv_heads, int hd, float theta, int pos,
+                                      uint16_t *__restrict__ kc, uint16_t *__restrict__ vc,
+                                      int cap)
+{
+    const int half = hd >> 1;
+    const int nq = heads * half;
+    const int nk = kv_heads * half;
+    const int nv = kv_heads * hd;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < nq + nk) {
+        const bool is_q = i < nq;
+        const int e = is_q ? i : i - nq;
+        const int j = e % half;
+        const int h = e / half;
+        float sn, cs, lo, hi;
+        pair_sincos(theta, j, hd, freq_div, pos, sn, cs);
+        if (is_q) {
+            const size_t base = (size_t)q_off + (size_t)h * hd + j;
+            rotate(q[base], q[base + half], cs, sn, lo, hi);
+            q[base] = lo;
+            q[base + half] = hi;
+        } else {
+            const size_t base = (size_t)k_off + (size_t)h * hd + j;
+            rotate(k[base], k[base + half], cs, sn, lo, hi);
+            uint16_t *d = kc + ((size_t)h * cap + pos) * hd;
+            d[j] = f16_bits(lo);
+            d[j + half] = f16_bits(hi);
+        }
+    } else if (i < nq + nk + nv) {
+        const int e = i - nq - nk;
+        const int h = e / hd;
+        const int j = e % hd;
+        vc[((size_t)h * hd + j) * cap + pos] = f16_bits(v[(size_t)v_off + e]);
+    }
+}
+
+// src [n][kv_heads*hd] -> K layout [kv][cap][hd]. Consecutive threads take
+// consecutive source elements, which are consecutive destination elements
+// within a head row, so both sides coalesce.
+template <typename T>
+__global__ void cache_append_kernel(const float *__restrict__ src, long long src_off,
+                                    T *__restrict__ dst, int n, int kv_heads, int hd, int cap,
+                                    int past)
+{
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int d = kv_heads * hd;
+    if (i >= (size_t)n * d) return;
+    const int ti = (int)(i / d);
+    const int h = (int)((i % d) / hd);
+    const int j = (int)(i % hd);
+    const float x = src[(size_t)src_off + i];
+    T *o = dst + ((size_t)h * cap + past + ti) * hd + j;
+    if constexpr (sizeof(T) == 2) {
+        *o = f16_bits(x);
+    } else {
+        *o = x;
+    }
+}
+
+// src [n][kv_heads*hd] -> V layout [kv][hd][cap]: a transpose. A block stages
+// 32 positions x 32 channels through shared memory so the reads run along the
+// channels and the writes along the positions.
+template <typename T>
+__global__ void cache_append_t_kernel(const float *__restrict__ src, long long src_off,
+                                      T *__restrict__ dst, int n, int kv_heads, int hd,
+                                      int cap, int past)
+{
+    __shared__ float tile[32][33];
+    const int d = kv_heads * hd;
+    const int c0 = blockIdx.x * 32;   // channel (h*hd + j)
+    const int t0 = blockIdx.y * 32;   // position within the step
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int ti = t0 + r, c = c0 + threadIdx.x;
+        tile[r][threadIdx.x] =
+            (ti < n && c < d) ? src[(size_t)src_off + (size_t)ti * d + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int c = c0 + r, ti = t0 + threadIdx.x;
+        if (c < d && ti < n) {
+            T *o = dst + (size_t)c * cap + past + ti;   // c = h*hd + j
+            const float x = tile[threadIdx.x][r];
+            if constexpr (sizeof(T) == 2) {
+                *o = f16_bits(x);
+            } else {
+                *o = x;
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void cache_grow_kernel(const T *__restrict__ src, T *__restrict__ dst,
+                                  long long rows, long long len, long long src_stride,
+                                  long long dst_stride)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * len) return;
+    const long long r = i / len;
+    const long long j = i % len;
+    dst[r * dst_stride + j] = src[r * src_stride + j];
+}
+
+__global__ void round_f16_kernel(const float *__restrict__ src, uint16_t *__restrict__ dst,
+                                 size_t n)
+{
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = f16_bits(src[i]);
+}
+
+// Whisper encoder staging. qkv is [t][3*d] f32 with d = heads*hd: keys are
+// the column block [d, 2d), values [2d, 3d). Keys go to [heads][tp][hd] f16,
+// values transposed to [heads][hd][tp] f16; positions t..tp are zero.
+__global__ void rows_stage_kernel(const float *__restrict__ qkv, uint16_t *__restrict__ k,
+                                  uint16_t *__restrict__ v, int t, int tp, int heads, int hd)
+{
+    __shared__ float tile[32][33];
+    const int d = heads * hd;
+    const int c0 = blockIdx.x * 32;   // channel within d
+    const int t0 = blockIdx.y * 32;
+    const size_t row = (size_t)3 * d;
+    // keys: straight copy with a cast
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int ti = t0 + r, c = c0 + threadIdx.x;
+        if (ti < tp && c < d) {
+            const float x = ti < t ? qkv[(size_t)ti * row + d + c] : 0.0f;
+            const int h = c / hd, j = c % hd;
+            k[((size_t)h * tp + ti) * hd + j] = f16_bits(x);
+        }
+    }
+    // values: transpose through the tile
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int ti = t0 + r, c = c0 + threadIdx.x;
+        tile[r][threadIdx.x] = (ti < t && c < d) ? qkv[(size_t)ti * row + 2 * d + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int c = c0 + r, ti = t0 + threadIdx.x;
+        if (c < d && ti < tp) {
+            v[(size_t)c * tp + ti] = f16_bits(tile[threadIdx.x][r]);
+        }
+    }
+}
+
+
+// Packed ragged sequences: which sequence a packed row belongs to.
+__device__ __forceinline__ int varlen_seq_of(const VarlenParams &p, int row)
+{
+    int b = 0;
+    while (b + 1 < p.nseq && row >= p.seq[b + 1].row0) b++;
+    return b;
+}
+
+// RoPE on q (in place) and on k (into the f16 K cache at past + position):
+// one thread per rotating pair. The arithmetic is `rope_kernel`'s followed by
+// the append's rounding, so the result equals the two-launch chain bit for
+// bit.
+__global__ void varlen_rope_kernel(const __grid_constant__ VarlenParams p)
+{
+    const int half = p.hd >> 1;
+    const int per_row = (p.heads + p.kv_heads) * half;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)p.total * per_row) return;
+    const int row = (int)(i / per_row);
+    const int e = (int)(i % per_row);
+    const int b = varlen_seq_of(p, row);
+    const VarlenSeq &sq = p.seq[b];
+    const int ti = row - sq.row0;
+    const int j = e % half;
+    const int hh = e / half;
+    float sn, cs, lo, hi;
+    pair_sincos(p.theta, j, p.hd, p.freq_div, sq.past + ti, sn, cs);
+    if (hh < p.heads) {
+        float *x = p.q + ((size_t)row * p.heads + hh) * p.hd + j;
+        rotate(x[0], x[half], cs, sn, lo, hi);
+        x[0] = lo;
+        x[half] = hi;
+    } else {
+        const int h = hh - p.heads;
+        const float *x = p.k + ((size_t)row * p.kv_heads + h) * p.hd + j;
+        rotate(x[0], x[half], cs, sn, lo, hi);
+        uint16_t *d = sq.k + ((size_t)h * sq.cap + sq.past + ti) * p.hd;
+        d[j] = f16_bits(lo);
+        d[j + half] = f16_bits(hi);
+    }
+}
+
+// v [n][kv*hd] of each sequence -> its transposed f16 V cache, through a
+// 32 x 32 shared tile. grid.z is the sequence.
+__global__ void varlen_append_v_kernel(const __grid_constant__ VarlenParams p)
+{
+    __shared__ float tile[32][33];
+    const VarlenSeq &sq = p.seq[blockIdx.z];
+    const int d = p.kv_heads * p.hd;
+    const int c0 = blockIdx.x * 32;
+    const int t0 = blockIdx.y * 32;
+    if (t0 >= sq.n) return;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int ti = t0 + r, c = c0 + threadIdx.x;
+        tile[r][threadIdx.x] =
+            (ti < sq.n && c < d) ? p.v[(size_t)(sq.row0 + ti) * d + c] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int c = c0 + r, ti = t0 + threadIdx.x;
+        if (c < d && ti < sq.n) {
+            sq.v[(size_t)c * sq.cap + sq.past + ti] = f16_bits(tile[threadIdx.x][r]);
+        }
+    }
+}
+
+inline unsigned flat_blocks(size_t n, int threads)
+{
+    return (unsigned)((n + threads - 1) / threads);
+}
+
+}  // namespace
+
+void launch_rope(cudaStream_t st, float *x, long long off, const float *freq_div, int t,
+                 int heads, int hd, float theta, int first)
+{
+    const size_t n = (size_t)t * heads * (hd / 2);
+    if (n == 0) return;
+    rope_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(x, off, freq_div, t, heads, hd, theta,
+                                                    first);
+}
+
+void launch_rope_cache_f16(cudaStream_t st, float *q, long long q_off, const float *k,
+                           long long k_off, const float *v, long long v_off,
+                           const float *freq_div, int heads, int kv_heads, int hd,
+                           float theta, int pos, uint16_t *kc, uint16_t *vc, int cap)
+{
+    const size_t n = (size_t)heads * hd / 2 + (size_t)kv_heads * hd / 2 + (size_t)kv_heads * hd;
+    rope_cache_f16_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(
+        q, q_off, k, k_off, v, v_off, freq_div, heads, kv_heads, hd, theta, pos, kc, vc, cap);
+}
+
+void launch_cache_append(cudaStream_t st, const float *src, long long src_off, void *dst,
+                         int n, int kv_heads, int hd, int cap, int past, bool transposed,
+                         bool f16)
+{
+    const size_t total = (size_t)n * kv_heads * hd;
+    if (total == 0) return;
+    if (!transposed) {
+        if (f16) {
+            cache_append_kernel<uint16_t><<<flat_blocks(total, 256), 256, 0, st>>>(
+                src, src_off, (uint16_t *)dst, n, kv_heads, hd, cap, past);
+        } else {
+            cache_append_kernel<float><<<flat_blocks(total, 256), 256, 0, st>>>(
+                src, src_off, (float *)dst, n, kv_heads, hd, cap, past);
+        }
+    } else {
+        const dim3 grid((kv_heads * hd + 31) / 32, (n + 31) / 32);
+        const dim3 block(32, 8);
+        if (f16) {
+            cache_append_t_kernel<uint16_t><<<grid, block, 0, st>>>(
+                src, src_off, (uint16_t *)dst, n, kv_heads, hd, cap, past);
+        } else {
+            cache_append_t_kernel<float><<<grid, block, 0, st>>>(
+                src, src_off, (float *)dst, n, kv_heads, hd, cap, past);
+        }
+    }
+}
+
+void launch_cache_grow(cudaStream_t st, const void *src, void *dst, long long rows,
+                       long long len, long long src_stride, long long dst_stride, int esize)
+{
+    const size_t total = (size_t)rows * len;
+    if (total == 0) return;
+    if (esize == 2) {
+        cache_grow_kernel<uint16_t><<<flat_blocks(total, 256), 256, 0, st>>>(
+            (const uint16_t *)src, (uint16_t *)dst, rows, len, src_stride, dst_stride);
+    } else {
+        cache_grow_kernel<float><<<flat_blocks(total, 256), 256, 0, st>>>(
+            (const float *)src, (float *)dst, rows, len, src_stride, dst_stride);
+    }
+}
+
+void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n)
+{
+    if (n == 0) return;
+    round_f16_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(src, dst, n);
+}
+
+void launch_rows_stage(cudaStream_t st, const float *qkv, uint16_t *k, uint16_t *v, int t,
+                       int tp, int heads, int hd)
+{
+    const dim3 grid((heads * hd + 31) / 32, (tp + 31) / 32);
+    const dim3 block(32, 8);
+    rows_stage_kernel<<<grid, block, 0, st>>>(qkv, k, v, t, tp, heads, hd);
+}
+
+void launch_varlen_rope_append(cudaStream_t st, const VarlenParams &p)
+{
+    if (p.total == 0) return;
+    const size_t n = (size_t)p.total * (p.heads + p.kv_heads) * (p.hd / 2);
+    varlen_rope_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(p);
+    int max_n = 0;
+    for (int b = 0; b < p.nseq; b++) max_n = p.seq[b].n > max_n ? p.seq[b].n : max_n;
+    const dim3 grid((p.kv_heads * p.hd + 31) / 32, (max_n + 31) / 32, p.nseq);
+    varlen_append_v_kernel<<<grid, dim3(32, 8), 0, st>>>(p);
+}

@@ -1,0 +1,394 @@
+"""Host-side mirror of `llmtie_cuda::Gpu` for the attention path.
+
+Same method names, argument order and refusals as the reference's device
+handle (crates/llmtie-cuda/src/device.rs), over the C ABI in
+include/llmtie_b200.h. Device buffers are torch CUDA tensors standing in for
+`CudaSlice<f32>` / `CudaSlice<u16>`: torch owns the memory, the library is
+given raw pointers and element counts. f16 buffers are `torch.float16`
+tensors (the reference carries the same bits as u16).
+
+All work runs on the handle's own non-blocking stream; torch allocations made
+through this class are made under that stream, so stream-ordered reuse holds.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+# ---- errors: one class per CudaError variant (crates/llmtie-cuda/src/error.rs) ----
+
+class CudaError(RuntimeError):
+    code = -1
+
+
+class NoDevice(CudaError):
+    code = 1
+
+
+class DriverError(CudaError):
+    code = 2
+
+
+class SliceOverrun(CudaError):
+    code = 3
+
+
+class CacheOverrun(CudaError):
+    code = 4
+
+
+class OddCacheCapacity(CudaError):
+    code = 5
+
+
+class OddHeadDim(CudaError):
+    code = 6
+
+
+class UnsupportedAttention(CudaError):
+    code = 7
+
+
+class RaggedBlock(CudaError):
+    code = 8
+
+
+class Misaligned(CudaError):
+    code = 9
+
+
+class MissingKernel(CudaError):
+    code = 10
+
+
+class DeviceTimeout(CudaError):
+    code = 11
+
+
+class InvalidArgument(CudaError):
+    code = 12
+
+
+_ERRORS = {
+    c.code: c
+    for c in (NoDevice, DriverError, SliceOverrun, CacheOverrun, OddCacheCapacity, OddHeadDim,
+              UnsupportedAttention, RaggedBlock, Misaligned, MissingKernel, DeviceTimeout,
+              InvalidArgument)
+}
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        msg = _lib.load().llmtie_last_error().decode("utf-8", "replace")
+        raise _ERRORS.get(status, CudaError)(msg)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class DecodeScratch:
+    """`DecodeScratch` (device.rs:166-233): the split-KV workspace a caller
+    keeps per cache. Empty until the first call allocates."""
+
+    def __init__(self) -> None:
+        self._gpu: Optional["Gpu"] = None
+        self._h = C.c_void_p()
+
+    def _bind(self, gpu: "Gpu") -> C.c_void_p:
+        if self._gpu is None:
+            _check(gpu._lib.llmtie_decode_scratch_new(gpu._h, C.byref(self._h)))
+            self._gpu = gpu
+        elif self._gpu is not gpu:
+            raise InvalidArgument("a DecodeScratch belongs to the Gpu that first used it")
+        return self._h
+
+    def close(self) -> None:
+        if self._gpu is not None and self._h and self._gpu._h:
+            self._gpu._lib.llmtie_decode_scratch_free(self._gpu._h, self._h)
+        self._h = C.c_void_p()
+        self._gpu = None
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Gpu:
+    """One device handle with its own stream (device.rs:737-842)."""
+
+    def __init__(self, ordinal: int = 0) -> None:
+        self._lib = _lib.load()
+        self._h = C.c_void_p()
+        _check(self._lib.llmtie_open(ordinal, C.byref(self._h)))
+        self.ordinal = ordinal
+        self.device = torch.device("cuda", ordinal)
+        self.stream = torch.cuda.ExternalStream(self._lib.llmtie_stream(self._h),
+                                                device=self.device)
+
+    @classmethod
+    def open(cls, ordinal: int = 0) -> "Gpu":
+        return cls(ordinal)
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.llmtie_close(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- memory -------------------------------------------------------------
+
+    def _empty(self, n: int, dtype: torch.dtype) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            return torch.empty(int(n), dtype=dtype, device=self.device)
+
+    def uninit(self, n: int) -> torch.Tensor:
+        return self._empty(n, torch.float32)
+
+    def zeros(self, n: int) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            return torch.zeros(int(n), dtype=torch.float32, device=self.device)
+
+    def zeros_f16(self, n: int) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            return torch.zeros(int(n), dtype=torch.float16, device=self.device)
+
+    def upload(self, x) -> torch.Tensor:
+        a = np.ascontiguousarray(np.asarray(x, dtype=np.float32)).reshape(-1)
+        t = self._empty(a.size, torch.float32)
+        if a.size:
+            _check(self._lib.llmtie_upload(self._h, t.data_ptr(), a.ctypes.data, a.nbytes))
+            self.synchronize()   # `a` may be a temporary
+        return t
+
+    def upload_u16(self, x) -> torch.Tensor:
+        a = np.ascontiguousarray(np.asarray(x, dtype=np.uint16)).reshape(-1)
+        t = self._empty(a.size, torch.float16)
+        if a.size:
+            _check(self._lib.llmtie_upload(self._h, t.data_ptr(), a.ctypes.data, a.nbytes))
+            self.synchronize()
+        return t
+
+    def upload_f16(self, x) -> torch.Tensor:
+        """f32 values rounded to f16 on the device (device.rs:1422-1431)."""
+        src = self.upload(x)
+        dst = self._empty(src.numel(), torch.float16)
+        _check(self._lib.llmtie_round_f16(self._h, src.data_ptr(), dst.data_ptr(), src.numel()))
+        return dst
+
+    def download(self, t: torch.Tensor) -> np.ndarray:
+        out = np.empty(t.numel(), dtype=np.float32)
+        assert t.dtype == torch.float32
+        if out.size:
+            _check(self._lib.llmtie_download(self._h, out.ctypes.data, t.data_ptr(), out.nbytes))
+        return out
+
+    def download_u16(self, t: torch.Tensor) -> np.ndarray:
+        out = np.empty(t.numel(), dtype=np.uint16)
+        assert t.element_size() == 2
+        if out.size:
+            _check(self._lib.llmtie_download(self._h, out.ctypes.data, t.data_ptr(), out.nbytes))
+        return out
+
+    def synchronize(self) -> None:
+        _check(self._lib.llmtie_synchronize(self._h))
+
+    # ---- RoPE ----------------------------------------------------------------
+
+    def rope(self, x, off, t, heads, head_dim, theta, first) -> None:
+        self.rope_scaled(x, off, None, t, heads, head_dim, theta, first)
+
+    def rope_scaled(self, x, off, freq_div, t, heads, head_dim, theta, first) -> None:
+        _check(self._lib.llmtie_rope_scaled(self._h, x.data_ptr(), x.numel(), off,
+                                            _ptr(freq_div), t, heads, head_dim, theta, first))
+
+    def rope_cache_f16(self, proj: Sequence[torch.Tensor], q, k, v, freq_div, heads, kv_heads,
+                       head_dim, theta, pos, kc, vc, cap) -> None:
+        """q, k, v are (buffer index, element offset) into `proj`."""
+        def span(which):
+            bi, off = which
+            if bi >= len(proj):
+                return None, 0, off
+            return proj[bi].data_ptr(), proj[bi].numel(), off
+        qp, ql, qo = span(q)
+        kp, kl, ko = span(k)
+        vp_, vl, vo = span(v)
+        _check(self._lib.llmtie_rope_cache_f16(
+            self._h, qp, ql, qo, kp, kl, ko, vp_, vl, vo, _ptr(freq_div), heads, kv_heads,
+            head_dim, theta, pos, kc.data_ptr(), kc.numel(), vc.data_ptr(), vc.numel(), cap))
+
+    # ---- KV cache ---------------------------------------------------------------
+
+    def cache_append_f16(self, src, src_off, dst, n, kv_heads, head_dim, cap, past,
+                         transposed) -> None:
+        _check(self._lib.llmtie_cache_append_f16(
+            self._h, src.data_ptr(), src.numel(), src_off, dst.data_ptr(), dst.numel(), n,
+            kv_heads, head_dim, cap, past, int(bool(transposed))))
+
+    def cache_append(self, src, src_off, dst, n, kv_heads, head_dim, cap, past,
+                     transposed) -> None:
+        _check(self._lib.llmtie_cache_append(
+            self._h, src.data_ptr(), src.numel(), src_off, dst.data_ptr(), dst.numel(), n,
+            kv_heads, head_dim, cap, past, int(bool(transposed))))
+
+    def cache_grow_f16(self, src, dst, kv_heads, head_dim, old_cap, new_cap, live,
+                       transposed) -> None:
+        _check(self._lib.llmtie_cache_grow_f16(
+            self._h, src.data_ptr(), src.numel(), dst.data_ptr(), dst.numel(), kv_heads,
+            head_dim, old_cap, new_cap, live, int(bool(transposed))))
+
+    def cache_grow(self, src, dst, kv_heads, head_dim, old_cap, new_cap, live,
+                   transposed) -> None:
+        _check(self._lib.llmtie_cache_grow(
+            self._h, src.data_ptr(), src.numel(), dst.data_ptr(), dst.numel(), kv_heads,
+            head_dim, old_cap, new_cap, live, int(bool(transposed))))
+
+    # ---- prefill / encoder --------------------------------------------------------
+
+    def supports_flash(self, head_dim, heads, kv_heads) -> bool:
+        return bool(self._lib.llmtie_supports_flash(head_dim, heads, kv_heads))
+
+    def flash_attn(self, q, k, v, tq, past, heads, kv_heads, head_dim, cap, scale,
+                   causal) -> torch.Tensor:
+        out = self.uninit(tq * heads * head_dim)
+        _check(self._lib.llmtie_flash_attn(
+            self._h, q.data_ptr(), q.numel(), k.data_ptr(), k.numel(), v.data_ptr(), v.numel(),
+            out.data_ptr(), out.numel(), tq, past, heads, kv_heads, head_dim, cap, scale,
+            int(bool(causal))))
+        return out
+
+    def flash_attn_f16(self, q, k, v, tq, past, heads, kv_heads, head_dim, cap, scale,
+                       causal) -> torch.Tensor:
+        out = self.uninit(tq * heads * head_dim)
+        _check(self._lib.llmtie_flash_attn_f16(
+            self._h, q.data_ptr(), q.numel(), k.data_ptr(), k.numel(), v.data_ptr(), v.numel(),
+            out.data_ptr(), out.numel(), tq, past, heads, kv_heads, head_dim, cap, scale,
+            int(bool(causal))))
+        return out
+
+    def flash_attn_rows(self, qkv, t, heads, head_dim, scale) -> torch.Tensor:
+        out = self._empty(t * heads * head_dim, torch.float16)
+        _check(self._lib.llmtie_flash_attn_rows(
+            self._h, qkv.data_ptr(), qkv.numel(), out.data_ptr(), out.numel(), t, heads,
+            head_dim, scale, None, 0))
+        return out
+
+    # ---- decode ----------------------------------------------------------------------
+
+    def attn_decode_f16(self, q, k, v, heads, kv_heads, head_dim, tk, cap, scale, scale_q,
+                        scratch: DecodeScratch) -> torch.Tensor:
+        out = self.uninit(heads * head_dim)
+        self.attn_decode_f16_row(q, 0, k, v, heads, kv_heads, head_dim, tk, cap, scale, scale_q,
+                                 scratch, out, 0)
+        return out
+
+    def attn_decode_f16_row(self, q, q_off, k, v, heads, kv_heads, head_dim, tk, cap, scale,
+                            scale_q, scratch: DecodeScratch, out, row) -> None:
+        """`attn_decode_f16_q_row` without the int8 twin (device.rs:6001-6038)."""
+        _check(self._lib.llmtie_attn_decode_f16(
+            self._h, q.data_ptr(), q.numel(), q_off, k.data_ptr(), k.numel(), v.data_ptr(),
+            v.numel(), heads, kv_heads, head_dim, tk, cap, scale, int(bool(scale_q)),
+            scratch._bind(self), out.data_ptr(), out.numel(), row * heads * head_dim))
+
+    def attn_decode(self, q, k, v, heads, kv_heads, head_dim, tk, cap, scale, scale_q,
+                    scratch: DecodeScratch) -> torch.Tensor:
+        out = self.uninit(heads * head_dim)
+        _check(self._lib.llmtie_attn_decode(
+            self._h, q.data_ptr(), q.numel(), 0, k.data_ptr(), k.numel(), v.data_ptr(),
+            v.numel(), heads, kv_heads, head_dim, tk, cap, scale, int(bool(scale_q)),
+            scratch._bind(self), out.data_ptr(), out.numel(), 0))
+        return out
+
+    # ---- batched / sharded supersets -------------------------------------------------------
+
+    @staticmethod
+    def _ptr_table(tensors) -> C.Array:
+        return (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+    @staticmethod
+    def _i32_table(xs) -> C.Array:
+        return (C.c_int32 * len(xs))(*[int(x) for x in xs])
+
+    def decode_batched(self, q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale, scale_q,
+                       scratch: DecodeScratch, out=None, partial=False) -> torch.Tensor:
+        batch = len(ks)
+        width = heads * (head_dim + 2) if partial else heads * head_dim
+        if out is None:
+            out = self.uninit(batch * width)
+        _check(self._lib.llmtie_decode_batched(
+            self._h, q.data_ptr(), q.numel(), self._ptr_table(ks), self._ptr_table(vs),
+            self._i32_table(tk), self._i32_table(cap), batch, heads, kv_heads, head_dim, scale,
+            int(bool(scale_q)), scratch._bind(self), out.data_ptr(), out.numel(),
+            int(bool(partial))))
+        return out
+
+    def lse_merge(self, parts_buf, parts, rows, head_dim, out=None) -> torch.Tensor:
+        if out is None:
+            out = self.uninit(rows * head_dim)
+        _check(self._lib.llmtie_lse_merge(self._h, parts_buf.data_ptr(), parts_buf.numel(),
+                                          parts, rows, head_dim, out.data_ptr(), out.numel()))
+        return out
+
+    def cross_attn(self, q, k, v, n, heads, head_dim, tk, cap, scale,
+                   scratch: DecodeScratch) -> torch.Tensor:
+        out = self.uninit(n * heads * head_dim)
+        _check(self._lib.llmtie_cross_attn(
+            self._h, q.data_ptr(), q.numel(), k.data_ptr(), k.numel(), v.data_ptr(), v.numel(),
+            n, heads, head_dim, tk, cap, scale, scratch._bind(self), out.data_ptr(),
+            out.numel()))
+        return out
+
+    def prefill_varlen(self, q, k, v, cu_seqlens, kcs, vcs, past, cap, freq_div, heads,
+                       kv_heads, head_dim, theta, scale, out=None) -> torch.Tensor:
+        batch = len(kcs)
+        total = int(cu_seqlens[batch])
+        if out is None:
+            out = self.uninit(total * heads * head_dim)
+        _check(self._lib.llmtie_prefill_varlen(
+            self._h, q.data_ptr(), q.numel(), k.data_ptr(), k.numel(), v.data_ptr(), v.numel(),
+            self._i32_table(cu_seqlens), batch, self._ptr_table(kcs), self._ptr_table(vcs),
+            self._i32_table(past), self._i32_table(cap), _ptr(freq_div), heads, kv_heads,
+            head_dim, theta, scale, out.data_ptr(), out.numel()))
+        return out
+
+    # ---- profiling ------------------------------------------------------------------------
+
+    def kprof_enable(self, on: bool = True) -> None:
+        self._lib.llmtie_kprof_enable(self._h, int(on))
+
+    def kprof_reset(self) -> None:
+        self._lib.llmtie_kprof_reset(self._h)
+
+    def kprof_report(self) -> dict:
+        need = self._lib.llmtie_kprof_report(self._h, None, 0)
+        buf = C.create_string_buffer(int(need) + 1)
+        self._lib.llmtie_kprof_report(self._h, buf, len(buf))
+        rep = {}
+        for line in buf.value.decode().splitlines():
+            name, count, ms = line.rsplit(" ", 2)
+            rep[name] = (int(count), float(ms))
+        return rep
+
+    def kernel_resources(self, name: str):
+        regs, local, smem = C.c_int32(), C.c_int32(), C.c_int32()
+        st = self._lib.llmtie_kernel_resources(name.encode(), C.byref(regs), C.byref(local),
+                                               C.byref(smem))
+        if st != 0:
+            return None
+        return regs.value, local.value, smem.value
+
+    def launch_count(self) -> int:
+        return int(self._lib.llmtie_launch_count(self._h))
