@@ -1,0 +1,477 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+
+The default workload is the long-context decode of the benchmark contract:
+batch 8, context 131072 per sequence, 32 Q / 8 KV heads, head_dim 128, f16 KV
+cache, the KV sequence split evenly over the N GPUs, an all-gather of the
+partial (O, max, sum) triples and a log-sum-exp merge (strong scaling: the
+total work is fixed as N grows). One step is one pass of decode attention
+over the whole batch (one layer). Inputs are seeded synthetic tensors drawn
+N(0,1) and rounded to f16; the KV cache is far larger than L2, so no flush is
+needed between iterations.
+
+`value` is whole-job KV bytes per second with everything resident in HBM;
+`e2e` is the same metric through the C ABI with host buffers: the step's
+q/k/v projections copied from pinned host memory, RoPE and the cache write,
+attention, and the context read back. The CPU arm (`--impl reference`, and the
+`cpu_baseline` object of the default arm) times the C restatement of the
+reference's own scalar attention on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HEADS, KV_HEADS, HD = 32, 8, 128
+SCALE = float(np.float32(HD) ** np.float32(-0.5))
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_TFLOPS = 1590.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant
+# kernel, from the ncu captures summarised under profiles/ (None: not captured).
+NCU_TRAFFIC = {
+    "decode128k": None,
+    "prefill8k": None,
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, FALLBACK_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while a region is timed."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                for name, cell in zip(names, r[5:9]):
+                    if cell.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---- synthetic inputs ---------------------------------------------------------
+
+def device_normal_f16(gpu, n: int, seed: int):
+    """n i.i.d. N(0,1) values rounded to f16, generated on the device."""
+    import torch
+
+    with torch.cuda.stream(gpu.stream):
+        gen = torch.Generator(device=gpu.device)
+        gen.manual_seed(seed)
+        out = torch.empty(n, dtype=torch.float16, device=gpu.device)
+        step = 1 << 26
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            out[a:b] = torch.randn(b - a, generator=gen, device=gpu.device,
+                                   dtype=torch.float32).to(torch.float16)
+    return out
+
+
+def dist_setup(n_gpus: int):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    elif n_gpus > 1:
+        raise SystemExit("bench.py --gpus N>1 must be launched with torch.distributed.run")
+    return world, rank, local
+
+
+def max_over_ranks(x: float, device) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier_sync(gpu):
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    gpu.synchronize()
+
+
+def time_steps(gpu, fn, steps: int, warmup: int) -> float:
+    """Seconds for exactly `steps` calls of fn, CUDA events on the handle's
+    stream, a barrier and a synchronize on both sides; max over ranks."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    barrier_sync(gpu)
+    with torch.cuda.stream(gpu.stream):
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+    barrier_sync(gpu)
+    return max_over_ranks(e0.elapsed_time(e1) / 1e3, gpu.device)
+
+
+# ---- workloads ------------------------------------------------------------------
+
+def decode128k(args, world, rank, local):
+    """Config 5, decode: batch 8 x 131072 context, KV split over the ranks."""
+    import torch
+
+    from ttsxabe_b200 import Gpu
+    from ttsxabe_b200.sharded import ShardedDecode, shard_bounds
+
+    batch, ctx = args.batch, args.context
+    gpu = Gpu.open(local)
+    t0, t1 = shard_bounds(ctx, world, rank)
+    tk = t1 - t0
+    cap = tk
+    ks = [device_normal_f16(gpu, KV_HEADS * cap * HD, 1000 + 17 * b + rank) for b in range(batch)]
+    vs = [device_normal_f16(gpu, KV_HEADS * cap * HD, 5000 + 17 * b + rank) for b in range(batch)]
+    with torch.cuda.stream(gpu.stream):
+        gen = torch.Generator(device=gpu.device)
+        gen.manual_seed(7)   # the same query on every rank
+        q = torch.randn(batch * HEADS * HD, generator=gen, device=gpu.device)
+        q = q.to(torch.float16).to(torch.float32)
+    sd = ShardedDecode.on_gpu(gpu, ks, vs, [tk] * batch, [cap] * batch, HEADS, KV_HEADS, HD,
+                              SCALE)
+    gpu.synchronize()
+
+    launches0 = gpu.launch_count()
+    with ClockSampler(local) as clocks:
+        secs = time_steps(gpu, lambda: sd.decode(q), args.steps, args.warmup)
+    launches = gpu.launch_count() - launches0 - (args.warmup * (1 if world == 1 else 2))
+    clk = clocks.summary()
+
+    # the attention kernel alone (what the roofline is about)
+    ksecs = time_steps(gpu, lambda: sd.partial_fn(q, world > 1), args.steps, 1)
+
+    kv_bytes_total = batch * 2 * KV_HEADS * ctx * HD * 2      # the reference's count
+    kv_bytes_rank = batch * 2 * KV_HEADS * tk * HD * 2
+
+    # ---- end to end through the C ABI with host buffers ------------------------
+    nq, nkv = HEADS * HD, KV_HEADS * HD
+    hq = torch.randn(batch * nq).to(torch.float16).to(torch.float32).pin_memory()
+    hk = torch.randn(batch * nkv).pin_memory()
+    hv = torch.randn(batch * nkv).pin_memory()
+    hout = torch.empty(batch * nq).pin_memory()
+    dqkv = gpu.uninit(batch * (nq + 2 * nkv))
+    lib, h = gpu._lib, gpu._h
+    pos = tk - 1          # the step's new token lands in the last cache slot
+    esz = 4
+
+    def e2e_step():
+        lib.llmtie_upload(h, dqkv.data_ptr(), hq.data_ptr(), batch * nq * esz)
+        lib.llmtie_upload(h, dqkv.data_ptr() + batch * nq * esz, hk.data_ptr(), batch * nkv * esz)
+        lib.llmtie_upload(h, dqkv.data_ptr() + batch * (nq + nkv) * esz, hv.data_ptr(),
+                          batch * nkv * esz)
+        for b in range(batch):
+            gpu.rope_cache_f16([dqkv], (0, b * nq), (0, batch * nq + b * nkv),
+                               (0, batch * (nq + nkv) + b * nkv), None, HEADS, KV_HEADS, HD,
+                               10000.0, pos, ks[b], vs[b], cap)
+        out = sd.decode(dqkv)          # q is the first batch*nq floats
+        lib.llmtie_download(h, hout.data_ptr(), out.data_ptr(), batch * nq * esz)
+
+    for _ in range(max(1, args.warmup)):
+        e2e_step()
+    barrier_sync(gpu)
+    w0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier_sync(gpu)
+    e2e_secs = max_over_ranks((time.perf_counter() - w0), gpu.device) / args.steps
+
+    hbm, _, which = measured_peaks()
+    per_step = secs / args.steps
+    achieved = kv_bytes_rank / (ksecs / args.steps) / 1e9
+    line = {
+        "metric": "decode KV GB/s",
+        "value": kv_bytes_total / per_step / 1e9,
+        "unit": "GB/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": per_step * 1e3,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f16 KV cache, f32 accumulate",
+        "data": "synthetic",
+        "config": {
+            "workload": "config 5 decode: batch %d, context %d per sequence, 32 Q / 8 KV heads, "
+                        "head_dim 128, f16 KV ~N(0,1), KV sequence split evenly over the GPUs, "
+                        "all-gather of (O, max, sum), LSE merge" % (batch, ctx),
+            "global_batch": batch,
+            "context": ctx,
+            "parallelism": "kv-seq-shard x%d" % world,
+            "l2": "inputs (%.0f MB per GPU) exceed L2, no flush" % (kv_bytes_rank / 1e6),
+        },
+        "tokens_per_s": batch / per_step,
+        "clocks": clk,
+        "e2e": {
+            "value": kv_bytes_total / e2e_secs / 1e9,
+            "unit": "GB/s",
+            "ms_per_step": e2e_secs * 1e3,
+            "h2d_bytes_per_step": batch * (nq + 2 * nkv) * esz,
+            "d2h_bytes_per_step": batch * nq * esz,
+        },
+        "gpu_launches": int(launches),
+        "roofline": {
+            "bound": "hbm",
+            "achieved": achieved,
+            "peak": hbm,
+            "unit": "GB/s",
+            "frac": achieved / hbm,
+            "traffic": NCU_TRAFFIC["decode128k"],
+            "peak_source": "of " + which,
+            "kernel": "decode_f16_kernel<128>",
+            "kernel_ms": ksecs / args.steps * 1e3,
+            "algorithmic_bytes_per_launch": kv_bytes_rank,
+            "frac_of_nominal_8tbs": achieved / 8000.0,
+        },
+    }
+    return gpu, line
+
+
+def prefill8k(args, world, rank, local):
+    """Config 5, prefill: causal, 8192 positions, split by KV head, no exchange."""
+    import torch
+
+    from ttsxabe_b200 import Gpu
+    from ttsxabe_b200.sharded import kv_head_shard
+
+    tq = args.seq
+    gpu = Gpu.open(local)
+    h0, h1 = kv_head_shard(KV_HEADS, world, rank)
+    kv = h1 - h0
+    heads = kv * (HEADS // KV_HEADS)
+    cap = tq
+    kc = device_normal_f16(gpu, kv * cap * HD, 11 + rank)
+    vc = device_normal_f16(gpu, kv * cap * HD, 13 + rank)
+    with torch.cuda.stream(gpu.stream):
+        q = torch.randn(tq * heads * HD, device=gpu.device).to(torch.float16).to(torch.float32)
+    out = gpu.uninit(tq * heads * HD)
+    lib, h = gpu._lib, gpu._h
+
+    def step():
+        lib.llmtie_flash_attn_f16(h, q.data_ptr(), q.numel(), kc.data_ptr(), kc.numel(),
+                                  vc.data_ptr(), vc.numel(), out.data_ptr(), out.numel(), tq, 0,
+                                  heads, kv, HD, cap, SCALE, 1)
+
+    launches0 = gpu.launch_count()
+    with ClockSampler(local) as clocks:
+        secs = time_steps(gpu, step, args.steps, args.warmup)
+    launches = gpu.launch_count() - launches0 - args.warmup
+    flops_total = 4.0 * HD * HEADS * (tq * (tq + 1) / 2)
+    flops_rank = 4.0 * HD * heads * (tq * (tq + 1) / 2)
+    _, tf, which = measured_peaks()
+    per_step = secs / args.steps
+    achieved = flops_rank / per_step / 1e12
+    line = {
+        "metric": "attn prefill TFLOP/s",
+        "value": flops_total / per_step / 1e12,
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": per_step * 1e3,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f16 operands, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "config 5 prefill: causal, seq %d, 32 Q / 8 KV heads, head_dim "
+                               "128, sharded by KV head" % tq,
+                   "seq_len": tq, "parallelism": "kv-head-shard x%d" % world,
+                   "l2": "flushed by the %d MB output written each step" % (out.numel() * 4 >> 20)},
+        "tokens_per_s": tq / per_step,
+        "clocks": clocks.summary(),
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf, "unit": "TFLOP/s",
+                     "frac": achieved / tf, "traffic": NCU_TRAFFIC["prefill8k"],
+                     "peak_source": "of " + which,
+                     "frac_of_nominal_2250": achieved / 2250.0},
+    }
+    return gpu, line
+
+
+# ---- CPU arms ---------------------------------------------------------------------
+
+def cpu_decode_sample(context: int, reps: int, threads: int = 0):
+    """Times the oracle's threaded decode on one sequence of the workload
+    (1 of 8; every sequence is the same amount of work). Returns GB/s."""
+    from oracle import oracle as O
+
+    rng = np.random.default_rng(0)
+    n = KV_HEADS * context * HD
+    k = rng.integers(0, 0x3C00, size=n, dtype=np.uint16)   # finite positive halves
+    v = rng.integers(0, 0x3C00, size=n, dtype=np.uint16)
+    q = rng.standard_normal(HEADS * HD).astype(np.float32)
+    best = None
+    used = 0
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        _, used = O.decode_fast(q, k, v, HEADS, KV_HEADS, HD, context, context, SCALE, False,
+                                threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    bytes_one = 2 * KV_HEADS * context * HD * 2
+    return bytes_one / best / 1e9, used, best
+
+
+def reference_arm(args):
+    """The reference's own CPU attention (its scalar decode restated in C,
+    threaded over heads and key slabs) on the host cores, on a bounded sample
+    of the same workload: one sequence of the eight per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+
+    ctx = args.context
+    times = []
+    rng = np.random.default_rng(0)
+    n = KV_HEADS * ctx * HD
+    k = rng.integers(0, 0x3C00, size=n, dtype=np.uint16)
+    v = rng.integers(0, 0x3C00, size=n, dtype=np.uint16)
+    q = rng.standard_normal(HEADS * HD).astype(np.float32)
+    used = 0
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        _, used = O.decode_fast(q, k, v, HEADS, KV_HEADS, HD, ctx, ctx, SCALE, False, 0)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    per = float(np.mean(times))
+    bytes_one = 2 * KV_HEADS * ctx * HD * 2
+    gbs = bytes_one / per / 1e9
+    sample = ("1 of the %d sequences per step (%d keys x 8 KV heads, %.0f MB of KV); "
+              "GB/s is per byte of KV read, so it scales to the full batch" %
+              (args.batch, ctx, bytes_one / 1e6))
+    print(json.dumps({
+        "impl": "reference",
+        "metric": "decode KV GB/s", "value": gbs, "unit": "GB/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per * 1e3 * args.batch,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 KV cache, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "config 5 decode: batch %d, context %d per sequence, 32 Q / 8 KV "
+                               "heads, head_dim 128 (CPU: bounded sample)" % (args.batch, ctx),
+                   "global_batch": args.batch, "context": ctx},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": used, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode128k", choices=["decode128k", "prefill8k"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=131072)
+    ap.add_argument("--seq", type=int, default=8192)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    world, rank, local = dist_setup(args.gpus)
+    fn = decode128k if args.workload == "decode128k" else prefill8k
+    gpu, line = fn(args, world, rank, local)
+    if rank == 0:
+        if world == 1 and not args.no_cpu and args.workload == "decode128k":
+            gbs, used, secs = cpu_decode_sample(args.context, reps=3)
+            line["cpu_baseline"] = {
+                "value": gbs, "unit": "GB/s", "cores": used, "kind": "port",
+                "sample": "1 of the %d sequences, best of 3 (%.2f s each); the C restatement of "
+                          "the reference's scalar decode, threaded over heads and key slabs"
+                          % (args.batch, secs)}
+        print(json.dumps(line))
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

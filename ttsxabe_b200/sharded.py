@@ -1,0 +1,111 @@
+"""One long context spread over several GPUs.
+
+The reference has no multi-GPU scheme; it scales a sequence inside one GPU by
+splitting the keys over blocks and merging partial (o, m, l) triples
+(crates/llmtie-cuda/src/kernels.rs:5779-5903, :6166-6175). This lifts the
+same algebra one level: every rank holds a contiguous slice of each
+sequence's KV positions in its own cache, decodes its slice into
+un-normalised triples, one all-gather moves the triples (a few hundred KB),
+and every rank merges them locally. Prefill shards by KV head instead and
+needs no exchange at all.
+
+One process per GPU; `torch.distributed` carries the all-gather (NCCL on
+GPUs, gloo in the CPU tests).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(tk: int, world: int, rank: int, align: int = 8) -> tuple[int, int]:
+    """Positions [t0, t1) of a tk-long sequence that `rank` holds: contiguous,
+    even to within `align`, and aligned so that every slice's value rows keep
+    16-byte alignment in its own cache."""
+    per = -(-tk // world)
+    per = -(-per // align) * align
+    t0 = min(tk, rank * per)
+    t1 = min(tk, t0 + per)
+    return t0, t1
+
+
+def kv_head_shard(kv_heads: int, world: int, rank: int) -> tuple[int, int]:
+    """KV heads [h0, h1) `rank` takes when a prefill is split by KV head
+    (its query heads are h0*group .. h1*group). Needs world <= kv_heads."""
+    if world > kv_heads:
+        raise ValueError(f"{world} ranks cannot split {kv_heads} KV heads")
+    per, extra = divmod(kv_heads, world)
+    h0 = rank * per + min(rank, extra)
+    return h0, h0 + per + (1 if rank < extra else 0)
+
+
+class ShardedDecode:
+    """Decode attention over KV slices held by the ranks of `group`.
+
+    `partial_fn(q, partial) -> tensor` computes this rank's result for its
+    slice: normalised [batch, heads*hd] when the world is one rank, else the
+    triples [batch, heads, hd+2]. `merge_fn(gathered, parts, rows) -> tensor`
+    merges [parts][rows][hd+2]. Both default to the GPU entry points; the CPU
+    tests inject host implementations to exercise the exchange itself.
+    """
+
+    def __init__(self, heads: int, head_dim: int, group: Optional[dist.ProcessGroup] = None,
+                 partial_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None,
+                 stream: Optional[torch.cuda.Stream] = None) -> None:
+        self.heads = heads
+        self.head_dim = head_dim
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.partial_fn = partial_fn
+        self.merge_fn = merge_fn
+        self.stream = stream
+        self._gathered = None
+
+    @classmethod
+    def on_gpu(cls, gpu, ks: Sequence[torch.Tensor], vs: Sequence[torch.Tensor],
+               tk: Sequence[int], cap: Sequence[int], heads: int, kv_heads: int, head_dim: int,
+               scale: float, scale_q: bool = False, group=None) -> "ShardedDecode":
+        """Binds the GPU entry points over this rank's caches."""
+        from .gpu import DecodeScratch
+
+        scratch = DecodeScratch()
+        batch = len(ks)
+        outs = {}
+
+        def partial_fn(q, partial):
+            width = heads * (head_dim + 2) if partial else heads * head_dim
+            if partial not in outs:
+                outs[partial] = gpu.uninit(batch * width)
+            return gpu.decode_batched(q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
+                                      scale_q, scratch, out=outs[partial], partial=partial)
+
+        merged = {}
+
+        def merge_fn(gathered, parts, rows):
+            if "out" not in merged:
+                merged["out"] = gpu.uninit(rows * head_dim)
+            return gpu.lse_merge(gathered, parts, rows, head_dim, out=merged["out"])
+
+        self = cls(heads, head_dim, group, partial_fn, merge_fn, gpu.stream)
+        self._scratch = scratch
+        return self
+
+    def decode(self, q: torch.Tensor) -> torch.Tensor:
+        """q: [batch, heads*hd] (rotated), the same on every rank. Returns the
+        attention output [batch*heads*hd] on every rank."""
+        if self.world == 1:
+            return self.partial_fn(q, False)
+        part = self.partial_fn(q, True)
+        if self._gathered is None or self._gathered.numel() != part.numel() * self.world:
+            self._gathered = torch.empty(part.numel() * self.world, dtype=part.dtype,
+                                         device=part.device)
+        if self.stream is not None:
+            with torch.cuda.stream(self.stream):
+                dist.all_gather_into_tensor(self._gathered, part.reshape(-1), group=self.group)
+        else:
+            dist.all_gather_into_tensor(self._gathered, part.reshape(-1), group=self.group)
+        rows = part.numel() // (self.head_dim + 2)
+        return self.merge_fn(self._gathered, self.world, rows)
