@@ -6,6 +6,7 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -657,13 +658,13 @@ extern "C" void llmtie_decode_scratch_free(llmtie_gpu *g, llmtie_decode_scratch 
     delete s;
 }
 
-// Grows the scratch to hold `pairs` heads of `splits` partials. Stream-ordered,
+// Grows the scratch to hold `partials` partial triples and `pairs` counters. Stream-ordered,
 // so a kernel still reading the old buffers is not disturbed; counters are
 // zero when allocated and every launch leaves them at zero.
 static llmtie_status scratch_reserve(llmtie_gpu *g, llmtie_decode_scratch *s, size_t pairs,
-                                     size_t splits, size_t hd)
+                                     size_t partials, size_t hd)
 {
-    const size_t floats = pairs * splits * 8 * (hd + 2);
+    const size_t floats = partials * 8 * (hd + 2);
     if (floats > s->part_floats) {
         if (s->part) cudaFreeAsync(s->part, g->stream);
         s->part = nullptr;
@@ -686,18 +687,40 @@ static llmtie_status scratch_reserve(llmtie_gpu *g, llmtie_decode_scratch *s, si
     return LLMTIE_OK;
 }
 
-// Picks the span of keys a block takes so that one wave of blocks covers the
-// whole launch: every block is resident at once and they finish together.
+// Picks how the keys are cut into blocks of the grid. Every block should be
+// resident at once and finish with the others, so the span is the smallest
+// multiple of 128 keys for which the whole launch is at most one wave.
 static void decode_plan(llmtie_gpu *g, DecodeParams &p, int hd)
 {
-    const int slots = decode_resident_blocks(hd, g->sm_count);
-    long long units = 0;   // 128-key units over every (sequence, kv head, row chunk)
     int max_tk = 0;
+    long long keys = 0;
     for (int b = 0; b < p.nseq; b++) {
-        units += (long long)((p.seq[b].tk + 127) / 128) * p.kv_heads * p.row_chunks;
         max_tk = std::max(max_tk, p.seq[b].tk);
+        keys += p.seq[b].tk;
     }
-    const long long per = std::max<long long>(1, (units + slots - 1) / slots);
+    // Long rows are worth reading in longer runs along the transposed value
+    // cache; short contexts want the finest split instead.
+    static const int forced = [] {
+        const char *e = getenv("LLMTIE_B200_DECODE_NB");
+        return e ? atoi(e) : 0;
+    }();
+    const long long per_pair = keys / std::max(1, p.nseq);
+    int nb = per_pair >= 8192 ? 2 : 1;
+    if (forced == 1 || forced == 2 || forced == 4 || forced == 8) nb = forced;
+    p.nb = nb;
+    const int slots = decode_resident_blocks(hd, g->sm_count, nb);
+    const long long pairs = (long long)p.kv_heads * p.row_chunks;
+    long long per = 1;   // span in units of 128 keys
+    for (;;) {
+        long long blocks = 0;
+        for (int b = 0; b < p.nseq; b++) {
+            blocks += ((p.seq[b].tk + per * 128 - 1) / (per * 128)) * pairs;
+        }
+        if (blocks <= slots || per * 128 >= max_tk) break;
+        // jump straight to the span the block count suggests, then refine
+        const long long guess = (per * blocks + slots - 1) / slots;
+        per = std::max(per + 1, guess);
+    }
     p.span = (int)(per * 128);
     p.max_splits = (max_tk + p.span - 1) / p.span;
 }
@@ -705,9 +728,57 @@ static void decode_plan(llmtie_gpu *g, DecodeParams &p, int hd)
 static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams &p, int hd,
                                    llmtie_decode_scratch *scratch)
 {
+    bool aligned = true;
+    for (int b = 0; b < p.nseq; b++) {
+        if (p.seq[b].cap % 8 != 0 || ((uintptr_t)p.seq[b].v & 15u) != 0) aligned = false;
+    }
+    static const bool no_stream = getenv("LLMTIE_B200_DECODE_NO_STREAM") != nullptr;
+    if (aligned && !no_stream) {
+        // The ring kernel, cut by work: one block per SM, never more blocks
+        // than 128-key units.
+        DecodeStreamParams sp;
+        memset(&sp, 0, sizeof(sp));
+        const int inner = p.kv_heads * p.row_chunks;
+        long long units = 0;
+        for (int b = 0; b < p.nseq; b++) {
+            sp.seq[b] = p.seq[b];
+            sp.unit0[b] = units;
+            sp.pair0[b] = b * inner;
+            units += (long long)((p.seq[b].tk + 127) / 128) * inner;
+        }
+        sp.unit0[p.nseq] = units;
+        sp.pair0[p.nseq] = p.nseq * inner;
+        sp.total_units = units;
+        sp.q = p.q;
+        sp.q_seq = p.q_seq;
+        sp.q_kv = p.q_kv;
+        sp.q_row = p.q_row;
+        sp.out = p.out;
+        sp.out_seq = p.out_seq;
+        sp.out_kv = p.out_kv;
+        sp.out_row = p.out_row;
+        sp.rows = p.rows;
+        sp.row_chunks = p.row_chunks;
+        sp.kv_heads = p.kv_heads;
+        sp.nseq = p.nseq;
+        sp.partial = p.partial;
+        sp.q_scale = p.q_scale;
+        sp.sl2 = p.sl2;
+        const int grid = (int)std::min<long long>(g->sm_count, units);
+        const llmtie_status s =
+            scratch_reserve(g, scratch, (size_t)p.nseq * inner, (size_t)grid * 2, (size_t)hd);
+        if (s != LLMTIE_OK) return s;
+        sp.part = scratch->part;
+        sp.ctr = scratch->ctr;
+        LaunchScope ls(g, name);
+        const cudaError_t e = launch_decode_stream(g->stream, sp, hd, grid);
+        if (e != cudaSuccess) return driver_fail(name, e);
+        return ls.done();
+    }
     decode_plan(g, p, hd);
     const size_t pairs = (size_t)p.nseq * p.row_chunks * p.kv_heads;
-    const llmtie_status s = scratch_reserve(g, scratch, pairs, (size_t)p.max_splits, (size_t)hd);
+    const llmtie_status s =
+        scratch_reserve(g, scratch, pairs, pairs * (size_t)p.max_splits, (size_t)hd);
     if (s != LLMTIE_OK) return s;
     p.part = scratch->part;
     p.ctr = scratch->ctr;

@@ -97,6 +97,7 @@ struct DecodeParams {
     int nseq;
     int span;              // keys per block of the grid, a multiple of 128
     int max_splits;        // grid.x
+    int nb;                // 32-key sub-blocks a warp takes per step: 1, 2, 4 or 8
     int partial;           // write (o, m, l) un-normalised, row stride hd + 2
     float q_scale;         // scale when it goes on q, else 1
     float sl2;             // (scale on the scores, else 1) * log2(e)
@@ -104,7 +105,24 @@ struct DecodeParams {
 // hd is 64 or 128. Returns the cudaError of the launch.
 cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd);
 // How many blocks of the decode kernel fit the device at once.
-int decode_resident_blocks(int hd, int sm_count);
+int decode_resident_blocks(int hd, int sm_count, int nb);
+// decode_stream.cu: the same operands cut over the grid by work (see there).
+struct DecodeStreamParams {
+    DecodeSeq seq[LLMTIE_DECODE_MAX_SEQ];
+    long long unit0[LLMTIE_DECODE_MAX_SEQ + 1];   // first 128-key unit of each sequence
+    int pair0[LLMTIE_DECODE_MAX_SEQ + 1];         // first (row chunk, kv head) pair of each
+    long long total_units;
+    const float *q;
+    long long q_seq, q_kv, q_row;
+    float *out;
+    long long out_seq, out_kv, out_row;
+    float *part;           // partials [block][2][8][hd + 2]
+    unsigned *ctr;         // arrival counters [pair]
+    int rows, row_chunks, kv_heads, nseq;
+    int partial;
+    float q_scale, sl2;
+};
+cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
                        const float *v, float *out, long long out_off, int heads, int kv_heads,
                        int hd, int tk, int cap, float q_scale, float s_scale);

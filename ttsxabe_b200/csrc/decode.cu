@@ -86,8 +86,8 @@ constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr int kRows = 8;   // query rows a block carries
 
-template <int HD, bool V16>
-__global__ void __launch_bounds__(kThreads, 3)
+template <int HD, bool V16, int NB>
+__global__ void __launch_bounds__(kThreads, NB == 1 ? 3 : 2)
 decode_f16_kernel(const __grid_constant__ DecodeParams p)
 {
     constexpr int KI = HD / 32;
@@ -148,45 +148,57 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p)
         o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
     }
 
-    for (int blk = k_begin + warp * 32; blk < k_end; blk += kWarps * 32) {
-        // ---- scores: four 8-key tiles ------------------------------------
-        float t[2][2][2];
+    // A warp takes 32 * NB consecutive keys a step. The scores of all of them
+    // are taken first, so that the value rows - one DRAM page each in the
+    // transposed cache - are then read 64 * NB contiguous bytes at a time.
+    for (int blk = k_begin + warp * 32 * NB; blk < k_end; blk += kWarps * 32 * NB) {
+        // ---- scores: NB sub-blocks of four 8-key tiles ----------------------
+        float t[NB][2][2][2];
 #pragma unroll
-        for (int mm = 0; mm < 2; mm++) {
+        for (int sb = 0; sb < NB; sb++) {
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int key = blk + 8 * (g >> 1) + 4 * mm + 2 * h + (g & 1);
-                const uint16_t *krow = kbase + ((size_t)kh * cap + key) * HD + 8 * c;
-                const bool live = key < k_end;
-                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int mm = 0; mm < 2; mm++) {
 #pragma unroll
-                for (int i = 0; i < KI; i++) {
-                    uint32_t r[4] = {0u, 0u, 0u, 0u};
-                    if (live) ldg128(r, krow + 32 * i);
-                    mma16816(acc, qa[i][0][0], qa[i][0][1], qa[i][0][2], qa[i][0][3], r[0], r[1]);
-                    mma16816(acc, qa[i][1][0], qa[i][1][1], qa[i][1][2], qa[i][1][3], r[2], r[3]);
+                for (int h = 0; h < 2; h++) {
+                    const int key = blk + 32 * sb + 8 * (g >> 1) + 4 * mm + 2 * h + (g & 1);
+                    const uint16_t *krow = kbase + ((size_t)kh * cap + key) * HD + 8 * c;
+                    const bool live = key < k_end;
+                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int i = 0; i < KI; i++) {
+                        uint32_t r[4] = {0u, 0u, 0u, 0u};
+                        if (live) ldg128(r, krow + 32 * i);
+                        mma16816(acc, qa[i][0][0], qa[i][0][1], qa[i][0][2], qa[i][0][3], r[0],
+                                 r[1]);
+                        mma16816(acc, qa[i][1][0], qa[i][1][1], qa[i][1][2], qa[i][1][3], r[2],
+                                 r[3]);
+                    }
+                    // this thread's two columns: keys blk + 32sb + 8c + 4mm + 2h + {0, 1}
+                    const int k0 = blk + 32 * sb + 8 * c + 4 * mm + 2 * h;
+                    t[sb][mm][h][0] = (k0 < k_end) ? (acc[0] + acc[2]) * p.sl2 : -CUDART_INF_F;
+                    t[sb][mm][h][1] =
+                        (k0 + 1 < k_end) ? (acc[1] + acc[3]) * p.sl2 : -CUDART_INF_F;
                 }
-                // this thread's two columns are keys blk + 8c + 4mm + 2h + {0, 1}
-                const int k0 = blk + 8 * c + 4 * mm + 2 * h;
-                t[mm][h][0] = (k0 < k_end) ? (acc[0] + acc[2]) * p.sl2 : -CUDART_INF_F;
-                t[mm][h][1] = (k0 + 1 < k_end) ? (acc[1] + acc[3]) * p.sl2 : -CUDART_INF_F;
             }
         }
 
-        // ---- online softmax over the block --------------------------------
+        // ---- online softmax over the step ------------------------------------
         float bm = -CUDART_INF_F;
 #pragma unroll
-        for (int mm = 0; mm < 2; mm++) {
+        for (int sb = 0; sb < NB; sb++) {
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                bm = fmaxf(bm, fmaxf(t[mm][h][0], t[mm][h][1]));
+            for (int mm = 0; mm < 2; mm++) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    bm = fmaxf(bm, fmaxf(t[sb][mm][h][0], t[sb][mm][h][1]));
+                }
             }
         }
         bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
         bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
         const float m_new = fmaxf(m, bm);
         if (__any_sync(0xffffffffu, m_new > m)) {
-            const float alpha = ex2(m - m_new);   // 0 on the first block
+            const float alpha = ex2(m - m_new);   // 0 on the first step
             l *= alpha;
 #pragma unroll
             for (int j = 0; j < NT; j++) {
@@ -197,45 +209,56 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p)
             }
         }
         m = m_new;
-        uint32_t pa[2][4];
+        uint32_t pa[NB][2][4];
 #pragma unroll
-        for (int mm = 0; mm < 2; mm++) {
+        for (int sb = 0; sb < NB; sb++) {
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const float p0 = ex2(t[mm][h][0] - m);
-                const float p1 = ex2(t[mm][h][1] - m);
-                l += p0 + p1;
-                split_pair(p0, p1, pa[mm][2 * h], pa[mm][2 * h + 1]);
+            for (int mm = 0; mm < 2; mm++) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const float p0 = ex2(t[sb][mm][h][0] - m);
+                    const float p1 = ex2(t[sb][mm][h][1] - m);
+                    l += p0 + p1;
+                    split_pair(p0, p1, pa[sb][mm][2 * h], pa[sb][mm][2 * h + 1]);
+                }
             }
         }
 
-        // ---- context: HD/8 tiles of 8 value rows --------------------------
-        const int g0 = blk + 8 * c;       // this thread's first key
-        const int nlive = k_end - g0;     // keys of its eight that exist
+        // ---- context: HD/8 tiles of 8 value rows, NB loads along each row ------
 #pragma unroll
         for (int j = 0; j < NT; j++) {
-            const uint16_t *vrow = vbase + ((size_t)kh * HD + 8 * j + g) * cap + g0;
-            uint32_t r[4] = {0u, 0u, 0u, 0u};
-            if (V16) {
-                if (nlive > 0) ldg128(r, vrow);
-            } else {
-                if (nlive > 0) ldg64(r[0], r[1], vrow);
-                if (nlive > 4) ldg64(r[2], r[3], vrow + 4);
-            }
-            if (nlive < 8) {
-                // Capacity past the live keys may hold anything, and 0 * NaN
-                // is NaN: clear what lies beyond.
+            const uint16_t *vrow = vbase + ((size_t)kh * HD + 8 * j + g) * cap + blk + 8 * c;
+            uint32_t r[NB][4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    if (nlive <= 2 * i) {
-                        r[i] = 0u;
-                    } else if (nlive == 2 * i + 1) {
-                        r[i] &= 0x0000ffffu;
+            for (int sb = 0; sb < NB; sb++) {
+                const int nlive = k_end - (blk + 32 * sb + 8 * c);   // keys of its eight that exist
+                r[sb][0] = r[sb][1] = r[sb][2] = r[sb][3] = 0u;
+                if (V16) {
+                    if (nlive > 0) ldg128(r[sb], vrow + 32 * sb);
+                } else {
+                    if (nlive > 0) ldg64(r[sb][0], r[sb][1], vrow + 32 * sb);
+                    if (nlive > 4) ldg64(r[sb][2], r[sb][3], vrow + 32 * sb + 4);
+                }
+                if (nlive < 8) {
+                    // Capacity past the live keys may hold anything, and 0 * NaN
+                    // is NaN: clear what lies beyond.
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        if (nlive <= 2 * i) {
+                            r[sb][i] = 0u;
+                        } else if (nlive == 2 * i + 1) {
+                            r[sb][i] &= 0x0000ffffu;
+                        }
                     }
                 }
             }
-            mma16816(o[j], pa[0][0], pa[0][1], pa[0][2], pa[0][3], r[0], r[1]);
-            mma16816(o[j], pa[1][0], pa[1][1], pa[1][2], pa[1][3], r[2], r[3]);
+#pragma unroll
+            for (int sb = 0; sb < NB; sb++) {
+                mma16816(o[j], pa[sb][0][0], pa[sb][0][1], pa[sb][0][2], pa[sb][0][3], r[sb][0],
+                         r[sb][1]);
+                mma16816(o[j], pa[sb][1][0], pa[sb][1][1], pa[sb][1][2], pa[sb][1][3], r[sb][2],
+                         r[sb][3]);
+            }
         }
     }
 
@@ -428,51 +451,70 @@ __global__ void lse_merge_kernel(const float *__restrict__ buf, int parts, int r
     }
 }
 
-const KernelReg reg_d128("attn_decode_h128", (const void *)decode_f16_kernel<128, true>);
-const KernelReg reg_d128u("attn_decode_h128_unaligned", (const void *)decode_f16_kernel<128, false>);
-const KernelReg reg_d64("attn_decode_h64", (const void *)decode_f16_kernel<64, true>);
-const KernelReg reg_d64u("attn_decode_h64_unaligned", (const void *)decode_f16_kernel<64, false>);
+const KernelReg reg_d128("attn_decode_h128", (const void *)decode_f16_kernel<128, true, 1>);
+const KernelReg reg_d128w("attn_decode_h128_wide", (const void *)decode_f16_kernel<128, true, 4>);
+const KernelReg reg_d128u("attn_decode_h128_unaligned",
+                          (const void *)decode_f16_kernel<128, false, 1>);
+const KernelReg reg_d64("attn_decode_h64", (const void *)decode_f16_kernel<64, true, 1>);
+const KernelReg reg_d64w("attn_decode_h64_wide", (const void *)decode_f16_kernel<64, true, 4>);
+const KernelReg reg_d64u("attn_decode_h64_unaligned",
+                         (const void *)decode_f16_kernel<64, false, 1>);
 const KernelReg reg_df32("attn_decode_f64", (const void *)decode_f32_kernel<64>);
 const KernelReg reg_merge("lse_merge", (const void *)lse_merge_kernel);
+
+template <int HD, bool V16, int NB>
+cudaError_t launch_one(cudaStream_t st, const DecodeParams &p)
+{
+    const dim3 grid(p.max_splits, p.kv_heads, p.nseq * p.row_chunks);
+    decode_f16_kernel<HD, V16, NB><<<grid, kThreads, 0, st>>>(p);
+    return cudaGetLastError();
+}
+
+template <int HD>
+cudaError_t launch_hd(cudaStream_t st, const DecodeParams &p, bool v16)
+{
+    if (!v16) return launch_one<HD, false, 1>(st, p);
+    switch (p.nb) {
+    case 8: return launch_one<HD, true, 8>(st, p);
+    case 4: return launch_one<HD, true, 4>(st, p);
+    case 2: return launch_one<HD, true, 2>(st, p);
+    default: return launch_one<HD, true, 1>(st, p);
+    }
+}
+
+template <int HD>
+int resident(int nb)
+{
+    int per_sm = 0;
+    cudaError_t e;
+    switch (nb) {
+    case 8: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &per_sm, decode_f16_kernel<HD, true, 8>, kThreads, 0); break;
+    case 4: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &per_sm, decode_f16_kernel<HD, true, 4>, kThreads, 0); break;
+    case 2: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &per_sm, decode_f16_kernel<HD, true, 2>, kThreads, 0); break;
+    default: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                 &per_sm, decode_f16_kernel<HD, true, 1>, kThreads, 0); break;
+    }
+    if (e != cudaSuccess || per_sm < 1) per_sm = 1;
+    return per_sm;
+}
 
 }  // namespace
 
 cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd)
 {
-    const dim3 grid(p.max_splits, p.kv_heads, p.nseq * p.row_chunks);
     bool v16 = true;
     for (int b = 0; b < p.nseq; b++) {
         if (p.seq[b].cap % 8 != 0 || ((uintptr_t)p.seq[b].v & 15u) != 0) v16 = false;
     }
-    if (hd == 128) {
-        if (v16) {
-            decode_f16_kernel<128, true><<<grid, kThreads, 0, st>>>(p);
-        } else {
-            decode_f16_kernel<128, false><<<grid, kThreads, 0, st>>>(p);
-        }
-    } else {
-        if (v16) {
-            decode_f16_kernel<64, true><<<grid, kThreads, 0, st>>>(p);
-        } else {
-            decode_f16_kernel<64, false><<<grid, kThreads, 0, st>>>(p);
-        }
-    }
-    return cudaGetLastError();
+    return hd == 128 ? launch_hd<128>(st, p, v16) : launch_hd<64>(st, p, v16);
 }
 
-int decode_resident_blocks(int hd, int sm_count)
+int decode_resident_blocks(int hd, int sm_count, int nb)
 {
-    int per_sm = 0;
-    cudaError_t e;
-    if (hd == 128) {
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_f16_kernel<128, true>,
-                                                          kThreads, 0);
-    } else {
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_f16_kernel<64, true>,
-                                                          kThreads, 0);
-    }
-    if (e != cudaSuccess || per_sm < 1) per_sm = 1;
-    return per_sm * sm_count;
+    return (hd == 128 ? resident<128>(nb) : resident<64>(nb)) * sm_count;
 }
 
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
