@@ -198,6 +198,28 @@ llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_t q_len, si
                                  int32_t scale_q, llmtie_decode_scratch *scratch,
                                  float *out, size_t out_len, size_t out_off);
 
+/* llmtie_attn_decode_f16 for callers that cannot allocate. This entry has no
+ * counterpart in the reference: there, as in llmtie_attn_decode_f16, the
+ * caller's DecodeScratch grows by a stream-ordered allocation inside the
+ * call. A per-token thread of a voice pipeline that must never wait on the
+ * driver, or a process that handed the whole device to its own pool, cannot
+ * take that, so here the partials and counters live in a static device array
+ * inside the library (about 1.3 MB on every GPU that loads it, until exit)
+ * and the call allocates and frees nothing.
+ * Limits, refused by name: at most 64 kv heads; capacity a multiple of 8 and
+ * 16-byte aligned caches (LLMTIE_ERR_MISALIGNED otherwise); head_dim and
+ * group as llmtie_attn_decode_f16.
+ * The first call on a device resolves the array's address; make that call
+ * before any stream capture. All calls share the array: it keeps the last
+ * call's contents (the call clears what must start at zero), and two calls
+ * that overlap on the GPU race - order them one after another. */
+llmtie_status llmtie_attn_decode_f16_noalloc(llmtie_gpu *g, const float *q, size_t q_len,
+                                             size_t q_off, const uint16_t *k, size_t k_len,
+                                             const uint16_t *v, size_t v_len, size_t heads,
+                                             size_t kv_heads, size_t head_dim, size_t tk,
+                                             size_t cap, float scale, int32_t scale_q,
+                                             float *out, size_t out_len, size_t out_off);
+
 /* ---- batched and sharded entries (supersets; the reference loops) ------------ */
 
 /* What crates/llmtie-translate/src/model.rs:824-859 does as a loop of

@@ -57,6 +57,8 @@ PROTOTYPES = {
         i32, [vp, vp, sz, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, i32, vp, vp, sz, sz]),
     "llmtie_attn_decode": (
         i32, [vp, vp, sz, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, i32, vp, vp, sz, sz]),
+    "llmtie_attn_decode_f16_noalloc": (
+        i32, [vp, vp, sz, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, i32, vp, sz, sz]),
     "llmtie_decode_batched": (
         i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp, sz, i32]),
     "llmtie_lse_merge": (i32, [vp, vp, sz, sz, sz, sz, vp, sz]),

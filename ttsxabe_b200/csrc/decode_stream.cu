@@ -26,6 +26,7 @@
 #include "common.cuh"
 
 #include <math_constants.h>
+#include <string.h>
 
 namespace {
 
@@ -456,4 +457,155 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, i
         decode_stream_kernel<64><<<grid, kThreads, ring_bytes<64>(), st>>>(p);
     }
     return cudaGetLastError();
+}
+
+// ---- a decode entry point that allocates nothing -----------------------------------
+//
+// llmtie_attn_decode_f16 grows its caller's DecodeScratch with a stream-ordered
+// allocation whenever a longer context needs more partials. Some callers
+// cannot have that: a voice pipeline's per-token thread, where an allocation
+// that has to go to the driver stalls every other stream on the card; or a
+// process that gave the whole device to its own pool up front and has nothing
+// left for anyone else to allocate from. For them the partials and the
+// arrival counters live in the two arrays below, which every GPU that loads
+// this library carries from load until exit (about 1.3 MB).
+//
+// The array names are host-side stand-ins, not device addresses. The address
+// the kernel is given comes from cudaGetSymbolAddress, taken once per device
+// with that device current, on the first call made on that device - so that
+// first call should be made before any stream capture begins.
+//
+// Every call shares the arrays, and they keep what the last call left:
+// the partials are always written before they are read, and the counters are
+// cleared at the start of each call. Two calls that overlap on the GPU (two
+// streams, two handles, two threads) would race on them; calls must be
+// ordered one after another.
+namespace {
+
+constexpr int kStaticMaxBlocks = 160;   // blocks the launch may use (one per SM)
+constexpr int kStaticMaxPairs = 64;     // kv heads it may carry
+constexpr size_t kStaticPartFloats = (size_t)kStaticMaxBlocks * 2 * kRows * (128 + 2);
+
+static __device__ __align__(256) float g_static_part[kStaticPartFloats];
+static __device__ __align__(256) unsigned g_static_ctr[kStaticMaxPairs];
+
+struct StaticScratch {
+    bool ready = false;
+    float *part = nullptr;
+    unsigned *ctr = nullptr;
+};
+StaticScratch g_static_addr[64];
+
+}  // namespace
+
+extern "C" llmtie_status llmtie_attn_decode_f16_noalloc(
+    llmtie_gpu *g, const float *q, size_t q_len, size_t q_off, const uint16_t *k, size_t k_len,
+    const uint16_t *v, size_t v_len, size_t heads, size_t kv_heads, size_t head_dim, size_t tk,
+    size_t cap, float scale, int32_t scale_q, float *out, size_t out_len, size_t out_off)
+{
+    if (!g) return llmtie_fail(LLMTIE_ERR_INVALID, "null device handle");
+    if (g->ordinal < 0 || g->ordinal >= 64) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "device ordinal %d is out of range", g->ordinal);
+    }
+    cudaSetDevice(g->ordinal);
+    if (head_dim != 64 && head_dim != 128) {
+        return llmtie_fail(LLMTIE_ERR_UNSUPPORTED_ATTENTION,
+                           "fused attention wants head_dim 64 or 128, got %zu", head_dim);
+    }
+    const size_t gmax = head_dim == 128 ? 4 : 8;
+    if (kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > gmax) {
+        return llmtie_fail(LLMTIE_ERR_UNSUPPORTED_ATTENTION,
+                           "fused attention wants heads a multiple of kv_heads with a group of "
+                           "at most %zu, got %zu heads over %zu", gmax, heads, kv_heads);
+    }
+    if (kv_heads > (size_t)kStaticMaxPairs) {
+        return llmtie_fail(LLMTIE_ERR_UNSUPPORTED_ATTENTION,
+                           "%zu kv heads is more than the %d the static scratch carries",
+                           kv_heads, kStaticMaxPairs);
+    }
+    if (tk == 0 || tk > cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", tk, cap);
+    }
+    if (cap > 0x7fffffffu) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "capacity does not fit 32 bits");
+    }
+    if (cap % 8 != 0 || ((uintptr_t)v & 15u) != 0 || ((uintptr_t)k & 15u) != 0) {
+        return llmtie_fail(LLMTIE_ERR_MISALIGNED,
+                           "the allocation-free decode wants 16-byte aligned caches and a "
+                           "capacity that is a multiple of 8, got %zu", cap);
+    }
+    const size_t need = kv_heads * cap * head_dim;
+    if (k_len < need || v_len < need) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", need,
+                           k_len < v_len ? k_len : v_len);
+    }
+    const size_t n = heads * head_dim;
+    if (q_len < q_off + n) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           q_off + n, q_len);
+    }
+    if (out_len < out_off + n) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           out_off + n, out_len);
+    }
+    if (out_off % 32 != 0) {
+        return llmtie_fail(LLMTIE_ERR_RAGGED_BLOCK,
+                           "a row of %zu does not divide into blocks of 32", out_off);
+    }
+
+    StaticScratch &ss = g_static_addr[g->ordinal];
+    if (!ss.ready) {
+        cudaError_t e = cudaGetSymbolAddress((void **)&ss.part, g_static_part);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress((void **)&ss.ctr, g_static_ctr);
+        if (e != cudaSuccess) {
+            return llmtie_fail(LLMTIE_ERR_DRIVER, "resolving the static scratch: %s",
+                               cudaGetErrorString(e));
+        }
+        ss.ready = true;
+    }
+
+    const size_t group = heads / kv_heads;
+    DecodeStreamParams sp;
+    memset(&sp, 0, sizeof(sp));
+    const long long units = (long long)((tk + 127) / 128) * (long long)kv_heads;
+    sp.nseq = 1;
+    sp.seq[0].k = k;
+    sp.seq[0].v = v;
+    sp.seq[0].tk = (int)tk;
+    sp.seq[0].cap = (int)cap;
+    sp.unit0[0] = 0;
+    sp.unit0[1] = units;
+    sp.pair0[0] = 0;
+    sp.pair0[1] = (int)kv_heads;
+    sp.total_units = units;
+    sp.q = q + q_off;
+    sp.q_kv = (long long)(group * head_dim);
+    sp.q_row = (long long)head_dim;
+    sp.out = out + out_off;
+    sp.out_kv = (long long)(group * head_dim);
+    sp.out_row = (long long)head_dim;
+    sp.rows = (int)group;
+    sp.row_chunks = 1;
+    sp.kv_heads = (int)kv_heads;
+    sp.partial = 0;
+    sp.q_scale = scale_q ? scale : 1.0f;
+    sp.sl2 = (scale_q ? 1.0f : scale) * 1.4426950408889634f;
+    sp.part = ss.part;
+    sp.ctr = ss.ctr;
+    long long grid = g->sm_count < kStaticMaxBlocks ? g->sm_count : kStaticMaxBlocks;
+    if (units < grid) grid = units;
+    // The counters must start at zero whatever an earlier call left behind.
+    cudaError_t e = cudaMemsetAsync(ss.ctr, 0, sizeof(unsigned) * kStaticMaxPairs, g->stream);
+    if (e != cudaSuccess) {
+        return llmtie_fail(LLMTIE_ERR_DRIVER, "clearing the static counters: %s",
+                           cudaGetErrorString(e));
+    }
+    LaunchScope ls(g, head_dim == 128 ? "attn_decode_h128_run" : "attn_decode_h64_run");
+    e = launch_decode_stream(g->stream, sp, (int)head_dim, (int)grid);
+    if (e != cudaSuccess) {
+        return llmtie_fail(LLMTIE_ERR_DRIVER, "attn_decode (static scratch): %s",
+                           cudaGetErrorString(e));
+    }
+    return ls.done();
 }

@@ -303,6 +303,20 @@ class Gpu:
             v.numel(), heads, kv_heads, head_dim, tk, cap, scale, int(bool(scale_q)),
             scratch._bind(self), out.data_ptr(), out.numel(), row * heads * head_dim))
 
+    def attn_decode_f16_noalloc(self, q, k, v, heads, kv_heads, head_dim, tk, cap, scale,
+                                scale_q, out=None) -> torch.Tensor:
+        """`attn_decode_f16` for callers that cannot allocate: no DecodeScratch,
+        the partials live in a static array inside the library. The output
+        buffer is still the caller's; pass `out` to keep this call free of any
+        allocation. Calls must not overlap on the GPU (they share the array)."""
+        if out is None:
+            out = self.uninit(heads * head_dim)
+        _check(self._lib.llmtie_attn_decode_f16_noalloc(
+            self._h, q.data_ptr(), q.numel(), 0, k.data_ptr(), k.numel(), v.data_ptr(),
+            v.numel(), heads, kv_heads, head_dim, tk, cap, scale, int(bool(scale_q)),
+            out.data_ptr(), out.numel(), 0))
+        return out
+
     def attn_decode(self, q, k, v, heads, kv_heads, head_dim, tk, cap, scale, scale_q,
                     scratch: DecodeScratch) -> torch.Tensor:
         out = self.uninit(heads * head_dim)
