@@ -469,7 +469,15 @@ static llmtie_status misaligned(const char *what, const void *p, size_t align)
                        what, (size_t)(uintptr_t)p, align);
 }
 
-// One sequence through the general kernel.
+// Whether a prefill takes the tensor-memory kernel (aligned f16 caches at
+// head_dim 128) or the general one. LLMTIE_B200_NO_TC forces the general one.
+static bool use_tc(const PrefillParams &p, int hd)
+{
+    static const bool off = getenv("LLMTIE_B200_NO_TC") != nullptr;
+    return !off && prefill_tc_eligible(p, hd);
+}
+
+// One sequence through the fused prefill kernels.
 static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q, size_t q_len,
                                 const void *k, size_t k_len, const void *v, size_t v_len,
                                 void *out, size_t out_len, size_t tq, size_t past, size_t heads,
@@ -524,7 +532,8 @@ static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q,
     p.q_scale = 1.0f;
     p.sl2 = scale * kLog2e;
     LaunchScope ls(g, name);
-    const cudaError_t e = launch_prefill_mma(g->stream, p, (int)hd);
+    const cudaError_t e = use_tc(p, (int)hd) ? launch_prefill_tc(g->stream, p, g->timeout_flag)
+                                             : launch_prefill_mma(g->stream, p, (int)hd);
     if (e != cudaSuccess) return driver_fail(name, e);
     return ls.done();
 }
@@ -1149,7 +1158,9 @@ extern "C" llmtie_status llmtie_prefill_varlen(
         pp.q_scale = 1.0f;
         pp.sl2 = scale * kLog2e;
         LaunchScope ls(g, "flash_attn_h");
-        const cudaError_t e = launch_prefill_mma(g->stream, pp, (int)head_dim);
+        const cudaError_t e = use_tc(pp, (int)head_dim)
+                                  ? launch_prefill_tc(g->stream, pp, g->timeout_flag)
+                                  : launch_prefill_mma(g->stream, pp, (int)head_dim);
         if (e != cudaSuccess) return driver_fail("flash_attn_h", e);
         const llmtie_status s = ls.done();
         if (s != LLMTIE_OK) return s;

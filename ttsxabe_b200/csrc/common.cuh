@@ -3,6 +3,7 @@
 // launchers each kernel file exports to the C ABI in abi.cu.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -156,6 +157,28 @@ struct PrefillParams {
     float sl2;             // (scale on the scores, else 1) * log2(e)
 };
 cudaError_t launch_prefill_mma(cudaStream_t st, const PrefillParams &p, int hd);
+
+// prefill_tc.cu: the tensor-memory kernel for aligned f16 caches at head_dim 128.
+#define LLMTIE_TC_MAX_SEQ 8
+struct PrefillTcSeq {
+    int row0, tq, past, tk;   // tk: keys the sequence holds (past + tq when causal)
+};
+struct PrefillTcParams {
+    alignas(64) CUtensorMap kmap[LLMTIE_TC_MAX_SEQ];
+    alignas(64) CUtensorMap vmap[LLMTIE_TC_MAX_SEQ];
+    PrefillTcSeq seq[LLMTIE_TC_MAX_SEQ];
+    int nseq;
+    const float *q;
+    long long q_stride;
+    float *out;
+    long long out_stride;
+    int heads, kv_heads, causal;
+    int pair_rows;            // pair two row blocks of one head instead of two heads of a group
+    float q_scale, sl2;
+    int *status;              // set to a site code when a bounded wait gives up
+};
+bool prefill_tc_eligible(const PrefillParams &p, int hd);
+cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int *status);
 
 // rope_cache.cu: packed ragged sequences, RoPE on q (in place) and k (into
 // the f16 K caches), v transposed into the f16 V caches.

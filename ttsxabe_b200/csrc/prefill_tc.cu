@@ -1,0 +1,672 @@
+// Fused prefill attention on the 5th-generation tensor cores: TMA-staged K/V
+// tiles, tcgen05.mma for both products with the accumulators in tensor
+// memory, softmax in registers one thread a query row.
+//
+// Arithmetic is the reference's `flash_attn_impl`
+// (crates/llmtie-cuda/src/kernels.rs:3078-3269): q rounded to f16, scores in
+// f32, logits in log2 units, ex2, the normaliser from un-rounded
+// probabilities, probabilities rounded to f16 into the value product, f32
+// accumulation, O / l at the end. The one liberty is the running maximum: it
+// is only moved when a tile's maximum exceeds it by more than 8 (in log2
+// units), so probabilities are bounded by 2^8 rather than 1 - well inside f16
+// - and the accumulator in tensor memory is rescaled only on those tiles.
+//
+// A block carries two query tiles of 128 rows that share their K/V tiles: two
+// query heads of one KV group at the same positions (grouped models), or two
+// consecutive row blocks of one head (ungrouped). Roles by warp:
+//
+//   warps 0-3   softmax of tile A: thread r owns row r (tensor-memory lane r)
+//   warps 4-7   softmax of tile B
+//   warp  8     TMA producer: K tile [128 keys][128] and V tile [128][128 keys]
+//               per step, two stages each, 128-byte swizzle, no multicast
+//   warps 10-11 idle (they complete the third warpgroup for setmaxnreg)
+//   warp  9     MMA issuer: S_t = Q_t K^T (SS), O_t += P_t V (P from tensor
+//               memory), in the order S_A S_B | PV_A S_A' PV_B S_B' | ... so
+//               that one tile's softmax runs under the other tile's MMAs
+//
+// Tensor memory (512 columns): S_A [0,128) S_B [128,256) O_A [256,384)
+// O_B [384,512); P_t overwrites the first 64 columns of S_t as packed f16.
+// Both caches are K-major as they lie in memory (key rows for Q K^T, rows of
+// the transposed value cache for P V), so both B operands come straight from
+// TMA tiles with no transposition.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records its site
+// in the handle's status word, the block drains and frees its tensor memory,
+// and the host reports LLMTIE_ERR_TIMEOUT.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+constexpr int BM = 128;            // query rows of a tile
+constexpr int BN = 128;            // keys of a step
+constexpr int HD = 128;
+constexpr int kThreads = 384;   // three warpgroups: softmax A, softmax B, {TMA, MMA, idle, idle}
+constexpr int SUB = 128 * 64 * 2;  // one swizzled sub-tile: 128 rows x 64 halves
+constexpr int TILE = 2 * SUB;      // 128 x 128 halves
+constexpr int kSmemBytes = 2 * TILE /*Q*/ + 2 * TILE /*K*/ + 2 * TILE /*V*/ + 1024 /*align*/;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+enum Bar {
+    Q_FULL = 0,    // +t
+    K_FULL = 2,    // +stage
+    K_EMPTY = 4,
+    V_FULL = 6,
+    V_EMPTY = 8,
+    S_FULL = 10,   // +t
+    P_FULL = 12,   // +t
+    O_DONE = 14,   // +t
+    NBARS = 16
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. Returns false once the limit ran out or another role gave
+// up; the caller then leaves its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          int *status, int site)
+{
+    for (uint32_t it = 0; it < kSpinLimit; it++) {
+        if (mbar_try(bar, parity)) return true;
+        if (it > 64) {
+            __nanosleep(32);
+            if ((it & 1023u) == 0 && *abort_flag) return false;
+        }
+    }
+    *abort_flag = 1;
+    atomicExch(status, site);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y, int z)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d),
+        "r"(a), "l"(b), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+// 32 consecutive columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(addr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(addr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_f16(float x0, float x1)
+{
+    return (uint32_t)__half_as_ushort(__float2half_rn(x0)) |
+           ((uint32_t)__half_as_ushort(__float2half_rn(x1)) << 16);
+}
+
+// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled operand
+// whose rows are 128 bytes: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);   // start address
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused when swizzled)
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                    // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                    // 128-byte swizzle
+    return d;
+}
+
+// kind::f16 instruction descriptor: f16 x f16 -> f32, both operands K-major,
+// M = 128, N = 128.
+constexpr uint32_t kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+struct Tile {
+    int head;
+    int r0;
+    int n;   // key tiles it attends to (0: idle)
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bars[NBARS];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag_s;
+    volatile int *abort_flag = &abort_flag_s;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    // ---- which two tiles this block carries ------------------------------------------
+    const PrefillTcSeq sq = p.seq[blockIdx.z];
+    const int group = p.heads / p.kv_heads;
+    const int row_blocks = (sq.tq + BM - 1) / BM;
+    int kh, head_a, head_b, r0_a, r0_b;
+    if (!p.pair_rows) {
+        const int pairs = group >> 1;
+        kh = blockIdx.y / pairs;
+        const int rb = row_blocks - 1 - (int)blockIdx.x;   // longest rows first
+        head_a = kh * group + 2 * (blockIdx.y % pairs);
+        head_b = head_a + 1;
+        r0_a = r0_b = rb * BM;
+    } else {
+        kh = blockIdx.y / group;
+        const int rp = (row_blocks + 1) / 2 - 1 - (int)blockIdx.x;
+        head_a = head_b = blockIdx.y;
+        r0_a = 2 * rp * BM;
+        r0_b = (2 * rp + 1) * BM;
+    }
+    const int all_keys = p.causal ? sq.past + sq.tq : sq.tk;
+    auto tiles_of = [&](int r0) {
+        if (r0 < 0 || r0 >= sq.tq) return 0;
+        const int last = p.causal ? min(sq.past + r0 + BM, all_keys) : all_keys;
+        return (last + BN - 1) / BN;
+    };
+    const int n_a = tiles_of(r0_a), n_b = tiles_of(r0_b);
+    auto n_of = [n_a, n_b](int t) { return t == 0 ? n_a : n_b; };
+    const int n_max = max(n_a, n_b);
+    if (n_max == 0) return;
+
+    // ---- shared memory carve-up (1024-byte aligned for the swizzle) -------------------
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    // Addresses by arithmetic, not tables: a table indexed by a stage or tile
+    // number that is not a compile-time constant would live in local memory.
+    const uint32_t bar0 = smem_u32(&bars[0]);
+    auto BAR = [bar0](int i) { return bar0 + 8u * (uint32_t)i; };
+    auto q_smem = [base](int t) { return base + (uint32_t)t * TILE; };
+    auto k_smem = [base](int s) { return base + (uint32_t)(2 + s) * TILE; };
+    auto v_smem = [base](int s) { return base + (uint32_t)(4 + s) * TILE; };
+    auto s_col = [](int t) { return (uint32_t)t * 128u; };
+    auto o_col = [](int t) { return 256u + (uint32_t)t * 128u; };
+
+    if (tid == 0) {
+        // a block that finds the status word set (an earlier block gave up)
+        // does nothing but allocate and free
+        abort_flag_s = (*(volatile int *)p.status != 0) ? 1 : 0;
+        mbar_init(BAR(Q_FULL + 0), 128);
+        mbar_init(BAR(Q_FULL + 1), 128);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(BAR(K_FULL + s), 1);
+            mbar_init(BAR(K_EMPTY + s), 1);
+            mbar_init(BAR(V_FULL + s), 1);
+            mbar_init(BAR(V_EMPTY + s), 1);
+            mbar_init(BAR(S_FULL + s), 1);
+            mbar_init(BAR(P_FULL + s), 128);
+            mbar_init(BAR(O_DONE + s), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(
+                         smem_u32(&tmem_slot))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const bool dead = abort_flag_s != 0;
+
+    // The register file is split by role: a warp scheduler holds one warp of
+    // each warpgroup, and 232 + 232 + 40 registers fit its 512 per lane.
+    if (warp < 8) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    }
+
+    if (dead) {
+        // nothing: fall through to the drain
+    } else if (warp < 8) {
+        // =========================== softmax warpgroups ===================================
+        const int t = warp >> 2;
+        Tile me;
+        me.head = t == 0 ? head_a : head_b;
+        me.r0 = t == 0 ? r0_a : r0_b;
+        me.n = n_of(t);
+        const int row = tid & 127;                       // query row in the tile = lane
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        if (me.n > 0) {
+            // -- stage Q: f32 rows -> f16, scaled, into the swizzled K-major layout ------
+            {
+                const float *qh = p.q + (long long)sq.row0 * p.q_stride + me.head * HD;
+                const int w = warp & 3;
+                for (int rr = 0; rr < 32; rr++) {
+                    const int r = 32 * w + rr;
+                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (me.r0 + r < sq.tq) {
+                        x = *(const float4 *)(qh + (long long)(me.r0 + r) * p.q_stride + 4 * lane);
+                    }
+                    const uint32_t lo = pack_f16(x.x * p.q_scale, x.y * p.q_scale);
+                    const uint32_t hi = pack_f16(x.z * p.q_scale, x.w * p.q_scale);
+                    const int chunk = (lane & 15) >> 1;
+                    const uint32_t dst = q_smem(t) + (uint32_t)(lane >> 4) * SUB + (uint32_t)r * 128 +
+                                         (uint32_t)((chunk ^ (r & 7)) << 4) + (uint32_t)(lane & 1) * 8;
+                    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(dst), "r"(lo), "r"(hi)
+                                 : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(BAR(Q_FULL + t));
+            }
+
+            const float sl2 = p.sl2;
+            const float thr = 8.0f / sl2;      // how far a tile maximum may exceed the reference
+            float m_ref = -CUDART_INF_F;       // in score units
+            float l = 0.0f;
+            const int my_pos = sq.past + me.r0 + row;   // causal: last key this row sees
+            bool ok = true;
+
+            for (int j = 0; j < me.n && ok; j++) {
+                ok = mbar_wait(BAR(S_FULL + t), (uint32_t)(j & 1), abort_flag, p.status, 10 + t);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t s[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; c++) tmem_ld32(lane_addr + s_col(t) + 32 * c, s[c]);
+                tmem_wait_ld();
+
+                // -- mask the tiles that reach past what this row may see -----------------
+                const int key0 = j * BN;
+                const int lim = (p.causal ? min(my_pos, all_keys - 1) : all_keys - 1) - key0;
+                if (key0 + BN - 1 > (p.causal ? sq.past + me.r0 : all_keys - 1)) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            if (32 * c + i > lim) s[c][i] = __float_as_uint(-CUDART_INF_F);
+                        }
+                    }
+                }
+
+                // -- tile maximum, lazy move of the reference maximum ----------------------
+                float mt = -CUDART_INF_F;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) mt = fmaxf(mt, __uint_as_float(s[c][i]));
+                }
+                if (j == 0) {
+                    m_ref = mt;
+                } else {
+                    const bool move = mt > m_ref + thr;
+                    if (__any_sync(0xffffffffu, move)) {
+                        const float m_new = move ? mt : m_ref;
+                        const float f = ex2((m_ref - m_new) * sl2);
+                        // PV of the previous step is complete (S of this step was
+                        // committed after it), so O may be rescaled in place.
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            uint32_t o[32];
+                            tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; i++) {
+                                o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                            }
+                            tmem_st32(lane_addr + o_col(t) + 32 * c, o);
+                        }
+                        tmem_wait_st();
+                        l *= f;
+                        m_ref = m_new;
+                    }
+                }
+
+                // -- probabilities: l from the un-rounded values, P rounded to f16 -----------
+                const float neg = -m_ref * sl2;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float p0 = ex2(fmaf(__uint_as_float(s[c][2 * i]), sl2, neg));
+                        const float p1 = ex2(fmaf(__uint_as_float(s[c][2 * i + 1]), sl2, neg));
+                        l += p0 + p1;
+                        pk[i] = pack_f16(p0, p1);
+                    }
+                    tmem_st16(lane_addr + s_col(t) + 16 * c, pk);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(BAR(P_FULL + t));
+            }
+
+            // -- epilogue: O / l to global ------------------------------------------------
+            if (ok) ok = mbar_wait(BAR(O_DONE + t), 0u, abort_flag, p.status, 20 + t);
+            if (ok) {
+                tc_fence_after();
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                float *orow = p.out + (long long)(sq.row0 + me.r0 + row) * p.out_stride + me.head * HD;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t o[32];
+                    tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
+                    tmem_wait_ld();
+                    if (me.r0 + row < sq.tq) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            float4 v;
+                            v.x = __uint_as_float(o[4 * i]) * inv;
+                            v.y = __uint_as_float(o[4 * i + 1]) * inv;
+                            v.z = __uint_as_float(o[4 * i + 2]) * inv;
+                            v.w = __uint_as_float(o[4 * i + 3]) * inv;
+                            *(float4 *)(orow + 32 * c + 4 * i) = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    } else if (warp == 8) {
+        // =============================== TMA producer =======================================
+        if (lane == 0) {
+            const CUtensorMap *kmap = &p.kmap[blockIdx.z];
+            const CUtensorMap *vmap = &p.vmap[blockIdx.z];
+            for (int j = 0; j < n_max; j++) {
+                const int s = j & 1;
+                const uint32_t ph = (uint32_t)((j >> 1) & 1);
+                if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1u, abort_flag, p.status, 30)) break;
+                mbar_expect_tx(BAR(K_FULL + s), TILE);
+                tma_load_3d(k_smem(s), kmap, BAR(K_FULL + s), 0, j * BN, kh);
+                tma_load_3d(k_smem(s) + SUB, kmap, BAR(K_FULL + s), 64, j * BN, kh);
+                if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1u, abort_flag, p.status, 31)) break;
+                mbar_expect_tx(BAR(V_FULL + s), TILE);
+                tma_load_3d(v_smem(s), vmap, BAR(V_FULL + s), j * BN, 0, kh);
+                tma_load_3d(v_smem(s) + SUB, vmap, BAR(V_FULL + s), j * BN + 64, 0, kh);
+            }
+        }
+    } else if (warp == 9) {
+        // ================================ MMA issuer =========================================
+        if (lane == 0) {
+            bool ok = true;
+            for (int t = 0; t < 2 && ok; t++) {
+                if (n_of(t) > 0) ok = mbar_wait(BAR(Q_FULL + t), 0u, abort_flag, p.status, 40 + t);
+            }
+            auto issue_s = [&](int t, int stage) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) {
+                    const uint32_t off = (uint32_t)(ks >> 2) * SUB + (uint32_t)(ks & 3) * 32;
+                    mma_ss(tmem + s_col(t), smem_desc(q_smem(t) + off), smem_desc(k_smem(stage) + off),
+                           kIdesc, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(BAR(S_FULL + t));
+            };
+            auto issue_pv = [&](int t, int stage, bool first, bool last) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) {
+                    const uint32_t off = (uint32_t)(ks >> 2) * SUB + (uint32_t)(ks & 3) * 32;
+                    mma_ts(tmem + o_col(t), tmem + s_col(t) + 8 * ks, smem_desc(v_smem(stage) + off),
+                           kIdesc, (first && ks == 0) ? 0u : 1u);
+                }
+                if (last) tc_commit(BAR(O_DONE + t));
+            };
+            if (ok) ok = mbar_wait(BAR(K_FULL + 0), 0u, abort_flag, p.status, 42);
+            if (ok) {
+                tc_fence_after();
+                for (int t = 0; t < 2; t++) {
+                    if (n_of(t) > 0) issue_s(t, 0);
+                }
+                tc_commit(BAR(K_EMPTY + 0));
+            }
+            for (int j = 0; j < n_max && ok; j++) {
+                const int s = j & 1;
+                const uint32_t ph = (uint32_t)((j >> 1) & 1);
+                ok = mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 43);
+                if (!ok) break;
+                if (j + 1 < n_max) {
+                    ok = mbar_wait(BAR(K_FULL + (s ^ 1)), (uint32_t)(((j + 1) >> 1) & 1), abort_flag,
+                                   p.status, 44);
+                    if (!ok) break;
+                }
+                for (int t = 0; t < 2 && ok; t++) {
+                    if (j < n_of(t)) {
+                        ok = mbar_wait(BAR(P_FULL + t), (uint32_t)(j & 1), abort_flag, p.status, 45 + t);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_pv(t, s, j == 0, j == n_of(t) - 1);
+                    }
+                    if (j + 1 < n_of(t)) issue_s(t, s ^ 1);
+                }
+                if (!ok) break;
+                tc_commit(BAR(V_EMPTY + s));
+                if (j + 1 < n_max) tc_commit(BAR(K_EMPTY + (s ^ 1)));
+            }
+        }
+    }
+
+    // ---- drain and free ----------------------------------------------------------------
+    if (*abort_flag) {
+        // Give copies and MMAs still in flight time to land before the shared
+        // and tensor memory go back to the SM.
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                             const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                             const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn()
+{
+    static EncodeFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) !=
+                cudaSuccess ||
+            res != cudaDriverEntryPointSuccess) {
+            ptr = nullptr;
+        }
+        return (EncodeFn)ptr;
+    }();
+    return fn;
+}
+
+// A 3-d map over one cache: `inner` contiguous elements, `rows` rows `row_stride`
+// elements apart, `planes` kv heads `plane_stride` elements apart; tiles of
+// 64 x 128 x 1 with the 128-byte swizzle. Reads past any extent return zero.
+bool encode_map(CUtensorMap *map, const void *basep, uint64_t inner, uint64_t rows, uint64_t planes,
+                uint64_t row_stride, uint64_t plane_stride)
+{
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {inner, rows, planes};
+    const cuuint64_t strides[2] = {row_stride * 2, plane_stride * 2};
+    const cuuint32_t box[3] = {64, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(basep), dims, strides, box,
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+const KernelReg reg_tc("flash_attn_h_tc", (const void *)prefill_tc_kernel);
+
+}  // namespace
+
+bool prefill_tc_eligible(const PrefillParams &p, int hd)
+{
+    if (hd != 128 || p.kv_f32 || p.out_f16) return false;
+    if (p.nseq > LLMTIE_TC_MAX_SEQ) return false;
+    if (((uintptr_t)p.q & 15u) != 0 || (p.q_stride & 3) != 0) return false;
+    if (((uintptr_t)p.out & 15u) != 0 || (p.out_stride & 3) != 0) return false;
+    for (int b = 0; b < p.nseq; b++) {
+        if (p.seq[b].cap % 8 != 0) return false;
+        // short sequences stay with the general kernel (a box wider than the tensor)
+        if ((p.causal ? p.seq[b].past + p.seq[b].tq : p.seq[b].tk) < 128) return false;
+        if (((uintptr_t)p.seq[b].k & 15u) != 0 || ((uintptr_t)p.seq[b].v & 15u) != 0) return false;
+    }
+    return encode_fn() != nullptr;
+}
+
+cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int *status)
+{
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBytes);
+        configured[dev] = true;
+    }
+    PrefillTcParams tp;
+    memset(&tp, 0, sizeof(tp));
+    int max_tq = 0;
+    for (int b = 0; b < p.nseq; b++) {
+        const PrefillSeq &s = p.seq[b];
+        const int live = p.causal ? s.past + s.tq : s.tk;
+        tp.seq[b].row0 = s.row0;
+        tp.seq[b].tq = s.tq;
+        tp.seq[b].past = s.past;
+        tp.seq[b].tk = live;
+        // keys: [kv][cap][hd] -> inner hd, rows = live keys, planes = kv heads
+        if (!encode_map(&tp.kmap[b], s.k, HD, (uint64_t)live, (uint64_t)p.kv_heads, HD,
+                        (uint64_t)s.cap * HD)) {
+            return cudaErrorInvalidValue;
+        }
+        // values: [kv][hd][cap] -> inner = live keys, rows = hd, planes = kv heads
+        if (!encode_map(&tp.vmap[b], s.v, (uint64_t)live, HD, (uint64_t)p.kv_heads,
+                        (uint64_t)s.cap, (uint64_t)s.cap * HD)) {
+            return cudaErrorInvalidValue;
+        }
+        max_tq = s.tq > max_tq ? s.tq : max_tq;
+    }
+    if (max_tq == 0) return cudaSuccess;
+    tp.nseq = p.nseq;
+    tp.q = p.q;
+    tp.q_stride = p.q_stride;
+    tp.out = (float *)p.out;
+    tp.out_stride = p.out_stride;
+    tp.heads = p.heads;
+    tp.kv_heads = p.kv_heads;
+    tp.causal = p.causal;
+    tp.q_scale = p.q_scale;
+    tp.sl2 = p.sl2;
+    tp.status = status;
+    const int group = p.heads / p.kv_heads;
+    tp.pair_rows = (group % 2 != 0) ? 1 : 0;
+    const int row_blocks = (max_tq + BM - 1) / BM;
+    dim3 grid;
+    if (!tp.pair_rows) {
+        grid = dim3(row_blocks, p.kv_heads * (group / 2), p.nseq);
+    } else {
+        grid = dim3((row_blocks + 1) / 2, p.heads, p.nseq);
+    }
+    prefill_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(tp);
+    return cudaGetLastError();
+}
