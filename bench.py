@@ -78,6 +78,9 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 5.0:
+                time.sleep(0.02)   # nvidia-smi takes a moment to deliver its first row
         except Exception:
             self.proc = None
         return self

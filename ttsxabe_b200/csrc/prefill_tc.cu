@@ -205,10 +205,14 @@ __device__ __forceinline__ float ex2(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two floats to packed f16, x0 in the low half: one cvt.rn.f16x2.f32. (Two
+// scalar conversions would each take a slot of the transcendental pipe, which
+// is the pipe this kernel is bound by.)
 __device__ __forceinline__ uint32_t pack_f16(float x0, float x1)
 {
-    return (uint32_t)__half_as_ushort(__float2half_rn(x0)) |
-           ((uint32_t)__half_as_ushort(__float2half_rn(x1)) << 16);
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(x1), "f"(x0));
+    return r;
 }
 
 // Shared-memory matrix descriptor of a K-major, 128-byte-swizzled operand
@@ -252,17 +256,19 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     const int group = p.heads / p.kv_heads;
     const int row_blocks = (sq.tq + BM - 1) / BM;
     int kh, head_a, head_b, r0_a, r0_b;
+    // blockIdx.x runs over the heads (neighbours share a KV head's tiles in L2),
+    // blockIdx.y over the row blocks, longest rows first.
     if (!p.pair_rows) {
         const int pairs = group >> 1;
-        kh = blockIdx.y / pairs;
-        const int rb = row_blocks - 1 - (int)blockIdx.x;   // longest rows first
-        head_a = kh * group + 2 * (blockIdx.y % pairs);
+        kh = blockIdx.x / pairs;
+        const int rb = row_blocks - 1 - (int)blockIdx.y;
+        head_a = kh * group + 2 * (blockIdx.x % pairs);
         head_b = head_a + 1;
         r0_a = r0_b = rb * BM;
     } else {
-        kh = blockIdx.y / group;
-        const int rp = (row_blocks + 1) / 2 - 1 - (int)blockIdx.x;
-        head_a = head_b = blockIdx.y;
+        kh = blockIdx.x / group;
+        const int rp = (row_blocks + 1) / 2 - 1 - (int)blockIdx.y;
+        head_a = head_b = blockIdx.x;
         r0_a = 2 * rp * BM;
         r0_b = (2 * rp + 1) * BM;
     }
@@ -390,12 +396,16 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 }
 
                 // -- tile maximum, lazy move of the reference maximum ----------------------
-                float mt = -CUDART_INF_F;
+                // four independent chains: one 128-long chain of dependent
+                // maxima would cost more than the exponentials
+                float mc[4];
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
+                    mc[c] = __uint_as_float(s[c][0]);
 #pragma unroll
-                    for (int i = 0; i < 32; i++) mt = fmaxf(mt, __uint_as_float(s[c][i]));
+                    for (int i = 1; i < 32; i++) mc[c] = fmaxf(mc[c], __uint_as_float(s[c][i]));
                 }
+                const float mt = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
                 if (j == 0) {
                     m_ref = mt;
                 } else {
@@ -424,6 +434,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
 
                 // -- probabilities: l from the un-rounded values, P rounded to f16 -----------
                 const float neg = -m_ref * sl2;
+                float lc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     uint32_t pk[16];
@@ -431,11 +442,12 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                     for (int i = 0; i < 16; i++) {
                         const float p0 = ex2(fmaf(__uint_as_float(s[c][2 * i]), sl2, neg));
                         const float p1 = ex2(fmaf(__uint_as_float(s[c][2 * i + 1]), sl2, neg));
-                        l += p0 + p1;
+                        lc[i & 3] += p0 + p1;
                         pk[i] = pack_f16(p0, p1);
                     }
                     tmem_st16(lane_addr + s_col(t) + 16 * c, pk);
                 }
+                l += (lc[0] + lc[1]) + (lc[2] + lc[3]);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(BAR(P_FULL + t));
@@ -523,11 +535,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
                 ok = mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 43);
                 if (!ok) break;
-                if (j + 1 < n_max) {
-                    ok = mbar_wait(BAR(K_FULL + (s ^ 1)), (uint32_t)(((j + 1) >> 1) & 1), abort_flag,
-                                   p.status, 44);
-                    if (!ok) break;
-                }
+                bool k_ready = false;
                 for (int t = 0; t < 2 && ok; t++) {
                     if (j < n_of(t)) {
                         ok = mbar_wait(BAR(P_FULL + t), (uint32_t)(j & 1), abort_flag, p.status, 45 + t);
@@ -535,7 +543,16 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         tc_fence_after();
                         issue_pv(t, s, j == 0, j == n_of(t) - 1);
                     }
-                    if (j + 1 < n_of(t)) issue_s(t, s ^ 1);
+                    if (j + 1 < n_of(t)) {
+                        if (!k_ready) {
+                            ok = mbar_wait(BAR(K_FULL + (s ^ 1)), (uint32_t)(((j + 1) >> 1) & 1),
+                                           abort_flag, p.status, 44);
+                            if (!ok) break;
+                            tc_fence_after();
+                            k_ready = true;
+                        }
+                        issue_s(t, s ^ 1);
+                    }
                 }
                 if (!ok) break;
                 tc_commit(BAR(V_EMPTY + s));
@@ -663,9 +680,9 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int *stat
     const int row_blocks = (max_tq + BM - 1) / BM;
     dim3 grid;
     if (!tp.pair_rows) {
-        grid = dim3(row_blocks, p.kv_heads * (group / 2), p.nseq);
+        grid = dim3(p.kv_heads * (group / 2), row_blocks, p.nseq);
     } else {
-        grid = dim3((row_blocks + 1) / 2, p.heads, p.nseq);
+        grid = dim3(p.heads, (row_blocks + 1) / 2, p.nseq);
     }
     prefill_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(tp);
     return cudaGetLastError();
