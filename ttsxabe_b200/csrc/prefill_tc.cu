@@ -38,6 +38,7 @@
 #include "common.cuh"
 
 #include <math_constants.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -48,7 +49,7 @@ constexpr int kThreads = 384;   // three warpgroups: softmax A, softmax B, {TMA,
 constexpr int SUB = 128 * 64 * 2;  // one swizzled sub-tile: 128 rows x 64 halves
 constexpr int TILE = 2 * SUB;      // 128 x 128 halves
 constexpr int kSmemBytes = 2 * TILE /*Q*/ + 2 * TILE /*K*/ + 2 * TILE /*V*/ + 1024 /*align*/;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr long long kWaitCycles = 1ll << 31;   // about a second
 
 enum Bar {
     Q_FULL = 0,    // +t
@@ -88,7 +89,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
@@ -97,16 +98,22 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait. Returns false once the limit ran out or another role gave
-// up; the caller then leaves its loop.
+// Bounded wait: a plain poll of the barrier's phase with no sleep of its own
+// (nanosleep's granularity is far coarser than the few hundred nanoseconds a
+// pipeline step lasts). The bound is a deadline in
+// SM cycles, checked every 256 polls together with the block's abort flag.
+// Returns false once the deadline passed or another role gave up; the caller
+// then leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           int *status, int site)
 {
-    for (uint32_t it = 0; it < kSpinLimit; it++) {
+    if (mbar_try(bar, parity)) return true;
+    const long long start = clock64();
+    for (uint32_t it = 1;; it++) {
         if (mbar_try(bar, parity)) return true;
-        if (it > 64) {
-            __nanosleep(32);
-            if ((it & 1023u) == 0 && *abort_flag) return false;
+        if ((it & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - start > kWaitCycles) break;
         }
     }
     *abort_flag = 1;
@@ -205,6 +212,38 @@ __device__ __forceinline__ float ex2(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Three-input maximum and the packed two-float FMA / add of this architecture:
+// the softmax is bound by how many instructions one warp per scheduler can
+// issue, so each of these halves a part of its stream.
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi)
+{
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // Two floats to packed f16, x0 in the low half: one cvt.rn.f16x2.f32. (Two
 // scalar conversions would each take a slot of the transcendental pipe, which
 // is the pipe this kernel is bound by.)
@@ -299,15 +338,16 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
         // a block that finds the status word set (an earlier block gave up)
         // does nothing but allocate and free
         abort_flag_s = (*(volatile int *)p.status != 0) ? 1 : 0;
-        mbar_init(BAR(Q_FULL + 0), 128);
-        mbar_init(BAR(Q_FULL + 1), 128);
+        // the softmax warpgroups arrive once per warp (lane 0 after a __syncwarp)
+        mbar_init(BAR(Q_FULL + 0), 4);
+        mbar_init(BAR(Q_FULL + 1), 4);
         for (int s = 0; s < 2; s++) {
             mbar_init(BAR(K_FULL + s), 1);
             mbar_init(BAR(K_EMPTY + s), 1);
             mbar_init(BAR(V_FULL + s), 1);
             mbar_init(BAR(V_EMPTY + s), 1);
             mbar_init(BAR(S_FULL + s), 1);
-            mbar_init(BAR(P_FULL + s), 128);
+            mbar_init(BAR(P_FULL + s), 4);
             mbar_init(BAR(O_DONE + s), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -325,11 +365,11 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     const bool dead = abort_flag_s != 0;
 
     // The register file is split by role: a warp scheduler holds one warp of
-    // each warpgroup, and 232 + 232 + 40 registers fit its 512 per lane.
+    // each warpgroup, and 208 + 208 + 88 registers are the 3 x 168 per lane the block was launched with (asking for more would wait forever).
     if (warp < 8) {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     } else {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
     }
 
     if (dead) {
@@ -348,22 +388,36 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             {
                 const float *qh = p.q + (long long)sq.row0 * p.q_stride + me.head * HD;
                 const int w = warp & 3;
-                for (int rr = 0; rr < 32; rr++) {
-                    const int r = 32 * w + rr;
-                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (me.r0 + r < sq.tq) {
-                        x = *(const float4 *)(qh + (long long)(me.r0 + r) * p.q_stride + 4 * lane);
+                // eight rows of loads in flight at a time: one load per
+                // iteration would serialise 32 global-memory latencies
+#pragma unroll
+                for (int rr0 = 0; rr0 < 32; rr0 += 8) {
+                    float4 x[8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int r = 32 * w + rr0 + u;
+                        x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (me.r0 + r < sq.tq) {
+                            x[u] = __ldg((const float4 *)(qh + (long long)(me.r0 + r) * p.q_stride +
+                                                          4 * lane));
+                        }
                     }
-                    const uint32_t lo = pack_f16(x.x * p.q_scale, x.y * p.q_scale);
-                    const uint32_t hi = pack_f16(x.z * p.q_scale, x.w * p.q_scale);
-                    const int chunk = (lane & 15) >> 1;
-                    const uint32_t dst = q_smem(t) + (uint32_t)(lane >> 4) * SUB + (uint32_t)r * 128 +
-                                         (uint32_t)((chunk ^ (r & 7)) << 4) + (uint32_t)(lane & 1) * 8;
-                    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(dst), "r"(lo), "r"(hi)
-                                 : "memory");
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int r = 32 * w + rr0 + u;
+                        const uint32_t lo = pack_f16(x[u].x * p.q_scale, x[u].y * p.q_scale);
+                        const uint32_t hi = pack_f16(x[u].z * p.q_scale, x[u].w * p.q_scale);
+                        const int chunk = (lane & 15) >> 1;
+                        const uint32_t dst = q_smem(t) + (uint32_t)(lane >> 4) * SUB +
+                                             (uint32_t)r * 128 + (uint32_t)((chunk ^ (r & 7)) << 4) +
+                                             (uint32_t)(lane & 1) * 8;
+                        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(dst), "r"(lo), "r"(hi)
+                                     : "memory");
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(BAR(Q_FULL + t));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(Q_FULL + t));
             }
 
             const float sl2 = p.sl2;
@@ -401,9 +455,11 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 float mc[4];
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
-                    mc[c] = __uint_as_float(s[c][0]);
+                    mc[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]));
 #pragma unroll
-                    for (int i = 1; i < 32; i++) mc[c] = fmaxf(mc[c], __uint_as_float(s[c][i]));
+                    for (int i = 2; i < 32; i += 2) {
+                        mc[c] = max3(mc[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+                    }
                 }
                 const float mt = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
                 if (j == 0) {
@@ -433,24 +489,36 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 }
 
                 // -- probabilities: l from the un-rounded values, P rounded to f16 -----------
-                const float neg = -m_ref * sl2;
-                float lc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const uint64_t sl2_2 = pack2(sl2, sl2);
+                const uint64_t neg_2 = pack2(-m_ref * sl2, -m_ref * sl2);
+                uint64_t lc[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of partial sums
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
-                        const float p0 = ex2(fmaf(__uint_as_float(s[c][2 * i]), sl2, neg));
-                        const float p1 = ex2(fmaf(__uint_as_float(s[c][2 * i + 1]), sl2, neg));
-                        lc[i & 3] += p0 + p1;
+                        const uint64_t x = fma2(pack2(__uint_as_float(s[c][2 * i]),
+                                                      __uint_as_float(s[c][2 * i + 1])),
+                                                sl2_2, neg_2);
+                        float p0, p1;
+                        unpack2(x, p0, p1);
+                        p0 = ex2(p0);
+                        p1 = ex2(p1);
+                        lc[i & 3] = add2(lc[i & 3], pack2(p0, p1));
                         pk[i] = pack_f16(p0, p1);
                     }
                     tmem_st16(lane_addr + s_col(t) + 16 * c, pk);
                 }
-                l += (lc[0] + lc[1]) + (lc[2] + lc[3]);
+                {
+                    float a0, a1, b0, b1;
+                    unpack2(add2(lc[0], lc[1]), a0, a1);
+                    unpack2(add2(lc[2], lc[3]), b0, b1);
+                    l += (a0 + a1) + (b0 + b1);
+                }
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(BAR(P_FULL + t));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(P_FULL + t));
             }
 
             // -- epilogue: O / l to global ------------------------------------------------
@@ -504,21 +572,28 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             for (int t = 0; t < 2 && ok; t++) {
                 if (n_of(t) > 0) ok = mbar_wait(BAR(Q_FULL + t), 0u, abort_flag, p.status, 40 + t);
             }
+            // Descriptors are built once; a k-step of 16 halves (32 bytes) adds 2
+            // to the start-address field, the second 64-wide sub-tile SUB >> 4.
+            const uint64_t dq0 = smem_desc(q_smem(0)), dk0 = smem_desc(k_smem(0)),
+                           dv0 = smem_desc(v_smem(0));
+            constexpr uint64_t kTileStep = TILE >> 4, kSubStep = SUB >> 4;
             auto issue_s = [&](int t, int stage) {
+                const uint64_t a = dq0 + (uint64_t)t * kTileStep;
+                const uint64_t b = dk0 + (uint64_t)stage * kTileStep;
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
-                    const uint32_t off = (uint32_t)(ks >> 2) * SUB + (uint32_t)(ks & 3) * 32;
-                    mma_ss(tmem + s_col(t), smem_desc(q_smem(t) + off), smem_desc(k_smem(stage) + off),
-                           kIdesc, ks > 0 ? 1u : 0u);
+                    const uint64_t off = (uint64_t)(ks >> 2) * kSubStep + (uint64_t)(ks & 3) * 2;
+                    mma_ss(tmem + s_col(t), a + off, b + off, kIdesc, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(BAR(S_FULL + t));
             };
             auto issue_pv = [&](int t, int stage, bool first, bool last) {
+                const uint64_t b = dv0 + (uint64_t)stage * kTileStep;
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
-                    const uint32_t off = (uint32_t)(ks >> 2) * SUB + (uint32_t)(ks & 3) * 32;
-                    mma_ts(tmem + o_col(t), tmem + s_col(t) + 8 * ks, smem_desc(v_smem(stage) + off),
-                           kIdesc, (first && ks == 0) ? 0u : 1u);
+                    const uint64_t off = (uint64_t)(ks >> 2) * kSubStep + (uint64_t)(ks & 3) * 2;
+                    mma_ts(tmem + o_col(t), tmem + s_col(t) + 8 * ks, b + off, kIdesc,
+                           (first && ks == 0) ? 0u : 1u);
                 }
                 if (last) tc_commit(BAR(O_DONE + t));
             };
