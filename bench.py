@@ -40,10 +40,14 @@ SCALE = float(np.float32(HD) ** np.float32(-0.5))
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1590.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant
-# kernel, from the ncu captures summarised under profiles/ (None: not captured).
+# DRAM traffic of the dominant kernel from the ncu captures summarised under
+# profiles/. The decode entry is dram__bytes_read.sum + dram__bytes_write.sum
+# per algorithmic byte, captured on a batch 8 x 16384-key launch (537.30 MB read
+# + 5.59 MB written for 536.87 MB of KV) and scaled to the launch at hand, since
+# traffic grows in proportion to the keys streamed; a full-size launch is too
+# large to capture.
 NCU_TRAFFIC = {
-    "decode128k": None,
+    "decode128k": (537.295e6 + 5.589e6) / 536.870912e6,
     "prefill8k": None,
 }
 
@@ -213,14 +217,25 @@ def decode128k(args, world, rank, local):
                               SCALE)
     gpu.synchronize()
 
+    # Kernels of ours per step: the attention kernel, and the merge when sharded.
     launches0 = gpu.launch_count()
-    with ClockSampler(local) as clocks:
-        secs = time_steps(gpu, lambda: sd.decode(q), args.steps, args.warmup)
-    launches = gpu.launch_count() - launches0 - (args.warmup * (1 if world == 1 else 2))
-    clk = clocks.summary()
+    sd.decode(q)
+    per_step = gpu.launch_count() - launches0
+    step = lambda: sd.decode(q)
+    if world > 1 and not args.no_graph:
+        # At 8 GPUs a step is ~100 us of device work behind three host calls;
+        # replaying it as a CUDA graph keeps the host out of the timed region.
+        graph, _ = sd.capture(q)
+        def step():
+            with torch.cuda.stream(gpu.stream):
+                graph.replay()
+    clocks = ClockSampler(local)
+    clocks.__enter__()
+    secs = time_steps(gpu, step, args.steps, args.warmup)
+    launches = per_step * args.steps
 
     # the attention kernel alone (what the roofline is about)
-    ksecs = time_steps(gpu, lambda: sd.partial_fn(q, world > 1), args.steps, 1)
+    ksecs = time_steps(gpu, lambda: sd.partial_fn(q, world > 1), args.steps, 3)
 
     kv_bytes_total = batch * 2 * KV_HEADS * ctx * HD * 2      # the reference's count
     kv_bytes_rank = batch * 2 * KV_HEADS * tk * HD * 2
@@ -256,6 +271,8 @@ def decode128k(args, world, rank, local):
         e2e_step()
     barrier_sync(gpu)
     e2e_secs = max_over_ranks((time.perf_counter() - w0), gpu.device) / args.steps
+    clocks.__exit__()
+    clk = clocks.summary()
 
     hbm, _, which = measured_peaks()
     per_step = secs / args.steps
@@ -292,13 +309,15 @@ def decode128k(args, world, rank, local):
             "d2h_bytes_per_step": batch * nq * esz,
         },
         "gpu_launches": int(launches),
+        "cuda_graph": bool(world > 1 and not args.no_graph),
         "roofline": {
             "bound": "hbm",
             "achieved": achieved,
             "peak": hbm,
             "unit": "GB/s",
             "frac": achieved / hbm,
-            "traffic": NCU_TRAFFIC["decode128k"],
+            "traffic": (None if NCU_TRAFFIC["decode128k"] is None
+                        else NCU_TRAFFIC["decode128k"] * kv_bytes_rank),
             "peak_source": "of " + which,
             "kernel": "decode_f16_kernel<128>",
             "kernel_ms": ksecs / args.steps * 1e3,
@@ -368,6 +387,121 @@ def prefill8k(args, world, rank, local):
                      "peak_source": "of " + which,
                      "frac_of_nominal_2250": achieved / 2250.0},
     }
+    return gpu, line
+
+
+def graph_time(gpu, fn, reps: int = 20, rounds: int = 5) -> float:
+    """Device seconds per call of fn: `reps` calls recorded into one CUDA graph
+    on the handle's stream and the graph replayed, so that host launch cost
+    does not hide microsecond kernels. Median of `rounds` replays."""
+    import torch
+
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=gpu.stream):
+        for _ in range(reps):
+            fn()
+    times = []
+    with torch.cuda.stream(gpu.stream):
+        graph.replay()
+        for _ in range(rounds):
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) / 1e3 / reps)
+    return float(np.median(times))
+
+
+def other_configs(args, world, rank, local):
+    """The remaining benchmark configs on one GPU, device time per call
+    (graph-replayed): config 1 and 2 prefill, config 3 decode at batch 1 and
+    16, config 4 Whisper encoder and cross-attention. Parity for each is in
+    tests/; this only times them."""
+    import torch
+
+    from ttsxabe_b200 import DecodeScratch, Gpu
+
+    gpu = Gpu.open(local)
+    hbm, tf, which = measured_peaks()
+    res = {}
+    rng = np.random.default_rng(0)
+
+    def randn(n):
+        with torch.cuda.stream(gpu.stream):
+            return torch.randn(n, device=gpu.device).to(torch.float16).to(torch.float32)
+
+    # config 1 / 2: ragged causal prefill with RoPE and the cache write
+    for name, lens in (("config1_prefill_128", [128]),
+                       ("config2_prefill_8x[256,512]", list(rng.integers(256, 513, size=8)))):
+        total = int(sum(lens))
+        cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        cap = 512
+        q, k, v = randn(total * HEADS * HD), randn(total * KV_HEADS * HD), randn(total * KV_HEADS * HD)
+        kcs = [gpu.zeros_f16(KV_HEADS * cap * HD) for _ in lens]
+        vcs = [gpu.zeros_f16(KV_HEADS * cap * HD) for _ in lens]
+        out = gpu.uninit(total * HEADS * HD)
+        fn = lambda: gpu.prefill_varlen(q, k, v, cu, kcs, vcs, [0] * len(lens), [cap] * len(lens),
+                                        None, HEADS, KV_HEADS, HD, 10000.0, SCALE, out=out)
+        t = graph_time(gpu, fn)
+        flops = 4.0 * HD * HEADS * sum(L * (L + 1) / 2 for L in lens)
+        res[name] = {"us": t * 1e6, "tflops": flops / t / 1e12, "tokens_per_s": total / t,
+                     "frac_of_tensor_peak": flops / t / 1e12 / tf}
+
+    # config 3: one query per sequence, context in [2048, 4096]
+    for batch in (1, 16):
+        tks = [int(x) for x in rng.integers(2048, 4097, size=batch)]
+        cap = 4096
+        ks = [device_normal_f16(gpu, KV_HEADS * cap * HD, 10 + b) for b in range(batch)]
+        vs = [device_normal_f16(gpu, KV_HEADS * cap * HD, 50 + b) for b in range(batch)]
+        q = randn(batch * HEADS * HD)
+        out = gpu.uninit(batch * HEADS * HD)
+        sc = DecodeScratch()
+        fn = lambda: gpu.decode_batched(q, ks, vs, tks, [cap] * batch, HEADS, KV_HEADS, HD, SCALE,
+                                        False, sc, out=out)
+        t = graph_time(gpu, fn)
+        byts = sum(2 * KV_HEADS * tk * HD * 2 for tk in tks)
+        res["config3_decode_batch%d" % batch] = {
+            "us": t * 1e6, "gbs": byts / t / 1e9, "tokens_per_s": batch / t,
+            "frac_of_hbm_peak": byts / t / 1e9 / hbm}
+
+    # config 4: Whisper large-v2 shapes
+    wh, whd, wt = 20, 64, 1500
+    d = wh * whd
+    for batch in (1, 8):
+        qkvs = [randn(wt * 3 * d) for _ in range(batch)]
+        work = gpu._empty(gpu._lib.llmtie_flash_rows_work_bytes(wt, wh, whd) // 2, torch.float16)
+        outs = [gpu._empty(wt * d, torch.float16) for _ in range(batch)]
+
+        def fn():   # the reference has no batch dimension here: one call per utterance
+            for b in range(batch):
+                gpu._lib.llmtie_flash_attn_rows(gpu._h, qkvs[b].data_ptr(), qkvs[b].numel(),
+                                                outs[b].data_ptr(), outs[b].numel(), wt, wh, whd,
+                                                0.125, work.data_ptr(), work.numel() * 2)
+        t = graph_time(gpu, fn, reps=5)
+        flops = batch * 4.0 * whd * wh * wt * wt
+        res["config4_encoder_batch%d" % batch] = {"us": t * 1e6, "tflops": flops / t / 1e12,
+                                                  "frac_of_tensor_peak": flops / t / 1e12 / tf}
+    kc = device_normal_f16(gpu, wh * wt * whd, 3)
+    vc = device_normal_f16(gpu, wh * wt * whd, 4)
+    sc = DecodeScratch()
+    for n in (1, 8, 32):
+        q = randn(n * d)
+        out = gpu.uninit(n * d)
+        fn = lambda: gpu._lib.llmtie_cross_attn(gpu._h, q.data_ptr(), q.numel(), kc.data_ptr(),
+                                                kc.numel(), vc.data_ptr(), vc.numel(), n, wh, whd,
+                                                wt, wt, 0.125, sc._bind(gpu), out.data_ptr(),
+                                                out.numel())
+        t = graph_time(gpu, fn)
+        byts = 2 * wh * wt * whd * 2
+        res["config4_cross_n%d" % n] = {"us": t * 1e6, "gbs": byts / t / 1e9}
+    line = {"metric": "per-config device time", "unit": "us", "n_gpus": 1, "data": "synthetic",
+            "timing": "CUDA-graph replay, median of 5", "peaks": {"hbm_gbs": hbm, "tflops": tf,
+                                                                  "source": which},
+            "configs": res}
     return gpu, line
 
 
@@ -445,11 +579,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode128k", choices=["decode128k", "prefill8k"])
+    ap.add_argument("--workload", default="decode128k",
+                    choices=["decode128k", "prefill8k", "configs"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=131072)
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time the sharded step as separate host calls, not a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -458,7 +595,8 @@ def main():
         return
 
     world, rank, local = dist_setup(args.gpus)
-    fn = decode128k if args.workload == "decode128k" else prefill8k
+    fn = {"decode128k": decode128k, "prefill8k": prefill8k, "configs": other_configs}[
+        args.workload]
     gpu, line = fn(args, world, rank, local)
     if rank == 0:
         if world == 1 and not args.no_cpu and args.workload == "decode128k":

@@ -532,7 +532,7 @@ static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q,
     p.q_scale = 1.0f;
     p.sl2 = scale * kLog2e;
     LaunchScope ls(g, name);
-    const cudaError_t e = use_tc(p, (int)hd) ? launch_prefill_tc(g->stream, p, g->timeout_flag)
+    const cudaError_t e = use_tc(p, (int)hd) ? launch_prefill_tc(g->stream, p, (int)hd, g->timeout_flag)
                                              : launch_prefill_mma(g->stream, p, (int)hd);
     if (e != cudaSuccess) return driver_fail(name, e);
     return ls.done();
@@ -639,7 +639,8 @@ extern "C" llmtie_status llmtie_flash_attn_rows(llmtie_gpu *g, const float *qkv,
         p.q_scale = scale;   // on q before it is rounded, as the encoder does
         p.sl2 = kLog2e;
         LaunchScope ls(g, "flash_attn_64_rows");
-        const cudaError_t e = launch_prefill_mma(g->stream, p, 64);
+        const cudaError_t e = use_tc(p, 64) ? launch_prefill_tc(g->stream, p, 64, g->timeout_flag)
+                                            : launch_prefill_mma(g->stream, p, 64);
         st = (e != cudaSuccess) ? driver_fail("flash_attn_64_rows", e) : ls.done();
     }
     if (own) llmtie_free(g, own);
@@ -1159,7 +1160,7 @@ extern "C" llmtie_status llmtie_prefill_varlen(
         pp.sl2 = scale * kLog2e;
         LaunchScope ls(g, "flash_attn_h");
         const cudaError_t e = use_tc(pp, (int)head_dim)
-                                  ? launch_prefill_tc(g->stream, pp, g->timeout_flag)
+                                  ? launch_prefill_tc(g->stream, pp, (int)head_dim, g->timeout_flag)
                                   : launch_prefill_mma(g->stream, pp, (int)head_dim);
         if (e != cudaSuccess) return driver_fail("flash_attn_h", e);
         const llmtie_status s = ls.done();

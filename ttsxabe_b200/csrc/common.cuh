@@ -158,7 +158,7 @@ struct PrefillParams {
 };
 cudaError_t launch_prefill_mma(cudaStream_t st, const PrefillParams &p, int hd);
 
-// prefill_tc.cu: the tensor-memory kernel for aligned f16 caches at head_dim 128.
+// prefill_tc.cu: the tensor-memory kernel for aligned f16 caches at head_dim 64 or 128.
 #define LLMTIE_TC_MAX_SEQ 8
 struct PrefillTcSeq {
     int row0, tq, past, tk;   // tk: keys the sequence holds (past + tq when causal)
@@ -170,15 +170,16 @@ struct PrefillTcParams {
     int nseq;
     const float *q;
     long long q_stride;
-    float *out;
+    void *out;                // f32, or f16 when out_f16
     long long out_stride;
+    int out_f16;
     int heads, kv_heads, causal;
     int pair_rows;            // pair two row blocks of one head instead of two heads of a group
     float q_scale, sl2;
     int *status;              // set to a site code when a bounded wait gives up
 };
 bool prefill_tc_eligible(const PrefillParams &p, int hd);
-cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int *status);
+cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, int *status);
 
 // rope_cache.cu: packed ragged sequences, RoPE on q (in place) and k (into
 // the f16 K caches), v transposed into the f16 V caches.

@@ -49,12 +49,10 @@ __device__ __forceinline__ void ldg64(uint32_t &r0, uint32_t &r1, const void *p)
     asm("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "l"(p));
 }
 
-__device__ __forceinline__ float ldcg(const float *p)
-{
-    float v;
-    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
-    return v;
-}
+// A load that bypasses L1 (the partials were written by other blocks). Not
+// volatile on purpose: the merge issues many of these and they must be free
+// to overlap; the fence and barrier before the merge keep them in place.
+__device__ __forceinline__ float ldcg(const float *p) { return __ldcg(p); }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1)

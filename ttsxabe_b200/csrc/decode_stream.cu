@@ -60,12 +60,10 @@ __device__ __forceinline__ void lds128(uint32_t (&r)[4], const void *smem)
                  : "r"(a));
 }
 
-__device__ __forceinline__ float ldcg(const float *p)
-{
-    float v;
-    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
-    return v;
-}
+// A load that bypasses L1 (the partials were written by other blocks). Not
+// volatile on purpose: the merge issues many of these and they must be free
+// to overlap; the fence and barrier before the merge keep them in place.
+__device__ __forceinline__ float ldcg(const float *p) { return __ldcg(p); }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1)
@@ -387,6 +385,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                 __threadfence();
                 if (tid < rows_here) {
                     float M = -CUDART_INF_F;
+#pragma unroll 4
                     for (int cc = c_first; cc <= c_last; cc++) {
                         const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
                         const float *pr =
@@ -396,28 +395,44 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                     sm_M[tid] = M;
                 }
                 __syncthreads();
-                for (int idx = tid; idx < rows_here * HD; idx += kThreads) {
-                    const int row = idx / HD, d = idx % HD;
+                // Each thread owns column tid of every row, and a row's loads are
+                // all issued before any is used: the merge costs a trip to L2
+                // per eight partials rather than one per value.
+                for (int row = 0; row < rows_here; row++) {
                     const float M = sm_M[row];
                     float O = 0.0f, L = 0.0f;
-                    for (int cc = c_first; cc <= c_last; cc++) {
-                        const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
-                        const float *pr =
-                            p.part + (((size_t)cc * 2 + sl) * kRows + row) * (HD + 2);
-                        const float mi = ldcg(pr + HD);
-                        const float f = (mi == -CUDART_INF_F) ? 0.0f : ex2(mi - M);
-                        O += f * ldcg(pr + d);
-                        L += f * ldcg(pr + HD + 1);
-                    }
-                    float *orow = orow0 + (long long)row * p.out_row;
-                    if (p.partial) {
-                        orow[d] = O;
-                        if (d == 0) {
-                            orow[HD] = M * kLn2;
-                            orow[HD + 1] = L;
+                    for (int c0 = c_first; c0 <= c_last; c0 += 8) {
+                        float mi[8], oi[8], li[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            const int cc = min(c0 + e, c_last);
+                            const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
+                            const float *pr =
+                                p.part + (((size_t)cc * 2 + sl) * kRows + row) * (HD + 2);
+                            mi[e] = ldcg(pr + HD);
+                            li[e] = ldcg(pr + HD + 1);
+                            oi[e] = ldcg(pr + tid % HD);
                         }
-                    } else {
-                        orow[d] = L > 0.0f ? O / L : 0.0f;
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            if (c0 + e <= c_last) {
+                                const float f = (mi[e] == -CUDART_INF_F) ? 0.0f : ex2(mi[e] - M);
+                                O += f * oi[e];
+                                L += f * li[e];
+                            }
+                        }
+                    }
+                    if (tid < HD) {
+                        float *orow = orow0 + (long long)row * p.out_row;
+                        if (p.partial) {
+                            orow[tid] = O;
+                            if (tid == 0) {
+                                orow[HD] = M * kLn2;
+                                orow[HD + 1] = L;
+                            }
+                        } else {
+                            orow[tid] = L > 0.0f ? O / L : 0.0f;
+                        }
                     }
                 }
                 if (tid == 0) p.ctr[pair] = 0u;   // at rest again for the next call

@@ -44,11 +44,20 @@ namespace {
 
 constexpr int BM = 128;            // query rows of a tile
 constexpr int BN = 128;            // keys of a step
-constexpr int HD = 128;
 constexpr int kThreads = 384;   // three warpgroups: softmax A, softmax B, {TMA, MMA, idle, idle}
-constexpr int SUB = 128 * 64 * 2;  // one swizzled sub-tile: 128 rows x 64 halves
-constexpr int TILE = 2 * SUB;      // 128 x 128 halves
-constexpr int kSmemBytes = 2 * TILE /*Q*/ + 2 * TILE /*K*/ + 2 * TILE /*V*/ + 1024 /*align*/;
+constexpr int SUB = 128 * 64 * 2;  // a swizzled Q or K sub-tile: 128 rows x 64 halves
+
+// Shared-memory geometry at head width HD. Q and K tiles are [128][HD] in
+// HD/64 sub-tiles of 128 x 64 halves; a V tile is [HD][128 keys] in two
+// sub-tiles of HD x 64 halves.
+template <int HD>
+struct Geo {
+    static constexpr int KT = HD / 64;
+    static constexpr int TILE_QK = KT * SUB;
+    static constexpr int SUBV = HD * 64 * 2;
+    static constexpr int TILE_V = 2 * SUBV;
+    static constexpr int SMEM = 2 * TILE_QK + 2 * TILE_QK + 2 * TILE_V + 1024;
+};
 constexpr long long kWaitCycles = 1ll << 31;   // about a second
 
 enum Bar {
@@ -268,8 +277,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
 }
 
 // kind::f16 instruction descriptor: f16 x f16 -> f32, both operands K-major,
-// M = 128, N = 128.
-constexpr uint32_t kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// M = 128, N = n.
+__host__ __device__ constexpr uint32_t idesc_n(uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
 
 struct Tile {
     int head;
@@ -277,9 +286,12 @@ struct Tile {
     int n;   // key tiles it attends to (0: idle)
 };
 
+template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
 {
+    using G = Geo<HD>;
+    constexpr int TILE_QK = G::TILE_QK, TILE_V = G::TILE_V, SUBV = G::SUBV, KT = G::KT;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bars[NBARS];
     __shared__ uint32_t tmem_slot;
@@ -328,9 +340,9 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     // number that is not a compile-time constant would live in local memory.
     const uint32_t bar0 = smem_u32(&bars[0]);
     auto BAR = [bar0](int i) { return bar0 + 8u * (uint32_t)i; };
-    auto q_smem = [base](int t) { return base + (uint32_t)t * TILE; };
-    auto k_smem = [base](int s) { return base + (uint32_t)(2 + s) * TILE; };
-    auto v_smem = [base](int s) { return base + (uint32_t)(4 + s) * TILE; };
+    auto q_smem = [base](int t) { return base + (uint32_t)t * TILE_QK; };
+    auto k_smem = [base](int s) { return base + (uint32_t)(2 + s) * TILE_QK; };
+    auto v_smem = [base](int s) { return base + (uint32_t)(4 * TILE_QK) + (uint32_t)s * TILE_V; };
     auto s_col = [](int t) { return (uint32_t)t * 128u; };
     auto o_col = [](int t) { return 256u + (uint32_t)t * 128u; };
 
@@ -388,29 +400,33 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             {
                 const float *qh = p.q + (long long)sq.row0 * p.q_stride + me.head * HD;
                 const int w = warp & 3;
-                // eight rows of loads in flight at a time: one load per
-                // iteration would serialise 32 global-memory latencies
+                constexpr int LPR = HD / 4;        // lanes (of four floats each) per row
+                constexpr int RPI = 32 / LPR;      // rows a warp covers per load
+                const int sub_row = lane / LPR;
+                const int col4 = lane % LPR;
+                // eight loads in flight at a time: one load per iteration
+                // would serialise that many global-memory latencies
 #pragma unroll
-                for (int rr0 = 0; rr0 < 32; rr0 += 8) {
+                for (int rr0 = 0; rr0 < 32; rr0 += 8 * RPI) {
                     float4 x[8];
 #pragma unroll
                     for (int u = 0; u < 8; u++) {
-                        const int r = 32 * w + rr0 + u;
+                        const int r = 32 * w + rr0 + u * RPI + sub_row;
                         x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (me.r0 + r < sq.tq) {
                             x[u] = __ldg((const float4 *)(qh + (long long)(me.r0 + r) * p.q_stride +
-                                                          4 * lane));
+                                                          4 * col4));
                         }
                     }
 #pragma unroll
                     for (int u = 0; u < 8; u++) {
-                        const int r = 32 * w + rr0 + u;
+                        const int r = 32 * w + rr0 + u * RPI + sub_row;
                         const uint32_t lo = pack_f16(x[u].x * p.q_scale, x[u].y * p.q_scale);
                         const uint32_t hi = pack_f16(x[u].z * p.q_scale, x[u].w * p.q_scale);
-                        const int chunk = (lane & 15) >> 1;
-                        const uint32_t dst = q_smem(t) + (uint32_t)(lane >> 4) * SUB +
+                        const int chunk = (col4 & 15) >> 1;
+                        const uint32_t dst = q_smem(t) + (uint32_t)(col4 >> 4) * SUB +
                                              (uint32_t)r * 128 + (uint32_t)((chunk ^ (r & 7)) << 4) +
-                                             (uint32_t)(lane & 1) * 8;
+                                             (uint32_t)(col4 & 1) * 8;
                         asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(dst), "r"(lo), "r"(hi)
                                      : "memory");
                     }
@@ -472,7 +488,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         // PV of the previous step is complete (S of this step was
                         // committed after it), so O may be rescaled in place.
 #pragma unroll
-                        for (int c = 0; c < 4; c++) {
+                        for (int c = 0; c < HD / 32; c++) {
                             uint32_t o[32];
                             tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
                             tmem_wait_ld();
@@ -526,21 +542,35 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             if (ok) {
                 tc_fence_after();
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                float *orow = p.out + (long long)(sq.row0 + me.r0 + row) * p.out_stride + me.head * HD;
+                const long long orow = (long long)(sq.row0 + me.r0 + row) * p.out_stride + me.head * HD;
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
+                for (int c = 0; c < HD / 32; c++) {
                     uint32_t o[32];
                     tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
                     tmem_wait_ld();
                     if (me.r0 + row < sq.tq) {
+                        if (p.out_f16) {
+                            uint16_t *dst = (uint16_t *)p.out + orow + 32 * c;
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            float4 v;
-                            v.x = __uint_as_float(o[4 * i]) * inv;
-                            v.y = __uint_as_float(o[4 * i + 1]) * inv;
-                            v.z = __uint_as_float(o[4 * i + 2]) * inv;
-                            v.w = __uint_as_float(o[4 * i + 3]) * inv;
-                            *(float4 *)(orow + 32 * c + 4 * i) = v;
+                            for (int i = 0; i < 4; i++) {
+                                uint4 v;
+                                v.x = pack_f16(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+                                v.y = pack_f16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+                                v.z = pack_f16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+                                v.w = pack_f16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+                                *(uint4 *)(dst + 8 * i) = v;
+                            }
+                        } else {
+                            float *dst = (float *)p.out + orow + 32 * c;
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                float4 v;
+                                v.x = __uint_as_float(o[4 * i]) * inv;
+                                v.y = __uint_as_float(o[4 * i + 1]) * inv;
+                                v.z = __uint_as_float(o[4 * i + 2]) * inv;
+                                v.w = __uint_as_float(o[4 * i + 3]) * inv;
+                                *(float4 *)(dst + 4 * i) = v;
+                            }
                         }
                     }
                 }
@@ -556,13 +586,15 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 const int s = j & 1;
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
                 if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1u, abort_flag, p.status, 30)) break;
-                mbar_expect_tx(BAR(K_FULL + s), TILE);
-                tma_load_3d(k_smem(s), kmap, BAR(K_FULL + s), 0, j * BN, kh);
-                tma_load_3d(k_smem(s) + SUB, kmap, BAR(K_FULL + s), 64, j * BN, kh);
+                mbar_expect_tx(BAR(K_FULL + s), TILE_QK);
+#pragma unroll
+                for (int kt = 0; kt < KT; kt++) {
+                    tma_load_3d(k_smem(s) + kt * SUB, kmap, BAR(K_FULL + s), 64 * kt, j * BN, kh);
+                }
                 if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1u, abort_flag, p.status, 31)) break;
-                mbar_expect_tx(BAR(V_FULL + s), TILE);
+                mbar_expect_tx(BAR(V_FULL + s), TILE_V);
                 tma_load_3d(v_smem(s), vmap, BAR(V_FULL + s), j * BN, 0, kh);
-                tma_load_3d(v_smem(s) + SUB, vmap, BAR(V_FULL + s), j * BN + 64, 0, kh);
+                tma_load_3d(v_smem(s) + SUBV, vmap, BAR(V_FULL + s), j * BN + 64, 0, kh);
             }
         }
     } else if (warp == 9) {
@@ -576,23 +608,25 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             // to the start-address field, the second 64-wide sub-tile SUB >> 4.
             const uint64_t dq0 = smem_desc(q_smem(0)), dk0 = smem_desc(k_smem(0)),
                            dv0 = smem_desc(v_smem(0));
-            constexpr uint64_t kTileStep = TILE >> 4, kSubStep = SUB >> 4;
+            constexpr uint64_t kQkStep = TILE_QK >> 4, kVStep = TILE_V >> 4;
+            constexpr uint64_t kSubStep = SUB >> 4, kSubVStep = SUBV >> 4;
+            constexpr uint32_t kIdescS = idesc_n(BN), kIdescPV = idesc_n(HD);
             auto issue_s = [&](int t, int stage) {
-                const uint64_t a = dq0 + (uint64_t)t * kTileStep;
-                const uint64_t b = dk0 + (uint64_t)stage * kTileStep;
+                const uint64_t a = dq0 + (uint64_t)t * kQkStep;
+                const uint64_t b = dk0 + (uint64_t)stage * kQkStep;
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) {
+                for (int ks = 0; ks < HD / 16; ks++) {
                     const uint64_t off = (uint64_t)(ks >> 2) * kSubStep + (uint64_t)(ks & 3) * 2;
-                    mma_ss(tmem + s_col(t), a + off, b + off, kIdesc, ks > 0 ? 1u : 0u);
+                    mma_ss(tmem + s_col(t), a + off, b + off, kIdescS, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(BAR(S_FULL + t));
             };
             auto issue_pv = [&](int t, int stage, bool first, bool last) {
-                const uint64_t b = dv0 + (uint64_t)stage * kTileStep;
+                const uint64_t b = dv0 + (uint64_t)stage * kVStep;
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) {
-                    const uint64_t off = (uint64_t)(ks >> 2) * kSubStep + (uint64_t)(ks & 3) * 2;
-                    mma_ts(tmem + o_col(t), tmem + s_col(t) + 8 * ks, b + off, kIdesc,
+                for (int ks = 0; ks < BN / 16; ks++) {
+                    const uint64_t off = (uint64_t)(ks >> 2) * kSubVStep + (uint64_t)(ks & 3) * 2;
+                    mma_ts(tmem + o_col(t), tmem + s_col(t) + 8 * ks, b + off, kIdescPV,
                            (first && ks == 0) ? 0u : 1u);
                 }
                 if (last) tc_commit(BAR(O_DONE + t));
@@ -672,28 +706,29 @@ EncodeFn encode_fn()
 
 // A 3-d map over one cache: `inner` contiguous elements, `rows` rows `row_stride`
 // elements apart, `planes` kv heads `plane_stride` elements apart; tiles of
-// 64 x 128 x 1 with the 128-byte swizzle. Reads past any extent return zero.
+// 64 x box_rows x 1 with the 128-byte swizzle. Reads past any extent return zero.
 bool encode_map(CUtensorMap *map, const void *basep, uint64_t inner, uint64_t rows, uint64_t planes,
-                uint64_t row_stride, uint64_t plane_stride)
+                uint64_t row_stride, uint64_t plane_stride, uint32_t box_rows)
 {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[3] = {inner, rows, planes};
     const cuuint64_t strides[2] = {row_stride * 2, plane_stride * 2};
-    const cuuint32_t box[3] = {64, 128, 1};
+    const cuuint32_t box[3] = {64, box_rows, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(basep), dims, strides, box,
               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-const KernelReg reg_tc("flash_attn_h_tc", (const void *)prefill_tc_kernel);
+const KernelReg reg_tc("flash_attn_h_tc", (const void *)prefill_tc_kernel<128>);
+const KernelReg reg_tc64("flash_attn_64_tc", (const void *)prefill_tc_kernel<64>);
 
 }  // namespace
 
 bool prefill_tc_eligible(const PrefillParams &p, int hd)
 {
-    if (hd != 128 || p.kv_f32 || p.out_f16) return false;
+    if ((hd != 128 && hd != 64) || p.kv_f32) return false;
     if (p.nseq > LLMTIE_TC_MAX_SEQ) return false;
     if (((uintptr_t)p.q & 15u) != 0 || (p.q_stride & 3) != 0) return false;
     if (((uintptr_t)p.out & 15u) != 0 || (p.out_stride & 3) != 0) return false;
@@ -706,16 +741,19 @@ bool prefill_tc_eligible(const PrefillParams &p, int hd)
     return encode_fn() != nullptr;
 }
 
-cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int *status)
+cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, int *status)
 {
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemBytes);
+        cudaFuncSetAttribute(prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Geo<128>::SMEM);
+        cudaFuncSetAttribute(prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Geo<64>::SMEM);
         configured[dev] = true;
     }
+    const uint64_t HD = (uint64_t)hd;
     PrefillTcParams tp;
     memset(&tp, 0, sizeof(tp));
     int max_tq = 0;
@@ -728,12 +766,12 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int *stat
         tp.seq[b].tk = live;
         // keys: [kv][cap][hd] -> inner hd, rows = live keys, planes = kv heads
         if (!encode_map(&tp.kmap[b], s.k, HD, (uint64_t)live, (uint64_t)p.kv_heads, HD,
-                        (uint64_t)s.cap * HD)) {
+                        (uint64_t)s.cap * HD, 128)) {
             return cudaErrorInvalidValue;
         }
         // values: [kv][hd][cap] -> inner = live keys, rows = hd, planes = kv heads
         if (!encode_map(&tp.vmap[b], s.v, (uint64_t)live, HD, (uint64_t)p.kv_heads,
-                        (uint64_t)s.cap, (uint64_t)s.cap * HD)) {
+                        (uint64_t)s.cap, (uint64_t)s.cap * HD, (uint32_t)hd)) {
             return cudaErrorInvalidValue;
         }
         max_tq = s.tq > max_tq ? s.tq : max_tq;
@@ -742,7 +780,8 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int *stat
     tp.nseq = p.nseq;
     tp.q = p.q;
     tp.q_stride = p.q_stride;
-    tp.out = (float *)p.out;
+    tp.out = p.out;
+    tp.out_f16 = p.out_f16;
     tp.out_stride = p.out_stride;
     tp.heads = p.heads;
     tp.kv_heads = p.kv_heads;
@@ -759,6 +798,10 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int *stat
     } else {
         grid = dim3(p.heads, (row_blocks + 1) / 2, p.nseq);
     }
-    prefill_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(tp);
+    if (hd == 128) {
+        prefill_tc_kernel<128><<<grid, kThreads, Geo<128>::SMEM, st>>>(tp);
+    } else {
+        prefill_tc_kernel<64><<<grid, kThreads, Geo<64>::SMEM, st>>>(tp);
+    }
     return cudaGetLastError();
 }

@@ -209,37 +209,37 @@ __device__ __forceinline__ int varlen_seq_of(const VarlenParams &p, int row)
     return b;
 }
 
-// RoPE on q (in place) and on k (into the f16 K cache at past + position):
-// one thread per rotating pair. The arithmetic is `rope_kernel`'s followed by
-// the append's rounding, so the result equals the two-launch chain bit for
-// bit.
+// RoPE on q (in place) and on k (into the f16 K cache at past + position). One
+// thread per (row, rotating pair): the angle depends on the position and the
+// pair only, so its accurate powf / sincosf is taken once and reused over every
+// head. The arithmetic per element is `rope_kernel`'s followed by the append's
+// rounding, so the result equals the two-launch chain bit for bit.
 __global__ void varlen_rope_kernel(const __grid_constant__ VarlenParams p)
 {
     const int half = p.hd >> 1;
-    const int per_row = (p.heads + p.kv_heads) * half;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)p.total * per_row) return;
-    const int row = (int)(i / per_row);
-    const int e = (int)(i % per_row);
+    if (i >= (long long)p.total * half) return;
+    const int row = (int)(i / half);
+    const int j = (int)(i % half);
     const int b = varlen_seq_of(p, row);
     const VarlenSeq &sq = p.seq[b];
     const int ti = row - sq.row0;
-    const int j = e % half;
-    const int hh = e / half;
     float sn, cs, lo, hi;
     pair_sincos(p.theta, j, p.hd, p.freq_div, sq.past + ti, sn, cs);
-    if (hh < p.heads) {
-        float *x = p.q + ((size_t)row * p.heads + hh) * p.hd + j;
-        rotate(x[0], x[half], cs, sn, lo, hi);
-        x[0] = lo;
-        x[half] = hi;
-    } else {
-        const int h = hh - p.heads;
-        const float *x = p.k + ((size_t)row * p.kv_heads + h) * p.hd + j;
-        rotate(x[0], x[half], cs, sn, lo, hi);
+    float *xq = p.q + (size_t)row * p.heads * p.hd + j;
+    for (int h = 0; h < p.heads; h++) {
+        rotate(xq[0], xq[half], cs, sn, lo, hi);
+        xq[0] = lo;
+        xq[half] = hi;
+        xq += p.hd;
+    }
+    const float *xk = p.k + (size_t)row * p.kv_heads * p.hd + j;
+    for (int h = 0; h < p.kv_heads; h++) {
+        rotate(xk[0], xk[half], cs, sn, lo, hi);
         uint16_t *d = sq.k + ((size_t)h * sq.cap + sq.past + ti) * p.hd;
         d[j] = f16_bits(lo);
         d[j + half] = f16_bits(hi);
+        xk += p.hd;
     }
 }
 
@@ -351,8 +351,8 @@ void launch_rows_stage(cudaStream_t st, const float *qkv, uint16_t *k, uint16_t 
 void launch_varlen_rope_append(cudaStream_t st, const VarlenParams &p)
 {
     if (p.total == 0) return;
-    const size_t n = (size_t)p.total * (p.heads + p.kv_heads) * (p.hd / 2);
-    varlen_rope_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(p);
+    const size_t n = (size_t)p.total * (p.hd / 2);
+    varlen_rope_kernel<<<flat_blocks(n, 128), 128, 0, st>>>(p);
     int max_n = 0;
     for (int b = 0; b < p.nseq; b++) max_n = p.seq[b].n > max_n ? p.seq[b].n : max_n;
     const dim3 grid((p.kv_heads * p.hd + 31) / 32, (max_n + 31) / 32, p.nseq);

@@ -109,3 +109,18 @@ class ShardedDecode:
             dist.all_gather_into_tensor(self._gathered, part.reshape(-1), group=self.group)
         rows = part.numel() // (self.head_dim + 2)
         return self.merge_fn(self._gathered, self.world, rows)
+
+    def capture(self, q: torch.Tensor):
+        """Records one decode step (attention, all-gather, merge) over the
+        fixed buffer `q` into a CUDA graph on the handle's stream and returns
+        (graph, out): `graph.replay()` re-runs the step with whatever `q` holds
+        then, at one launch's host cost. The step is run once uncaptured first
+        so that every buffer it needs exists before capture begins."""
+        if self.stream is None:
+            raise RuntimeError("capture needs the GPU binding (ShardedDecode.on_gpu)")
+        self.decode(q)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=self.stream):
+            out = self.decode(q)
+        return graph, out
