@@ -774,7 +774,11 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         sp.partial = p.partial;
         sp.q_scale = p.q_scale;
         sp.sl2 = p.sl2;
-        const int grid = (int)std::min<long long>(g->sm_count, units);
+        // One block per SM, but never fewer than four units (512 keys) a block:
+        // a short context cut any finer spends longer merging partials than
+        // it saved streaming them.
+        const int grid =
+            (int)std::min<long long>(g->sm_count, std::max<long long>(1, units / 4));
         const llmtie_status s =
             scratch_reserve(g, scratch, (size_t)p.nseq * inner, (size_t)grid * 2, (size_t)hd);
         if (s != LLMTIE_OK) return s;
