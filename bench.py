@@ -145,6 +145,8 @@ def dist_setup(n_gpus: int):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
+        # plain peer loads and stores only: no NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     elif n_gpus > 1:
@@ -214,8 +216,22 @@ def decode128k(args, world, rank, local):
         q = torch.randn(batch * HEADS * HD, generator=gen, device=gpu.device)
         q = q.to(torch.float16).to(torch.float32)
     sd = ShardedDecode.on_gpu(gpu, ks, vs, [tk] * batch, [cap] * batch, HEADS, KV_HEADS, HD,
-                              SCALE)
+                              SCALE, p2p=not args.nccl)
     gpu.synchronize()
+
+    # The sharded paths have no single-GPU test to stand on, so the fused
+    # exchange is checked here against the all-gather path on the same inputs.
+    exchange_err = None
+    if world > 1 and not args.nccl:
+        ref = ShardedDecode.on_gpu(gpu, ks, vs, [tk] * batch, [cap] * batch, HEADS, KV_HEADS, HD,
+                                   SCALE, p2p=False)
+        a = sd.decode(q).clone()
+        b = sd.decode(q).clone()      # a second step: the other gather buffer
+        c = ref.decode(q)
+        gpu.synchronize()
+        exchange_err = float(max((a - c).abs().max().item(), (b - c).abs().max().item()))
+        if not (exchange_err < 1e-5):
+            raise SystemExit("fused exchange disagrees with the all-gather path: %g" % exchange_err)
 
     # Kernels of ours per step: the attention kernel, and the merge when sharded.
     launches0 = gpu.launch_count()
@@ -310,6 +326,9 @@ def decode128k(args, world, rank, local):
         },
         "gpu_launches": int(launches),
         "cuda_graph": bool(world > 1 and not args.no_graph),
+        "exchange": ("none" if world == 1 else "nccl all-gather" if args.nccl
+                     else "peer-memory push fused into the decode kernel"),
+        "exchange_max_abs_vs_allgather": exchange_err,
         "roofline": {
             "bound": "hbm",
             "achieved": achieved,
@@ -585,6 +604,9 @@ def main():
     ap.add_argument("--context", type=int, default=131072)
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--nccl", action="store_true",
+                    help="exchange the triples with an NCCL all-gather instead of the fused "
+                         "peer-memory push")
     ap.add_argument("--no-graph", action="store_true",
                     help="time the sharded step as separate host calls, not a CUDA graph")
     args = ap.parse_args()

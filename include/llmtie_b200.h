@@ -242,6 +242,38 @@ llmtie_status llmtie_decode_batched(llmtie_gpu *g, const float *q, size_t q_len,
 llmtie_status llmtie_lse_merge(llmtie_gpu *g, const float *parts_buf, size_t parts_len,
                                size_t parts, size_t rows, size_t head_dim, float *out,
                                size_t out_len);
+/* The same two steps with the exchange between GPUs fused into the kernels
+ * (no counterpart in the reference, which has no multi-GPU path). Every rank
+ * holds a slice of each sequence's positions. `gather[r]` and `flags[r]` are
+ * rank r's buffers as mapped into this process (symmetric / peer memory):
+ * gather is f32 [2][world][batch*heads][head_dim+2], flags uint32 [world],
+ * both zero before the first step; `step` is a uint32 of this rank's own,
+ * zero before the first step.
+ * llmtie_decode_batched_push decodes this rank's slice and stores the
+ * un-normalised triples straight into slot [step&1][rank] of EVERY rank's
+ * gather buffer with plain peer stores over NVLink; the block that finishes
+ * the launch's last head then raises flag [rank] on every rank and advances
+ * `step`. llmtie_lse_merge_wait, enqueued after it on the same stream, waits
+ * (bounded: about a second, then LLMTIE_ERR_TIMEOUT at the next synchronize)
+ * until all `world` flags have reached this rank's step and merges. All ranks
+ * must make the same sequence of calls. At most 32 sequences a call; caches
+ * 16-byte aligned with capacities that are multiples of 8. */
+typedef struct llmtie_exchange {
+    int32_t world;
+    int32_t rank;
+    float *const *gather;     /* HOST array of `world` device pointers */
+    uint32_t *const *flags;   /* HOST array of `world` device pointers */
+    uint32_t *step;           /* device pointer, this rank's */
+} llmtie_exchange;
+llmtie_status llmtie_decode_batched_push(llmtie_gpu *g, const float *q, size_t q_len,
+                                         const uint16_t *const *k_ptrs,
+                                         const uint16_t *const *v_ptrs, const int32_t *tk,
+                                         const int32_t *cap, size_t batch, size_t heads,
+                                         size_t kv_heads, size_t head_dim, float scale,
+                                         int32_t scale_q, llmtie_decode_scratch *scratch,
+                                         const llmtie_exchange *xch);
+llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_exchange *xch, size_t rows,
+                                    size_t head_dim, float *out, size_t out_len);
 /* AsrModel::attend (crates/llmtie-asr/src/model.rs:573-641) fused: n query
  * rows (q f32 [n][heads*hd], scale applied to q) over f16 cross caches
  * K [heads][cap][hd], V [heads][hd][cap] with tk live keys, non-causal;

@@ -11,6 +11,7 @@ from .gpu import (  # noqa: F401
     DecodeScratch,
     DeviceTimeout,
     DriverError,
+    Exchange,
     Gpu,
     InvalidArgument,
     Misaligned,

@@ -62,6 +62,9 @@ PROTOTYPES = {
     "llmtie_decode_batched": (
         i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp, sz, i32]),
     "llmtie_lse_merge": (i32, [vp, vp, sz, sz, sz, sz, vp, sz]),
+    "llmtie_decode_batched_push": (
+        i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp]),
+    "llmtie_lse_merge_wait": (i32, [vp, vp, sz, sz, vp, sz]),
     "llmtie_cross_attn": (
         i32, [vp, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, vp, vp, sz]),
     "llmtie_prefill_varlen": (

@@ -736,14 +736,20 @@ static void decode_plan(llmtie_gpu *g, DecodeParams &p, int hd)
 }
 
 static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams &p, int hd,
-                                   llmtie_decode_scratch *scratch)
+                                   llmtie_decode_scratch *scratch,
+                                   const llmtie_exchange *xch = nullptr)
 {
     bool aligned = true;
     for (int b = 0; b < p.nseq; b++) {
         if (p.seq[b].cap % 8 != 0 || ((uintptr_t)p.seq[b].v & 15u) != 0) aligned = false;
     }
     static const bool no_stream = getenv("LLMTIE_B200_DECODE_NO_STREAM") != nullptr;
-    if (aligned && !no_stream) {
+    if (xch && !aligned) {
+        return llmtie_fail(LLMTIE_ERR_MISALIGNED,
+                           "the exchanging decode wants 16-byte aligned caches and capacities "
+                           "that are multiples of 8");
+    }
+    if (aligned && (!no_stream || xch)) {
         // The ring kernel, cut by work: one block per SM, never more blocks
         // than 128-key units.
         DecodeStreamParams sp;
@@ -779,11 +785,24 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         // it saved streaming them.
         const int grid =
             (int)std::min<long long>(g->sm_count, std::max<long long>(1, units / 4));
+        const size_t pairs = (size_t)p.nseq * inner;
         const llmtie_status s =
-            scratch_reserve(g, scratch, (size_t)p.nseq * inner, (size_t)grid * 2, (size_t)hd);
+            scratch_reserve(g, scratch, pairs + 1, (size_t)grid * 2, (size_t)hd);
         if (s != LLMTIE_OK) return s;
         sp.part = scratch->part;
         sp.ctr = scratch->ctr;
+        if (xch) {
+            sp.xch_world = xch->world;
+            sp.xch_rank = xch->rank;
+            for (int r = 0; r < xch->world; r++) {
+                sp.xch_gather[r] = xch->gather[r];
+                sp.xch_flags[r] = xch->flags[r];
+            }
+            sp.xch_step = xch->step;
+            sp.xch_done = scratch->ctr + pairs;   // one more counter after the pairs'
+            sp.xch_pairs = (int)pairs;
+            sp.xch_rank_stride = (long long)p.nseq * p.out_seq;
+        }
         LaunchScope ls(g, name);
         const cudaError_t e = launch_decode_stream(g->stream, sp, hd, grid);
         if (e != cudaSuccess) return driver_fail(name, e);
@@ -924,13 +943,14 @@ extern "C" llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_
     return ls.done();
 }
 
-extern "C" llmtie_status llmtie_decode_batched(llmtie_gpu *g, const float *q, size_t q_len,
-                                               const uint16_t *const *k_ptrs,
-                                               const uint16_t *const *v_ptrs, const int32_t *tk,
-                                               const int32_t *cap, size_t batch, size_t heads,
-                                               size_t kv_heads, size_t head_dim, float scale,
-                                               int32_t scale_q, llmtie_decode_scratch *scratch,
-                                               float *out, size_t out_len, int32_t partial)
+static llmtie_status decode_batched_impl(llmtie_gpu *g, const float *q, size_t q_len,
+                                         const uint16_t *const *k_ptrs,
+                                         const uint16_t *const *v_ptrs, const int32_t *tk,
+                                         const int32_t *cap, size_t batch, size_t heads,
+                                         size_t kv_heads, size_t head_dim, float scale,
+                                         int32_t scale_q, llmtie_decode_scratch *scratch,
+                                         float *out, size_t out_len, int32_t partial,
+                                         const llmtie_exchange *xch)
 {
     NEED_HANDLE(g);
     if (!scratch) return llmtie_fail(LLMTIE_ERR_INVALID, "null decode scratch");
@@ -947,9 +967,19 @@ extern "C" llmtie_status llmtie_decode_batched(llmtie_gpu *g, const float *q, si
         return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
                            batch * n, q_len);
     }
-    if (out_len < batch * on) {
+    if (!xch && out_len < batch * on) {
         return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
                            batch * on, out_len);
+    }
+    if (xch) {
+        if (xch->world < 2 || xch->world > LLMTIE_MAX_RANKS || xch->rank < 0 ||
+            xch->rank >= xch->world || !xch->gather || !xch->flags || !xch->step) {
+            return llmtie_fail(LLMTIE_ERR_INVALID, "a malformed exchange descriptor");
+        }
+        if (batch > LLMTIE_DECODE_MAX_SEQ) {
+            return llmtie_fail(LLMTIE_ERR_INVALID, "the exchanging decode takes at most %d "
+                               "sequences a call", LLMTIE_DECODE_MAX_SEQ);
+        }
     }
     for (size_t b = 0; b < batch; b++) {
         if (cap[b] <= 0 || cap[b] % 4 != 0) {
@@ -992,10 +1022,54 @@ extern "C" llmtie_status llmtie_decode_batched(llmtie_gpu *g, const float *q, si
         p.sl2 = (scale_q ? 1.0f : scale) * kLog2e;
         const llmtie_status s = decode_launch(
             g, head_dim == 128 ? "attn_decode_h128" : "attn_decode_h64", p, (int)head_dim,
-            scratch);
+            scratch, xch);
         if (s != LLMTIE_OK) return s;
     }
     return LLMTIE_OK;
+}
+
+extern "C" llmtie_status llmtie_decode_batched(llmtie_gpu *g, const float *q, size_t q_len,
+                                               const uint16_t *const *k_ptrs,
+                                               const uint16_t *const *v_ptrs, const int32_t *tk,
+                                               const int32_t *cap, size_t batch, size_t heads,
+                                               size_t kv_heads, size_t head_dim, float scale,
+                                               int32_t scale_q, llmtie_decode_scratch *scratch,
+                                               float *out, size_t out_len, int32_t partial)
+{
+    return decode_batched_impl(g, q, q_len, k_ptrs, v_ptrs, tk, cap, batch, heads, kv_heads,
+                               head_dim, scale, scale_q, scratch, out, out_len, partial, nullptr);
+}
+
+extern "C" llmtie_status llmtie_decode_batched_push(
+    llmtie_gpu *g, const float *q, size_t q_len, const uint16_t *const *k_ptrs,
+    const uint16_t *const *v_ptrs, const int32_t *tk, const int32_t *cap, size_t batch,
+    size_t heads, size_t kv_heads, size_t head_dim, float scale, int32_t scale_q,
+    llmtie_decode_scratch *scratch, const llmtie_exchange *xch)
+{
+    if (!xch) return llmtie_fail(LLMTIE_ERR_INVALID, "null exchange descriptor");
+    return decode_batched_impl(g, q, q_len, k_ptrs, v_ptrs, tk, cap, batch, heads, kv_heads,
+                               head_dim, scale, scale_q, scratch, nullptr, 0, 1, xch);
+}
+
+extern "C" llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_exchange *xch,
+                                               size_t rows, size_t head_dim, float *out,
+                                               size_t out_len)
+{
+    NEED_HANDLE(g);
+    if (!xch || xch->world < 2 || xch->world > LLMTIE_MAX_RANKS || xch->rank < 0 ||
+        xch->rank >= xch->world || !xch->gather || !xch->flags || !xch->step) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "a malformed exchange descriptor");
+    }
+    if (out_len < rows * head_dim) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           rows * head_dim, out_len);
+    }
+    if (head_dim == 0 || head_dim > 1024) return unsupported(head_dim, rows, rows);
+    if (rows == 0) return LLMTIE_OK;
+    LaunchScope ls(g, "lse_merge_wait");
+    launch_lse_merge_wait(g->stream, xch->gather[xch->rank], xch->flags[xch->rank], xch->step,
+                          xch->world, (int)rows, (int)head_dim, out, g->timeout_flag);
+    return ls.done();
 }
 
 extern "C" llmtie_status llmtie_lse_merge(llmtie_gpu *g, const float *parts_buf,

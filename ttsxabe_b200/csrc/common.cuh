@@ -107,6 +107,7 @@ struct DecodeParams {
 cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd);
 // How many blocks of the decode kernel fit the device at once.
 int decode_resident_blocks(int hd, int sm_count, int nb);
+#define LLMTIE_MAX_RANKS 8
 // decode_stream.cu: the same operands cut over the grid by work (see there).
 struct DecodeStreamParams {
     DecodeSeq seq[LLMTIE_DECODE_MAX_SEQ];
@@ -122,6 +123,15 @@ struct DecodeStreamParams {
     int rows, row_chunks, kv_heads, nseq;
     int partial;
     float q_scale, sl2;
+    // Exchange between ranks (xch_world > 0, partial mode): finished triples go
+    // to slot [step & 1][xch_rank] of every rank's gather buffer instead of `out`.
+    int xch_world, xch_rank;
+    float *xch_gather[LLMTIE_MAX_RANKS];     // every rank's gather buffer, as mapped here
+    unsigned *xch_flags[LLMTIE_MAX_RANKS];   // every rank's flag array [world]
+    unsigned *xch_step;                      // this rank's step counter
+    unsigned *xch_done;                      // pairs finished in this launch, zero at rest
+    int xch_pairs;                           // pairs in this launch
+    long long xch_rank_stride;               // floats one rank's triples take
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
@@ -129,6 +139,11 @@ void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const f
                        int hd, int tk, int cap, float q_scale, float s_scale);
 void launch_lse_merge(cudaStream_t st, const float *parts_buf, int parts, int rows, int hd,
                       float *out);
+// Waits (bounded) until every rank's flag has reached this rank's step, then
+// merges the gather buffer the step filled.
+void launch_lse_merge_wait(cudaStream_t st, const float *gather, const unsigned *flags,
+                           const unsigned *step, int world, int rows, int hd, float *out,
+                           int *status);
 
 // prefill_mma.cu
 #define LLMTIE_PREFILL_MAX_SEQ 32

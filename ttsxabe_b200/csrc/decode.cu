@@ -499,7 +499,66 @@ int resident(int nb)
     return per_sm;
 }
 
+// The same merge over the gather buffer that the ranks' decode kernels
+// filled directly (peer stores over NVLink). Thread 0 of each block first
+// waits, bounded, until every rank's flag has reached this rank's step: a
+// flag is raised only after all of that rank's triples are visible
+// system-wide. Layout: gather [2][world][rows][hd + 2], flags [world].
+__global__ void lse_merge_wait_kernel(const float *__restrict__ gather,
+                                      const unsigned *flags, const unsigned *step, int world,
+                                      int rows, int hd, float *__restrict__ out, int *status)
+{
+    __shared__ unsigned s_expected;
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+        const unsigned expected = *(volatile const unsigned *)step;
+        const long long t0 = clock64();
+        int ok = 1;
+        for (int r = 0; r < world && ok; r++) {
+            while ((int)(*(volatile const unsigned *)(flags + r) - expected) < 0) {
+                if (clock64() - t0 > (1ll << 31)) {   // about a second
+                    ok = 0;
+                    atomicExch(status, 60 + r);
+                    break;
+                }
+            }
+        }
+        s_expected = expected;
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    __threadfence();
+    const int row = blockIdx.x;
+    const int stride = hd + 2;
+    const float *buf = gather + (size_t)((s_expected - 1u) & 1u) * world * rows * stride;
+    float M = -CUDART_INF_F;
+    for (int i = 0; i < world; i++) {
+        M = fmaxf(M, __ldcg(buf + ((size_t)i * rows + row) * stride + hd));
+    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float O = 0.0f, L = 0.0f;
+        for (int i = 0; i < world; i++) {
+            const float *pr = buf + ((size_t)i * rows + row) * stride;
+            const float mi = __ldcg(pr + hd);
+            const float f = (mi == -CUDART_INF_F) ? 0.0f : __expf(mi - M);
+            O += f * __ldcg(pr + d);
+            L += f * __ldcg(pr + hd + 1);
+        }
+        out[(size_t)row * hd + d] = L > 0.0f ? O / L : 0.0f;
+    }
+}
+
+const KernelReg reg_merge_wait("lse_merge_wait", (const void *)lse_merge_wait_kernel);
+
 }  // namespace
+
+void launch_lse_merge_wait(cudaStream_t st, const float *gather, const unsigned *flags,
+                           const unsigned *step, int world, int rows, int hd, float *out,
+                           int *status)
+{
+    lse_merge_wait_kernel<<<rows, hd, 0, st>>>(gather, flags, step, world, rows, hd, out, status);
+}
 
 cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd)
 {

@@ -124,6 +124,11 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     const int c = lane & 3;
     unsigned char *ring = ring_all + (size_t)warp * kStages * STAGE;
 
+    // When ranks exchange, the step number picks which of the two gather
+    // buffers this launch fills; every block reads it before any block can
+    // have finished the launch and advanced it.
+    const unsigned xch_step = p.xch_world ? *(volatile const unsigned *)p.xch_step : 0u;
+
     const long long W = p.total_units;
     const long long G = gridDim.x;
     const long long u0 = (long long)blockIdx.x * W / G;
@@ -333,8 +338,53 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         // (slot 0); one that started before it is its last (slot 1).
         const int slot = (u == u0) ? 0 : 1;
         float *part = p.part + ((size_t)blockIdx.x * 2 + slot) * kRows * (HD + 2);
-        float *orow0 = p.out + (long long)b * p.out_seq + (long long)kh * p.out_kv +
-                       (long long)(rc * kRows) * p.out_row;
+        const long long ooff = (long long)b * p.out_seq + (long long)kh * p.out_kv +
+                               (long long)(rc * kRows) * p.out_row;
+        // One finished value of the pair: normalised into `out`, or the
+        // un-normalised triple - into `out`, or, when ranks exchange, straight
+        // into every rank's gather buffer over NVLink (this rank's included).
+        auto emit = [&](int row, int d, float O, float M, float L) {
+            const long long at = ooff + (long long)row * p.out_row;
+            if (!p.partial) {
+                p.out[at + d] = L > 0.0f ? O / L : 0.0f;
+            } else if (p.xch_world == 0) {
+                p.out[at + d] = O;
+                if (d == 0) {
+                    p.out[at + HD] = M * kLn2;
+                    p.out[at + HD + 1] = L;
+                }
+            } else {
+                const long long slot_at =
+                    ((long long)(xch_step & 1u) * p.xch_world + p.xch_rank) * p.xch_rank_stride + at;
+                for (int r = 0; r < p.xch_world; r++) {
+                    float *dst = p.xch_gather[r] + slot_at;
+                    dst[d] = O;
+                    if (d == 0) {
+                        dst[HD] = M * kLn2;
+                        dst[HD + 1] = L;
+                    }
+                }
+            }
+        };
+        // After a pair's values are out: count it, and the block that finishes
+        // the launch's last pair raises this rank's flag on every rank.
+        auto pair_done = [&]() {
+            if (p.xch_world == 0) return;
+            __threadfence_system();
+            __syncthreads();
+            if (tid == 0) {
+                const unsigned prev = atomicAdd(p.xch_done, 1u);
+                if (prev == (unsigned)(p.xch_pairs - 1)) {
+                    *p.xch_done = 0u;
+                    const unsigned next = xch_step + 1u;
+                    __threadfence_system();
+                    for (int r = 0; r < p.xch_world; r++) {
+                        *(volatile unsigned *)(p.xch_flags[r] + p.xch_rank) = next;
+                    }
+                    *(volatile unsigned *)p.xch_step = next;
+                }
+            }
+        };
         for (int idx = tid; idx < rows_here * HD; idx += kThreads) {
             const int row = idx / HD, d = idx % HD;
             float M = sm_m[0][row];
@@ -349,16 +399,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                 L += f * sm_l[w][row];
             }
             if (whole) {
-                float *orow = orow0 + (long long)row * p.out_row;
-                if (p.partial) {
-                    orow[d] = O;
-                    if (d == 0) {
-                        orow[HD] = M * kLn2;
-                        orow[HD + 1] = L;
-                    }
-                } else {
-                    orow[d] = L > 0.0f ? O / L : 0.0f;
-                }
+                emit(row, d, O, M, L);
             } else {
                 float *pr = part + row * (HD + 2);
                 pr[d] = O;
@@ -369,6 +410,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
         }
 
+        if (whole) pair_done();
         if (!whole) {
             // ---- the last block of this pair to arrive merges every partial -------------
             const int c_first = covering(pair_u0, W, G);
@@ -422,19 +464,9 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                             }
                         }
                     }
-                    if (tid < HD) {
-                        float *orow = orow0 + (long long)row * p.out_row;
-                        if (p.partial) {
-                            orow[tid] = O;
-                            if (tid == 0) {
-                                orow[HD] = M * kLn2;
-                                orow[HD + 1] = L;
-                            }
-                        } else {
-                            orow[tid] = L > 0.0f ? O / L : 0.0f;
-                        }
-                    }
+                    if (tid < HD) emit(row, tid, O, M, L);
                 }
+                pair_done();
                 if (tid == 0) p.ctr[pair] = 0u;   // at rest again for the next call
             }
         }

@@ -122,6 +122,27 @@ class DecodeScratch:
             pass
 
 
+class _ExchangeStruct(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32),
+                ("gather", C.POINTER(C.c_void_p)), ("flags", C.POINTER(C.c_void_p)),
+                ("step", C.c_void_p)]
+
+
+class Exchange:
+    """The peer-memory descriptor `llmtie_decode_batched_push` and
+    `llmtie_lse_merge_wait` take: every rank's gather buffer and flag array as
+    mapped into this process, and this rank's step counter."""
+
+    def __init__(self, world: int, rank: int, gather_ptrs, flag_ptrs, step_ptr: int) -> None:
+        self.world, self.rank = world, rank
+        self._gather = (C.c_void_p * world)(*gather_ptrs)
+        self._flags = (C.c_void_p * world)(*flag_ptrs)
+        self.struct = _ExchangeStruct(world, rank, self._gather, self._flags, step_ptr)
+
+    def ref(self):
+        return C.byref(self.struct)
+
+
 class Gpu:
     """One device handle with its own stream (device.rs:737-842)."""
 
@@ -347,6 +368,22 @@ class Gpu:
             self._i32_table(tk), self._i32_table(cap), batch, heads, kv_heads, head_dim, scale,
             int(bool(scale_q)), scratch._bind(self), out.data_ptr(), out.numel(),
             int(bool(partial))))
+        return out
+
+    def decode_batched_push(self, q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale, scale_q,
+                            scratch: DecodeScratch, xch: Exchange) -> None:
+        """Decodes this rank's slices and pushes the triples into every rank's
+        gather buffer over peer memory (see include/llmtie_b200.h)."""
+        _check(self._lib.llmtie_decode_batched_push(
+            self._h, q.data_ptr(), q.numel(), self._ptr_table(ks), self._ptr_table(vs),
+            self._i32_table(tk), self._i32_table(cap), len(ks), heads, kv_heads, head_dim, scale,
+            int(bool(scale_q)), scratch._bind(self), xch.ref()))
+
+    def lse_merge_wait(self, xch: Exchange, rows, head_dim, out=None) -> torch.Tensor:
+        if out is None:
+            out = self.uninit(rows * head_dim)
+        _check(self._lib.llmtie_lse_merge_wait(self._h, xch.ref(), rows, head_dim,
+                                               out.data_ptr(), out.numel()))
         return out
 
     def lse_merge(self, parts_buf, parts, rows, head_dim, out=None) -> torch.Tensor:

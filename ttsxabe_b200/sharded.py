@@ -63,17 +63,25 @@ class ShardedDecode:
         self.merge_fn = merge_fn
         self.stream = stream
         self._gathered = None
+        self._fused = None
 
     @classmethod
     def on_gpu(cls, gpu, ks: Sequence[torch.Tensor], vs: Sequence[torch.Tensor],
                tk: Sequence[int], cap: Sequence[int], heads: int, kv_heads: int, head_dim: int,
-               scale: float, scale_q: bool = False, group=None) -> "ShardedDecode":
-        """Binds the GPU entry points over this rank's caches."""
+               scale: float, scale_q: bool = False, group=None, p2p: bool = False
+               ) -> "ShardedDecode":
+        """Binds the GPU entry points over this rank's caches. With `p2p` the
+        exchange is fused into the kernels: the decode kernel stores its triples
+        into every rank's gather buffer over NVLink peer memory and a waiting
+        merge kernel follows it - no collective call in the step."""
         from .gpu import DecodeScratch
 
         scratch = DecodeScratch()
         batch = len(ks)
         outs = {}
+        if p2p and dist.is_initialized() and dist.get_world_size(group) > 1:
+            return cls._on_gpu_p2p(gpu, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
+                                   scale_q, group, scratch)
 
         def partial_fn(q, partial):
             width = heads * (head_dim + 2) if partial else heads * head_dim
@@ -93,9 +101,61 @@ class ShardedDecode:
         self._scratch = scratch
         return self
 
+    @classmethod
+    def _on_gpu_p2p(cls, gpu, ks, vs, tk, cap, heads, kv_heads, head_dim, scale, scale_q, group,
+                    scratch) -> "ShardedDecode":
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .gpu import Exchange
+
+        world = dist.get_world_size(group)
+        rank = dist.get_rank(group)
+        batch = len(ks)
+        rows = batch * heads
+        pg = group if group is not None else dist.group.WORLD
+        with torch.cuda.stream(gpu.stream):
+            # [2 steps in flight][world][rows][hd + 2] triples, then the flags
+            gather = symm_mem.empty(2 * world * rows * (head_dim + 2), dtype=torch.float32,
+                                    device=gpu.device)
+            flags = symm_mem.empty(64, dtype=torch.int32, device=gpu.device)
+            gather.zero_()
+            flags.zero_()
+            step = torch.zeros(1, dtype=torch.int32, device=gpu.device)
+            out = torch.empty(rows * head_dim, dtype=torch.float32, device=gpu.device)
+        gh = symm_mem.rendezvous(gather, pg)
+        fh = symm_mem.rendezvous(flags, pg)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        xch = Exchange(world, rank, [int(p) for p in gh.buffer_ptrs],
+                       [int(p) for p in fh.buffer_ptrs], step.data_ptr())
+
+        self = cls(heads, head_dim, group, None, None, gpu.stream)
+        self._keep = (gather, flags, step, gh, fh, xch, scratch, out)
+
+        def fused(q):
+            gpu.decode_batched_push(q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
+                                    scale_q, scratch, xch)
+            return gpu.lse_merge_wait(xch, rows, head_dim, out=out)
+
+        self._fused = fused
+        # the attention kernel alone, for timing: triples into a local buffer
+        local = {}
+
+        def partial_fn(q, partial):
+            width = heads * (head_dim + 2) if partial else heads * head_dim
+            if partial not in local:
+                local[partial] = gpu.uninit(batch * width)
+            return gpu.decode_batched(q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
+                                      scale_q, scratch, out=local[partial], partial=partial)
+
+        self.partial_fn = partial_fn
+        return self
+
     def decode(self, q: torch.Tensor) -> torch.Tensor:
         """q: [batch, heads*hd] (rotated), the same on every rank. Returns the
         attention output [batch*heads*hd] on every rank."""
+        if getattr(self, "_fused", None) is not None:
+            return self._fused(q)
         if self.world == 1:
             return self.partial_fn(q, False)
         part = self.partial_fn(q, True)
