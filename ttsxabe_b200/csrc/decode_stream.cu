@@ -97,6 +97,128 @@ __device__ __forceinline__ int covering(long long u, long long W, long long G)
     return (int)(((u + 1) * G + W - 1) / W - 1);
 }
 
+// One finished value of a pair: normalised into `out`, or the un-normalised
+// triple - into `out`, or, when ranks exchange, straight into every rank's
+// gather buffer over NVLink (this rank's included).
+template <int HD>
+__device__ __forceinline__ void emit_value(const DecodeStreamParams &p, long long ooff,
+                                           unsigned xch_step, int row, int d, float O, float M,
+                                           float L)
+{
+    constexpr float kLn2 = 0.6931471805599453f;
+    const long long at = ooff + (long long)row * p.out_row;
+    if (!p.partial) {
+        p.out[at + d] = L > 0.0f ? O / L : 0.0f;
+    } else if (p.xch_world == 0) {
+        p.out[at + d] = O;
+        if (d == 0) {
+            p.out[at + HD] = M * kLn2;
+            p.out[at + HD + 1] = L;
+        }
+    } else {
+        const long long slot_at =
+            ((long long)(xch_step & 1u) * p.xch_world + p.xch_rank) * p.xch_rank_stride + at;
+        for (int r = 0; r < p.xch_world; r++) {
+            float *dst = p.xch_gather[r] + slot_at;
+            dst[d] = O;
+            if (d == 0) {
+                dst[HD] = M * kLn2;
+                dst[HD + 1] = L;
+            }
+        }
+    }
+}
+
+// The last block of a pair to arrive merges every partial of the pair. Kept
+// out of line: its register needs must not shape the allocation of the key
+// loop, which is what the kernel's bandwidth hangs on.
+template <int HD>
+__device__ __noinline__ void merge_pair(const DecodeStreamParams &p, long long pair_u0,
+                                        int c_first, int c_last, int rows_here, long long W,
+                                        long long G, long long ooff, unsigned xch_step)
+{
+    const int tid = threadIdx.x;
+    const int count = c_last - c_first + 1;
+    auto emit = [&](int row, int d, float O, float M, float L) {
+        emit_value<HD>(p, ooff, xch_step, row, d, O, M, L);
+    };
+                // Each thread owns column tid % HD of every row. Rows are taken
+    // four at a time and contributors four at a time, so that all of
+    // a batch's loads are in flight together: with at most four
+    // contributors (the usual case) the whole merge is one trip to
+    // L2. m and l are read by every thread (a broadcast), so no
+    // exchange through shared memory is needed.
+    const int d = tid % HD;
+    for (int r0 = 0; r0 < rows_here; r0 += 4) {
+        float Mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+        if (count > 4) {
+            for (int c0 = c_first; c0 <= c_last; c0 += 8) {
+                float mi[4][8];
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const int cc = min(c0 + e, c_last);
+                        const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
+                        const int row = min(r0 + rr, rows_here - 1);
+                        mi[rr][e] = ldcg(p.part + (((size_t)cc * 2 + sl) * kRows + row) *
+                                                      (HD + 2) + HD);
+                    }
+                }
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) Mx[rr] = fmaxf(Mx[rr], mi[rr][e]);
+                }
+            }
+        }
+        float Ox[4] = {0.0f, 0.0f, 0.0f, 0.0f}, Lx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+            float mi[4][4], li[4][4], oi[4][4];
+#pragma unroll
+            for (int rr = 0; rr < 4; rr++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int cc = min(c0 + e, c_last);
+                    const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
+                    const int row = min(r0 + rr, rows_here - 1);
+                    const float *pr =
+                        p.part + (((size_t)cc * 2 + sl) * kRows + row) * (HD + 2);
+                    mi[rr][e] = ldcg(pr + HD);
+                    li[rr][e] = ldcg(pr + HD + 1);
+                    oi[rr][e] = ldcg(pr + d);
+                }
+            }
+            if (count <= 4) {
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) Mx[rr] = fmaxf(Mx[rr], mi[rr][e]);
+                }
+            }
+#pragma unroll
+            for (int rr = 0; rr < 4; rr++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    if (c0 + e <= c_last) {
+                        const float f = (mi[rr][e] == -CUDART_INF_F)
+                                            ? 0.0f
+                                            : ex2(mi[rr][e] - Mx[rr]);
+                        Ox[rr] += f * oi[rr][e];
+                        Lx[rr] += f * li[rr][e];
+                    }
+                }
+            }
+        }
+        if (tid < HD) {
+#pragma unroll
+            for (int rr = 0; rr < 4; rr++) {
+                if (r0 + rr < rows_here) emit(r0 + rr, d, Ox[rr], Mx[rr], Lx[rr]);
+            }
+        }
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
@@ -340,31 +462,8 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         float *part = p.part + ((size_t)blockIdx.x * 2 + slot) * kRows * (HD + 2);
         const long long ooff = (long long)b * p.out_seq + (long long)kh * p.out_kv +
                                (long long)(rc * kRows) * p.out_row;
-        // One finished value of the pair: normalised into `out`, or the
-        // un-normalised triple - into `out`, or, when ranks exchange, straight
-        // into every rank's gather buffer over NVLink (this rank's included).
         auto emit = [&](int row, int d, float O, float M, float L) {
-            const long long at = ooff + (long long)row * p.out_row;
-            if (!p.partial) {
-                p.out[at + d] = L > 0.0f ? O / L : 0.0f;
-            } else if (p.xch_world == 0) {
-                p.out[at + d] = O;
-                if (d == 0) {
-                    p.out[at + HD] = M * kLn2;
-                    p.out[at + HD + 1] = L;
-                }
-            } else {
-                const long long slot_at =
-                    ((long long)(xch_step & 1u) * p.xch_world + p.xch_rank) * p.xch_rank_stride + at;
-                for (int r = 0; r < p.xch_world; r++) {
-                    float *dst = p.xch_gather[r] + slot_at;
-                    dst[d] = O;
-                    if (d == 0) {
-                        dst[HD] = M * kLn2;
-                        dst[HD + 1] = L;
-                    }
-                }
-            }
+            emit_value<HD>(p, ooff, xch_step, row, d, O, M, L);
         };
         // After a pair's values are out: count it, and the block that finishes
         // the launch's last pair raises this rank's flag on every rank.
@@ -425,47 +524,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             __syncthreads();
             if (sm_last) {
                 __threadfence();
-                if (tid < rows_here) {
-                    float M = -CUDART_INF_F;
-#pragma unroll 4
-                    for (int cc = c_first; cc <= c_last; cc++) {
-                        const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
-                        const float *pr =
-                            p.part + (((size_t)cc * 2 + sl) * kRows + tid) * (HD + 2);
-                        M = fmaxf(M, ldcg(pr + HD));
-                    }
-                    sm_M[tid] = M;
-                }
-                __syncthreads();
-                // Each thread owns column tid of every row, and a row's loads are
-                // all issued before any is used: the merge costs a trip to L2
-                // per eight partials rather than one per value.
-                for (int row = 0; row < rows_here; row++) {
-                    const float M = sm_M[row];
-                    float O = 0.0f, L = 0.0f;
-                    for (int c0 = c_first; c0 <= c_last; c0 += 8) {
-                        float mi[8], oi[8], li[8];
-#pragma unroll
-                        for (int e = 0; e < 8; e++) {
-                            const int cc = min(c0 + e, c_last);
-                            const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
-                            const float *pr =
-                                p.part + (((size_t)cc * 2 + sl) * kRows + row) * (HD + 2);
-                            mi[e] = ldcg(pr + HD);
-                            li[e] = ldcg(pr + HD + 1);
-                            oi[e] = ldcg(pr + tid % HD);
-                        }
-#pragma unroll
-                        for (int e = 0; e < 8; e++) {
-                            if (c0 + e <= c_last) {
-                                const float f = (mi[e] == -CUDART_INF_F) ? 0.0f : ex2(mi[e] - M);
-                                O += f * oi[e];
-                                L += f * li[e];
-                            }
-                        }
-                    }
-                    if (tid < HD) emit(row, tid, O, M, L);
-                }
+                merge_pair<HD>(p, pair_u0, c_first, c_last, rows_here, W, G, ooff, xch_step);
                 pair_done();
                 if (tid == 0) p.ctr[pair] = 0u;   // at rest again for the next call
             }
