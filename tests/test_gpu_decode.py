@@ -190,3 +190,63 @@ def test_partial_triples_merge_to_the_whole(gpu):
                         parts * per, scale, False)
     assert_parity("merged partials", want, merged)
     assert_close_to("merged partials", want, merged, 2e-5)
+
+
+def test_peer_push_exchange_on_one_device(gpu):
+    """The fused multi-GPU exchange, with both "ranks" on one device: each rank
+    decodes its slice of the keys and pushes its triples into every rank's
+    gather buffer (here: two buffers in the same memory), then each rank's
+    waiting merge runs. The kernels are enqueued one after another on one
+    stream, so every flag a merge waits for was raised by a kernel that has
+    already finished. Two steps, to use both gather buffers."""
+    import torch
+
+    from ttsxabe_b200 import DecodeScratch, Exchange
+
+    heads, kv, hd, batch, world = 32, 8, 128, 3, 2
+    rows = batch * heads
+    rng = np.random.default_rng(91)
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    per = [1000, 1536]                     # keys held by rank 0 and rank 1
+    caps = [1024, 1536]
+    kfull = [normal_f16(rng, kv * sum(per) * hd).reshape(kv, sum(per), hd) for _ in range(batch)]
+    vfull = [normal_f16(rng, kv * sum(per) * hd).reshape(kv, sum(per), hd) for _ in range(batch)]
+    with torch.cuda.stream(gpu.stream):
+        gathers = [torch.zeros(2 * world * rows * (hd + 2), dtype=torch.float32, device=gpu.device)
+                   for _ in range(world)]
+        flags = [torch.zeros(64, dtype=torch.int32, device=gpu.device) for _ in range(world)]
+        steps = [torch.zeros(1, dtype=torch.int32, device=gpu.device) for _ in range(world)]
+    xchs = [Exchange(world, r, [g_.data_ptr() for g_ in gathers], [f.data_ptr() for f in flags],
+                     steps[r].data_ptr()) for r in range(world)]
+    caches = []
+    for r in range(world):
+        t0 = sum(per[:r])
+        ks, vs = [], []
+        for b in range(batch):
+            kc = np.zeros((kv, caps[r], hd), np.float32)
+            vc = np.zeros((kv, hd, caps[r]), np.float32)
+            kc[:, :per[r], :] = kfull[b][:, t0:t0 + per[r], :]
+            vc[:, :, :per[r]] = vfull[b][:, t0:t0 + per[r], :].transpose(0, 2, 1)
+            ks.append(gpu.upload_u16(O.round_f16(kc)))
+            vs.append(gpu.upload_u16(O.round_f16(vc)))
+        caches.append((ks, vs))
+    scratch = [DecodeScratch() for _ in range(world)]
+    for step in range(2):
+        q = normal_f16(rng, batch * heads * hd)
+        dq = gpu.upload(q)
+        for r in range(world):
+            gpu.decode_batched_push(dq, caches[r][0], caches[r][1], [per[r]] * batch,
+                                    [caps[r]] * batch, heads, kv, hd, scale, False, scratch[r],
+                                    xchs[r])
+        outs = [gpu.download(gpu.lse_merge_wait(xchs[r], rows, hd)) for r in range(world)]
+        assert np.array_equal(outs[0], outs[1]), "both ranks must merge to the same context"
+        for b in range(batch):
+            kc = np.ascontiguousarray(kfull[b])
+            vc = np.ascontiguousarray(vfull[b].transpose(0, 2, 1))
+            want = O.decode_f64(q.reshape(batch, -1)[b], O.round_f16(kc), O.round_f16(vc), heads,
+                                kv, hd, 0, sum(per), sum(per), scale, False)
+            assert_parity(f"peer push step {step} sequence {b}", want,
+                          outs[0].reshape(batch, -1)[b])
+            assert_close_to(f"peer push step {step} sequence {b}", want,
+                            outs[0].reshape(batch, -1)[b], 2e-5)
+        assert int(steps[0].item()) == step + 1 and int(steps[1].item()) == step + 1
