@@ -78,7 +78,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -216,13 +216,14 @@ def decode128k(args, world, rank, local):
         q = torch.randn(batch * HEADS * HD, generator=gen, device=gpu.device)
         q = q.to(torch.float16).to(torch.float32)
     sd = ShardedDecode.on_gpu(gpu, ks, vs, [tk] * batch, [cap] * batch, HEADS, KV_HEADS, HD,
-                              SCALE, p2p=not args.nccl)
+                              SCALE, p2p=False if args.exchange == "nccl" else args.exchange)
     gpu.synchronize()
 
     # The sharded paths have no single-GPU test to stand on, so the fused
     # exchange is checked here against the all-gather path on the same inputs.
     exchange_err = None
-    if world > 1 and not args.nccl:
+    fused_exchange = sd.exchange.startswith("peer-")
+    if fused_exchange:
         ref = ShardedDecode.on_gpu(gpu, ks, vs, [tk] * batch, [cap] * batch, HEADS, KV_HEADS, HD,
                                    SCALE, p2p=False)
         a = sd.decode(q).clone()
@@ -258,24 +259,22 @@ def decode128k(args, world, rank, local):
 
     # ---- end to end through the C ABI with host buffers ------------------------
     nq, nkv = HEADS * HD, KV_HEADS * HD
-    hq = torch.randn(batch * nq).to(torch.float16).to(torch.float32).pin_memory()
-    hk = torch.randn(batch * nkv).pin_memory()
-    hv = torch.randn(batch * nkv).pin_memory()
+    # one pinned staging buffer [q | k | v], so the step's inputs are one copy
+    hqkv = torch.randn(batch * (nq + 2 * nkv)).pin_memory()
+    hqkv[:batch * nq] = hqkv[:batch * nq].to(torch.float16).to(torch.float32)
     hout = torch.empty(batch * nq).pin_memory()
     dqkv = gpu.uninit(batch * (nq + 2 * nkv))
+    dq = dqkv[:batch * nq]
+    dk = dqkv[batch * nq:batch * (nq + nkv)]
+    dv = dqkv[batch * (nq + nkv):]
     lib, h = gpu._lib, gpu._h
     pos = tk - 1          # the step's new token lands in the last cache slot
     esz = 4
 
     def e2e_step():
-        lib.llmtie_upload(h, dqkv.data_ptr(), hq.data_ptr(), batch * nq * esz)
-        lib.llmtie_upload(h, dqkv.data_ptr() + batch * nq * esz, hk.data_ptr(), batch * nkv * esz)
-        lib.llmtie_upload(h, dqkv.data_ptr() + batch * (nq + nkv) * esz, hv.data_ptr(),
-                          batch * nkv * esz)
-        for b in range(batch):
-            gpu.rope_cache_f16([dqkv], (0, b * nq), (0, batch * nq + b * nkv),
-                               (0, batch * (nq + nkv) + b * nkv), None, HEADS, KV_HEADS, HD,
-                               10000.0, pos, ks[b], vs[b], cap)
+        lib.llmtie_upload(h, dqkv.data_ptr(), hqkv.data_ptr(), batch * (nq + 2 * nkv) * esz)
+        gpu.rope_cache_batched(dq, dk, dv, None, HEADS, KV_HEADS, HD, 10000.0, [pos] * batch,
+                               ks, vs, [cap] * batch)
         out = sd.decode(dqkv)          # q is the first batch*nq floats
         lib.llmtie_download(h, hout.data_ptr(), out.data_ptr(), batch * nq * esz)
 
@@ -326,8 +325,11 @@ def decode128k(args, world, rank, local):
         },
         "gpu_launches": int(launches),
         "cuda_graph": bool(world > 1 and not args.no_graph),
-        "exchange": ("none" if world == 1 else "nccl all-gather" if args.nccl
-                     else "peer-memory push fused into the decode kernel"),
+        "exchange": {"none": "none", "all-gather": "nccl all-gather",
+                     "peer-push": "peer-memory push fused into the decode kernel, merge in a "
+                                  "second waiting kernel",
+                     "peer-fused": "peer-memory push, wait and merge all fused into the decode "
+                                   "kernel"}[sd.exchange],
         "exchange_max_abs_vs_allgather": exchange_err,
         "roofline": {
             "bound": "hbm",
@@ -338,7 +340,7 @@ def decode128k(args, world, rank, local):
             "traffic": (None if NCU_TRAFFIC["decode128k"] is None
                         else NCU_TRAFFIC["decode128k"] * kv_bytes_rank),
             "peak_source": "of " + which,
-            "kernel": "decode_f16_kernel<128>",
+            "kernel": "decode_stream_kernel<128>",
             "kernel_ms": ksecs / args.steps * 1e3,
             "algorithmic_bytes_per_launch": kv_bytes_rank,
             "frac_of_nominal_8tbs": achieved / 8000.0,
@@ -595,8 +597,8 @@ def reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k",
                     choices=["decode128k", "prefill8k", "configs"])
@@ -604,12 +606,16 @@ def main():
     ap.add_argument("--context", type=int, default=131072)
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--nccl", action="store_true",
-                    help="exchange the triples with an NCCL all-gather instead of the fused "
-                         "peer-memory push")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "push", "nccl"],
+                    help="how the ranks exchange their triples: everything in the decode "
+                         "kernel over peer memory (fused), the push in the kernel and the merge "
+                         "in a second waiting kernel (push), or an NCCL all-gather (nccl)")
+    ap.add_argument("--nccl", action="store_true", help="the same as --exchange nccl")
     ap.add_argument("--no-graph", action="store_true",
                     help="time the sharded step as separate host calls, not a CUDA graph")
     args = ap.parse_args()
+    if args.nccl:
+        args.exchange = "nccl"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     if args.impl == "reference":

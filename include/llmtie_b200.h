@@ -137,6 +137,18 @@ llmtie_status llmtie_rope_cache_f16(llmtie_gpu *g, float *q, size_t q_len, size_
                                     uint16_t *kc, size_t kc_len, uint16_t *vc,
                                     size_t vc_len, size_t cap);
 
+/* Gpu::rope_cache_f16 for `batch` sequences decoding together, one launch:
+ * what crates/llmtie-translate/src/model.rs:824-846 does as a loop. q f32
+ * [batch][heads*hd] is rotated in place; k and v f32 [batch][kv_heads*hd]
+ * go to each sequence's own caches at pos[b]. pos, cap, kc_ptrs and vc_ptrs
+ * are HOST arrays of `batch`. Bit for bit the single-sequence entry. */
+llmtie_status llmtie_rope_cache_batched(llmtie_gpu *g, float *q, size_t q_len, const float *k,
+                                        size_t k_len, const float *v, size_t v_len,
+                                        const float *freq_div, size_t batch, size_t heads,
+                                        size_t kv_heads, size_t head_dim, float theta,
+                                        const int32_t *pos, uint16_t *const *kc_ptrs,
+                                        uint16_t *const *vc_ptrs, const int32_t *cap);
+
 /* ---- prefill / encoder attention ------------------------------------------- */
 
 /* Gpu::supports_flash (device.rs:5697-5699). */
@@ -274,6 +286,28 @@ llmtie_status llmtie_decode_batched_push(llmtie_gpu *g, const float *q, size_t q
                                          const llmtie_exchange *xch);
 llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_exchange *xch, size_t rows,
                                     size_t head_dim, float *out, size_t out_len);
+/* The whole sharded step in ONE kernel (no counterpart in the reference):
+ * llmtie_decode_batched_push with the merge fused in as well. The block that
+ * finishes a (sequence, KV head) pair on this rank stores the pair's triple
+ * into every rank's gather buffer and raises that pair's flag there;
+ * before it exits it waits (bounded: about a second, then LLMTIE_ERR_TIMEOUT
+ * at the next synchronize) for the other ranks' flags of the same pair and
+ * merges the pair into out f32 [batch][heads*hd], normalised. So the cross-
+ * rank merge of early pairs overlaps the streaming of later ones, and only
+ * the last pairs' exchange is exposed. xch->flags is unused; pair_flags is a
+ * HOST array of `world` device pointers, each rank's [batch*kv_heads][world]
+ * words, zero before the first step. gather and step as for the push entry.
+ * A world of one rank is allowed (the rank merges its own triples). All
+ * ranks must make the same sequence of calls; at most 32 sequences a call. */
+llmtie_status llmtie_decode_batched_fused(llmtie_gpu *g, const float *q, size_t q_len,
+                                          const uint16_t *const *k_ptrs,
+                                          const uint16_t *const *v_ptrs, const int32_t *tk,
+                                          const int32_t *cap, size_t batch, size_t heads,
+                                          size_t kv_heads, size_t head_dim, float scale,
+                                          int32_t scale_q, llmtie_decode_scratch *scratch,
+                                          const llmtie_exchange *xch,
+                                          uint32_t *const *pair_flags, float *out,
+                                          size_t out_len);
 /* AsrModel::attend (crates/llmtie-asr/src/model.rs:573-641) fused: n query
  * rows (q f32 [n][heads*hd], scale applied to q) over f16 cross caches
  * K [heads][cap][hd], V [heads][hd][cap] with tk live keys, non-causal;

@@ -250,3 +250,44 @@ def test_peer_push_exchange_on_one_device(gpu):
             assert_close_to(f"peer push step {step} sequence {b}", want,
                             outs[0].reshape(batch, -1)[b], 2e-5)
         assert int(steps[0].item()) == step + 1 and int(steps[1].item()) == step + 1
+
+
+@pytest.mark.parametrize("shape", [
+    # heads, kv, hd, batch, contexts
+    (32, 8, 128, 3, [1000, 4096, 37]),
+    (128, 128, 64, 32, [100] * 32),      # ~27 pairs a block: more than a block's list holds
+])
+def test_fused_exchange_with_a_world_of_one(gpu, shape):
+    """The one-kernel sharded step with a single rank: the kernel pushes its
+    triples into its own gather buffer, raises its own pair flags, waits for
+    them and merges. Nothing waits on another launch. Must equal the plain
+    decode of the same caches; two steps, to use both gather buffers."""
+    import torch
+
+    from ttsxabe_b200 import DecodeScratch, Exchange
+
+    heads, kv, hd, batch, tks = shape
+    rows = batch * heads
+    rng = np.random.default_rng(17)
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    caps = [-(-t // 8) * 8 for t in tks]
+    ks = [gpu.upload_u16(O.round_f16(normal_f16(rng, kv * c * hd))) for c in caps]
+    vs = [gpu.upload_u16(O.round_f16(normal_f16(rng, kv * c * hd))) for c in caps]
+    with torch.cuda.stream(gpu.stream):
+        gather = torch.zeros(2 * rows * (hd + 2), dtype=torch.float32, device=gpu.device)
+        flags = torch.zeros(64, dtype=torch.int32, device=gpu.device)
+        pflags = torch.zeros(batch * kv, dtype=torch.int32, device=gpu.device)
+        step = torch.zeros(1, dtype=torch.int32, device=gpu.device)
+    xch = Exchange(1, 0, [gather.data_ptr()], [flags.data_ptr()], step.data_ptr(),
+                   [pflags.data_ptr()])
+    scratch, plain = DecodeScratch(), DecodeScratch()
+    for s in range(2):
+        dq = gpu.upload(normal_f16(rng, batch * heads * hd))
+        got = gpu.download(gpu.decode_batched_fused(dq, ks, vs, tks, caps, heads, kv, hd, scale,
+                                                    False, scratch, xch))
+        want = gpu.download(gpu.decode_batched(dq, ks, vs, tks, caps, heads, kv, hd, scale,
+                                               False, plain))
+        gpu.synchronize()
+        assert_close_to(f"fused step {s}", want, got, 1e-5)
+        assert int(step.item()) == s + 1
+        assert int(pflags.min().item()) == s + 1

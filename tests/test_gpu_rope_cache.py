@@ -138,6 +138,39 @@ def test_rope_cache_f16_is_the_four_launch_chain(gpu):
         assert np.abs(dk - O.widen_f16(okc)).max() <= 2e-3   # one f16 ulp at |x| < 4
 
 
+def test_batched_rope_cache_is_the_single_sequence_entry_bit_for_bit(gpu):
+    """One launch over several sequences with their own caches, positions and
+    capacities equals one rope_cache_f16 call per sequence
+    (the loop of crates/llmtie-translate/src/model.rs:824-846)."""
+    heads, kv, hd = 8, 2, 64
+    nq, nk = heads * hd, kv * hd
+    caps, poss = [32, 64, 48, 16], [31, 0, 17, 9]
+    batch = len(caps)
+    q, k, v = O.seq(batch * nq, 61), O.seq(batch * nk, 62), O.seq(batch * nk, 63)
+    pats = [(O.round_f16(O.seq(kv * c * hd, 70 + i)), O.round_f16(O.seq(kv * c * hd, 80 + i)))
+            for i, c in enumerate(caps)]
+    for div in (None, LLAMA3_DIV[:hd // 2]):
+        ddiv = None if div is None else gpu.upload(div)
+        dq, dk, dv = gpu.upload(q), gpu.upload(k), gpu.upload(v)
+        kcs = [gpu.upload_u16(p[0]) for p in pats]
+        vcs = [gpu.upload_u16(p[1]) for p in pats]
+        gpu.rope_cache_batched(dq, dk, dv, ddiv, heads, kv, hd, 10000.0, poss, kcs, vcs, caps)
+        one = [gpu.upload(q), gpu.upload(k), gpu.upload(v)]
+        kcs1 = [gpu.upload_u16(p[0]) for p in pats]
+        vcs1 = [gpu.upload_u16(p[1]) for p in pats]
+        for b in range(batch):
+            gpu.rope_cache_f16(one, (0, b * nq), (1, b * nk), (2, b * nk), ddiv, heads, kv, hd,
+                               10000.0, poss[b], kcs1[b], vcs1[b], caps[b])
+        assert np.array_equal(gpu.download(dq), gpu.download(one[0]))
+        assert np.array_equal(gpu.download(dk), k)      # keys are not rotated in place
+        for b in range(batch):
+            assert np.array_equal(gpu.download_u16(kcs[b]), gpu.download_u16(kcs1[b]))
+            assert np.array_equal(gpu.download_u16(vcs[b]), gpu.download_u16(vcs1[b]))
+    with pytest.raises(Exception):
+        gpu.rope_cache_batched(dq, dk, dv, None, heads, kv, hd, 10000.0, [32, 0, 0, 0], kcs, vcs,
+                               caps)
+
+
 @pytest.mark.parametrize("transposed", [False, True])
 def test_growing_a_cache_restrides_every_head(gpu, transposed):
     live, kv, hd, small, large = 5, 3, 4, 8, 16

@@ -44,6 +44,8 @@ PROTOTYPES = {
         i32,
         [vp, vp, sz, sz, vp, sz, sz, vp, sz, sz, vp, sz, sz, sz, f32, sz, vp, sz, vp, sz, sz],
     ),
+    "llmtie_rope_cache_batched": (
+        i32, [vp, vp, sz, vp, sz, vp, sz, vp, sz, sz, sz, sz, f32, pi32, pvp, pvp, pi32]),
     "llmtie_supports_flash": (i32, [sz, sz, sz]),
     "llmtie_flash_attn_f16": (
         i32, [vp, vp, sz, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, sz, f32, i32]),
@@ -64,6 +66,8 @@ PROTOTYPES = {
     "llmtie_lse_merge": (i32, [vp, vp, sz, sz, sz, sz, vp, sz]),
     "llmtie_decode_batched_push": (
         i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp]),
+    "llmtie_decode_batched_fused": (
+        i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp, pvp, vp, sz]),
     "llmtie_lse_merge_wait": (i32, [vp, vp, sz, sz, vp, sz]),
     "llmtie_cross_attn": (
         i32, [vp, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, vp, vp, sz]),

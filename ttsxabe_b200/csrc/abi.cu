@@ -448,6 +448,61 @@ extern "C" llmtie_status llmtie_rope_cache_f16(llmtie_gpu *g, float *q, size_t q
     return ls.done();
 }
 
+extern "C" llmtie_status llmtie_rope_cache_batched(
+    llmtie_gpu *g, float *q, size_t q_len, const float *k, size_t k_len, const float *v,
+    size_t v_len, const float *freq_div, size_t batch, size_t heads, size_t kv_heads,
+    size_t head_dim, float theta, const int32_t *pos, uint16_t *const *kc_ptrs,
+    uint16_t *const *vc_ptrs, const int32_t *cap)
+{
+    NEED_HANDLE(g);
+    if (!pos || !kc_ptrs || !vc_ptrs || !cap) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "null sequence table");
+    }
+    if (head_dim % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_HEAD_DIM, "a rotary head of odd width %zu", head_dim);
+    }
+    if (q_len < batch * heads * head_dim) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           batch * heads * head_dim, q_len);
+    }
+    if (k_len < batch * kv_heads * head_dim || v_len < batch * kv_heads * head_dim) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           batch * kv_heads * head_dim, std::min(k_len, v_len));
+    }
+    for (size_t b = 0; b < batch; b++) {
+        if (cap[b] <= 0 || cap[b] % 2 != 0) {
+            return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                               "an f16 cache with an odd capacity of %d", cap[b]);
+        }
+        if (pos[b] < 0 || pos[b] >= cap[b]) {
+            return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                               "appending at %d to a cache with room for %d", pos[b] + 1, cap[b]);
+        }
+    }
+    for (size_t b0 = 0; b0 < batch; b0 += 32) {
+        const size_t nb = std::min<size_t>(32, batch - b0);
+        RopeBatchParams p;
+        memset(&p, 0, sizeof(p));
+        p.nseq = (int)nb;
+        for (size_t b = 0; b < nb; b++) {
+            p.seq[b] = {kc_ptrs[b0 + b], vc_ptrs[b0 + b], pos[b0 + b], cap[b0 + b]};
+        }
+        p.q = q + b0 * heads * head_dim;
+        p.k = k + b0 * kv_heads * head_dim;
+        p.v = v + b0 * kv_heads * head_dim;
+        p.freq_div = freq_div;
+        p.heads = (int)heads;
+        p.kv_heads = (int)kv_heads;
+        p.hd = (int)head_dim;
+        p.theta = theta;
+        LaunchScope ls(g, "rope_cache_f16");
+        launch_rope_cache_batched(g->stream, p);
+        const llmtie_status s = ls.done();
+        if (s != LLMTIE_OK) return s;
+    }
+    return LLMTIE_OK;
+}
+
 // ---- prefill / encoder attention -----------------------------------------------
 
 extern "C" int32_t llmtie_supports_flash(size_t head_dim, size_t heads, size_t kv_heads)
@@ -735,9 +790,17 @@ static void decode_plan(llmtie_gpu *g, DecodeParams &p, int hd)
     p.max_splits = (max_tk + p.span - 1) / p.span;
 }
 
+// What the fused exchange adds to an exchange descriptor: every rank's pair
+// flags and where this rank's merged rows go.
+struct FusedMerge {
+    uint32_t *const *pair_flags;
+    float *out;
+};
+
 static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams &p, int hd,
                                    llmtie_decode_scratch *scratch,
-                                   const llmtie_exchange *xch = nullptr)
+                                   const llmtie_exchange *xch = nullptr,
+                                   const FusedMerge *fused = nullptr)
 {
     bool aligned = true;
     for (int b = 0; b < p.nseq; b++) {
@@ -783,8 +846,8 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         // One block per SM, but never fewer than four units (512 keys) a block:
         // a short context cut any finer spends longer merging partials than
         // it saved streaming them.
-        const int grid =
-            (int)std::min<long long>(g->sm_count, std::max<long long>(1, units / 4));
+        const int grid = (int)std::min<long long>(
+            std::min(g->sm_count, LLMTIE_STREAM_MAX_BLOCKS), std::max<long long>(1, units / 4));
         const size_t pairs = (size_t)p.nseq * inner;
         const llmtie_status s =
             scratch_reserve(g, scratch, pairs + 1, (size_t)grid * 2, (size_t)hd);
@@ -802,6 +865,12 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
             sp.xch_done = scratch->ctr + pairs;   // one more counter after the pairs'
             sp.xch_pairs = (int)pairs;
             sp.xch_rank_stride = (long long)p.nseq * p.out_seq;
+            if (fused) {
+                sp.xch_fused = 1;
+                for (int r = 0; r < xch->world; r++) sp.xch_pflags[r] = fused->pair_flags[r];
+                sp.xch_out = fused->out;
+                sp.xch_status = g->timeout_flag;
+            }
         }
         LaunchScope ls(g, name);
         const cudaError_t e = launch_decode_stream(g->stream, sp, hd, grid);
@@ -950,7 +1019,8 @@ static llmtie_status decode_batched_impl(llmtie_gpu *g, const float *q, size_t q
                                          size_t kv_heads, size_t head_dim, float scale,
                                          int32_t scale_q, llmtie_decode_scratch *scratch,
                                          float *out, size_t out_len, int32_t partial,
-                                         const llmtie_exchange *xch)
+                                         const llmtie_exchange *xch,
+                                         const FusedMerge *fused = nullptr)
 {
     NEED_HANDLE(g);
     if (!scratch) return llmtie_fail(LLMTIE_ERR_INVALID, "null decode scratch");
@@ -972,8 +1042,10 @@ static llmtie_status decode_batched_impl(llmtie_gpu *g, const float *q, size_t q
                            batch * on, out_len);
     }
     if (xch) {
-        if (xch->world < 2 || xch->world > LLMTIE_MAX_RANKS || xch->rank < 0 ||
-            xch->rank >= xch->world || !xch->gather || !xch->flags || !xch->step) {
+        // (a world of one rank is a valid fused exchange: the rank merges its own triple)
+        if (xch->world < (fused ? 1 : 2) || xch->world > LLMTIE_MAX_RANKS || xch->rank < 0 ||
+            xch->rank >= xch->world || !xch->gather || !xch->step ||
+            (fused ? !fused->pair_flags || !fused->out : !xch->flags)) {
             return llmtie_fail(LLMTIE_ERR_INVALID, "a malformed exchange descriptor");
         }
         if (batch > LLMTIE_DECODE_MAX_SEQ) {
@@ -1022,7 +1094,7 @@ static llmtie_status decode_batched_impl(llmtie_gpu *g, const float *q, size_t q
         p.sl2 = (scale_q ? 1.0f : scale) * kLog2e;
         const llmtie_status s = decode_launch(
             g, head_dim == 128 ? "attn_decode_h128" : "attn_decode_h64", p, (int)head_dim,
-            scratch, xch);
+            scratch, xch, fused);
         if (s != LLMTIE_OK) return s;
     }
     return LLMTIE_OK;
@@ -1049,6 +1121,23 @@ extern "C" llmtie_status llmtie_decode_batched_push(
     if (!xch) return llmtie_fail(LLMTIE_ERR_INVALID, "null exchange descriptor");
     return decode_batched_impl(g, q, q_len, k_ptrs, v_ptrs, tk, cap, batch, heads, kv_heads,
                                head_dim, scale, scale_q, scratch, nullptr, 0, 1, xch);
+}
+
+extern "C" llmtie_status llmtie_decode_batched_fused(
+    llmtie_gpu *g, const float *q, size_t q_len, const uint16_t *const *k_ptrs,
+    const uint16_t *const *v_ptrs, const int32_t *tk, const int32_t *cap, size_t batch,
+    size_t heads, size_t kv_heads, size_t head_dim, float scale, int32_t scale_q,
+    llmtie_decode_scratch *scratch, const llmtie_exchange *xch, uint32_t *const *pair_flags,
+    float *out, size_t out_len)
+{
+    if (!xch) return llmtie_fail(LLMTIE_ERR_INVALID, "null exchange descriptor");
+    if (out_len < batch * heads * head_dim) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           batch * heads * head_dim, out_len);
+    }
+    const FusedMerge fused = {pair_flags, out};
+    return decode_batched_impl(g, q, q_len, k_ptrs, v_ptrs, tk, cap, batch, heads, kv_heads,
+                               head_dim, scale, scale_q, scratch, nullptr, 0, 1, xch, &fused);
 }
 
 extern "C" llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_exchange *xch,

@@ -61,6 +61,22 @@ void launch_rope_cache_f16(cudaStream_t st, float *q, long long q_off, const flo
                            long long k_off, const float *v, long long v_off,
                            const float *freq_div, int heads, int kv_heads, int hd,
                            float theta, int pos, uint16_t *kc, uint16_t *vc, int cap);
+struct RopeBatchSeq {
+    uint16_t *kc;
+    uint16_t *vc;
+    int pos, cap;
+};
+struct RopeBatchParams {
+    RopeBatchSeq seq[32];
+    int nseq;
+    float *q;              // [nseq][heads*hd], rotated in place
+    const float *k;        // [nseq][kv_heads*hd]
+    const float *v;
+    const float *freq_div;
+    int heads, kv_heads, hd;
+    float theta;
+};
+void launch_rope_cache_batched(cudaStream_t st, const RopeBatchParams &p);
 void launch_cache_append(cudaStream_t st, const float *src, long long src_off, void *dst,
                          int n, int kv_heads, int hd, int cap, int past, bool transposed,
                          bool f16);
@@ -109,8 +125,10 @@ cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd);
 int decode_resident_blocks(int hd, int sm_count, int nb);
 #define LLMTIE_MAX_RANKS 8
 // decode_stream.cu: the same operands cut over the grid by work (see there).
+#define LLMTIE_STREAM_MAX_BLOCKS 160
 struct DecodeStreamParams {
     DecodeSeq seq[LLMTIE_DECODE_MAX_SEQ];
+    int ustart[LLMTIE_STREAM_MAX_BLOCKS + 1];     // block c takes units [ustart[c], ustart[c+1])
     long long unit0[LLMTIE_DECODE_MAX_SEQ + 1];   // first 128-key unit of each sequence
     int pair0[LLMTIE_DECODE_MAX_SEQ + 1];         // first (row chunk, kv head) pair of each
     long long total_units;
@@ -132,6 +150,13 @@ struct DecodeStreamParams {
     unsigned *xch_done;                      // pairs finished in this launch, zero at rest
     int xch_pairs;                           // pairs in this launch
     long long xch_rank_stride;               // floats one rank's triples take
+    // Fused merge (xch_fused): the block that finishes a pair on this rank
+    // raises that pair's flag on every rank, and before it exits waits for the
+    // other ranks' flags of the pair and merges it into xch_out, normalised.
+    int xch_fused;
+    unsigned *xch_pflags[LLMTIE_MAX_RANKS];  // every rank's pair flags [pairs][world]
+    float *xch_out;                          // [rows][hd], this rank's merged result
+    int *xch_status;                         // set when a bounded wait gave up
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,

@@ -15,7 +15,8 @@
 // Why by work. One block per SM is resident (the ring is 192 KB), and a grid
 // cut by (sequence, KV head) leaves SMs idle whenever their count does not
 // divide 148. Instead all 128-key units of the launch are laid end to end,
-// pair after pair, and block c takes units [c W / G, (c + 1) W / G). A block
+// pair after pair, and block c takes a contiguous run of them (the host cuts
+// the runs, see stream_partition). A block
 // whose range covers a whole (sequence, KV head) pair writes its output
 // directly; a range that cuts a pair writes a partial (o, m, l), and the last
 // block of that pair to arrive merges (crates/llmtie-cuda/src/kernels.rs:
@@ -60,11 +61,6 @@ __device__ __forceinline__ void lds128(uint32_t (&r)[4], const void *smem)
                  : "r"(a));
 }
 
-// A load that bypasses L1 (the partials were written by other blocks). Not
-// volatile on purpose: the merge issues many of these and they must be free
-// to overlap; the fence and barrier before the merge keep them in place.
-__device__ __forceinline__ float ldcg(const float *p) { return __ldcg(p); }
-
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1)
 {
@@ -90,11 +86,20 @@ __device__ __forceinline__ void split_pair(float x0, float x1, uint32_t &hi, uin
     lo = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
 }
 
-// The block that holds unit u when W units are cut over G blocks as
-// [c W / G, (c + 1) W / G): the largest c with floor(c W / G) <= u.
-__device__ __forceinline__ int covering(long long u, long long W, long long G)
+// The block whose run holds unit u: the largest c with ustart[c] <= u. The
+// runs are strictly increasing, so it is unique.
+__device__ __forceinline__ int block_of(const int *ustart, int u, int G)
 {
-    return (int)(((u + 1) * G + W - 1) / W - 1);
+    int lo = 0, hi = G - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (ustart[mid] <= u) {
+            lo = mid;
+        } else {
+            hi = mid - 1;
+        }
+    }
+    return lo;
 }
 
 // One finished value of a pair: normalised into `out`, or the un-normalised
@@ -132,90 +137,187 @@ __device__ __forceinline__ void emit_value(const DecodeStreamParams &p, long lon
 // The last block of a pair to arrive merges every partial of the pair. Kept
 // out of line: its register needs must not shape the allocation of the key
 // loop, which is what the kernel's bandwidth hangs on.
+//
+// The partials are brought into the (now idle) ring with asynchronous copies,
+// every one of them in flight at once, so the merge costs one trip to L2
+// however many blocks contributed; cp.async.cg reads L2, where the other
+// blocks' stores are after their fences. Up to kMergeBatch contributors fit
+// the ring at a time; more are folded in batch after batch under a running
+// maximum.
 template <int HD>
-__device__ __noinline__ void merge_pair(const DecodeStreamParams &p, long long pair_u0,
-                                        int c_first, int c_last, int rows_here, long long W,
-                                        long long G, long long ooff, unsigned xch_step)
+__device__ __noinline__ void merge_pair(const DecodeStreamParams &p, unsigned char *stage,
+                                        const int *ustart, int pair_u0, int c_first, int c_last, int rows_here,
+                                        long long ooff, unsigned xch_step)
 {
+    constexpr int SLOT = kRows * (HD + 2);            // floats of one partial slot
+    constexpr int kMergeBatch = 32;
+    constexpr int RSTEP = kThreads / HD;              // rows a pass of the block covers
+    constexpr int RMAX = kRows / RSTEP;
+    static_assert(kMergeBatch * SLOT * 4 <= kWarps * kStages * (32 * HD * 2 + HD * 64),
+                  "a merge batch must fit the ring");
     const int tid = threadIdx.x;
-    const int count = c_last - c_first + 1;
-    auto emit = [&](int row, int d, float O, float M, float L) {
-        emit_value<HD>(p, ooff, xch_step, row, d, O, M, L);
-    };
-                // Each thread owns column tid % HD of every row. Rows are taken
-    // four at a time and contributors four at a time, so that all of
-    // a batch's loads are in flight together: with at most four
-    // contributors (the usual case) the whole merge is one trip to
-    // L2. m and l are read by every thread (a broadcast), so no
-    // exchange through shared memory is needed.
     const int d = tid % HD;
-    for (int r0 = 0; r0 < rows_here; r0 += 4) {
-        float Mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-        if (count > 4) {
-            for (int c0 = c_first; c0 <= c_last; c0 += 8) {
-                float mi[4][8];
+    const int rg = tid / HD;
+    const int chunks = (rows_here * (HD + 2) * 4 + 15) >> 4;   // 16-byte chunks a contributor
+    const float *st = (const float *)stage;
+
+    float Mx[RMAX], Ox[RMAX], Lx[RMAX];
 #pragma unroll
-                for (int rr = 0; rr < 4; rr++) {
+    for (int i = 0; i < RMAX; i++) {
+        Mx[i] = -CUDART_INF_F;
+        Ox[i] = 0.0f;
+        Lx[i] = 0.0f;
+    }
+    if (c_last - c_first < 4) {
+        // Up to four contributors (the usual case): every load straight into
+        // registers, all in flight together, and no pass through the ring.
+        const int count = c_last - c_first + 1;
+        const float *src[4];
 #pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        const int cc = min(c0 + e, c_last);
-                        const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
-                        const int row = min(r0 + rr, rows_here - 1);
-                        mi[rr][e] = ldcg(p.part + (((size_t)cc * 2 + sl) * kRows + row) *
-                                                      (HD + 2) + HD);
-                    }
-                }
+        for (int e = 0; e < 4; e++) {
+            const int cc = min(c_first + e, c_last);
+            const int sl = (ustart[cc] >= pair_u0) ? 0 : 1;
+            src[e] = p.part + ((size_t)cc * 2 + sl) * SLOT;
+        }
+        float mi[RMAX][4], li[RMAX][4], oi[RMAX][4];
 #pragma unroll
-                for (int rr = 0; rr < 4; rr++) {
+        for (int i = 0; i < RMAX; i++) {
+            const int row = min(rg + i * RSTEP, rows_here - 1);
 #pragma unroll
-                    for (int e = 0; e < 8; e++) Mx[rr] = fmaxf(Mx[rr], mi[rr][e]);
-                }
+            for (int e = 0; e < 4; e++) {
+                const float *pr = src[e] + row * (HD + 2);
+                mi[i][e] = __ldcg(pr + HD);
+                li[i][e] = __ldcg(pr + HD + 1);
+                oi[i][e] = __ldcg(pr + d);
             }
         }
-        float Ox[4] = {0.0f, 0.0f, 0.0f, 0.0f}, Lx[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int c0 = c_first; c0 <= c_last; c0 += 4) {
-            float mi[4][4], li[4][4], oi[4][4];
 #pragma unroll
-            for (int rr = 0; rr < 4; rr++) {
+        for (int i = 0; i < RMAX; i++) {
+            const int row = rg + i * RSTEP;
+            if (row < rows_here) {
+                float M = -CUDART_INF_F;
+#pragma unroll
+                for (int e = 0; e < 4; e++) M = fmaxf(M, mi[i][e]);   // repeats are harmless
+                float O = 0.0f, L = 0.0f;
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const int cc = min(c0 + e, c_last);
-                    const int sl = ((long long)cc * W / G >= pair_u0) ? 0 : 1;
-                    const int row = min(r0 + rr, rows_here - 1);
-                    const float *pr =
-                        p.part + (((size_t)cc * 2 + sl) * kRows + row) * (HD + 2);
-                    mi[rr][e] = ldcg(pr + HD);
-                    li[rr][e] = ldcg(pr + HD + 1);
-                    oi[rr][e] = ldcg(pr + d);
-                }
-            }
-            if (count <= 4) {
-#pragma unroll
-                for (int rr = 0; rr < 4; rr++) {
-#pragma unroll
-                    for (int e = 0; e < 4; e++) Mx[rr] = fmaxf(Mx[rr], mi[rr][e]);
-                }
-            }
-#pragma unroll
-            for (int rr = 0; rr < 4; rr++) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    if (c0 + e <= c_last) {
-                        const float f = (mi[rr][e] == -CUDART_INF_F)
-                                            ? 0.0f
-                                            : ex2(mi[rr][e] - Mx[rr]);
-                        Ox[rr] += f * oi[rr][e];
-                        Lx[rr] += f * li[rr][e];
+                    if (e < count) {
+                        const float f = (mi[i][e] == -CUDART_INF_F) ? 0.0f : ex2(mi[i][e] - M);
+                        O += f * oi[i][e];
+                        L += f * li[i][e];
                     }
                 }
+                emit_value<HD>(p, ooff, xch_step, row, d, O, M, L);
             }
         }
-        if (tid < HD) {
+        return;
+    }
+    for (int c0 = c_first; c0 <= c_last; c0 += kMergeBatch) {
+        const int nb = min(kMergeBatch, c_last - c0 + 1);
+        for (int idx = tid; idx < nb * chunks; idx += kThreads) {
+            const int e = idx / chunks, ch = idx - e * chunks;
+            const int cc = c0 + e;
+            const int sl = (ustart[cc] >= pair_u0) ? 0 : 1;
+            cp_async16(stage + ((size_t)e * SLOT * 4 + ch * 16),
+                       p.part + ((size_t)cc * 2 + sl) * SLOT + ch * 4, 16);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
 #pragma unroll
-            for (int rr = 0; rr < 4; rr++) {
-                if (r0 + rr < rows_here) emit(r0 + rr, d, Ox[rr], Mx[rr], Lx[rr]);
+        for (int i = 0; i < RMAX; i++) {
+            const int row = rg + i * RSTEP;
+            if (row < rows_here) {
+                float bm = -CUDART_INF_F;
+                for (int e = 0; e < nb; e++) bm = fmaxf(bm, st[e * SLOT + row * (HD + 2) + HD]);
+                const float m_new = fmaxf(Mx[i], bm);
+                const float keep = (Mx[i] == -CUDART_INF_F) ? 0.0f : ex2(Mx[i] - m_new);
+                float O = Ox[i] * keep, L = Lx[i] * keep;
+                for (int e = 0; e < nb; e++) {
+                    const float *pr = st + e * SLOT + row * (HD + 2);
+                    const float mi = pr[HD];
+                    const float f = (mi == -CUDART_INF_F) ? 0.0f : ex2(mi - m_new);
+                    O += f * pr[d];
+                    L += f * pr[HD + 1];
+                }
+                Mx[i] = m_new;
+                Ox[i] = O;
+                Lx[i] = L;
             }
         }
+        __syncthreads();   // the stage is free for the next batch
+    }
+#pragma unroll
+    for (int i = 0; i < RMAX; i++) {
+        const int row = rg + i * RSTEP;
+        if (row < rows_here) emit_value<HD>(p, ooff, xch_step, row, d, Ox[i], Mx[i], Lx[i]);
+    }
+}
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// The cross-rank half of a fused step: waits until every rank has delivered
+// its triple of `pair` for this step into this rank's gather buffer (each
+// rank raises the pair's flag after a system-wide fence), then merges the
+// `world` triples of each of the pair's rows into xch_out, normalised. The
+// wait is bounded (about a second); when it runs out the status word is set
+// and the pair is left unmerged, so the launch still ends.
+template <int HD>
+__device__ __noinline__ void cross_merge(const DecodeStreamParams &p, int pair, int row0,
+                                         int rows_here, unsigned xch_step)
+{
+    constexpr int RSTEP = kThreads / HD;
+    __shared__ int s_ok;
+    const int tid = threadIdx.x;
+    const int world = p.xch_world;
+    const unsigned want = xch_step + 1u;
+    if (tid == 0) s_ok = 1;
+    __syncthreads();
+    if (tid < world) {
+        const unsigned *f = p.xch_pflags[p.xch_rank] + (size_t)pair * world + tid;
+        const long long t0 = clock64();
+        while ((int)(ld_acquire_sys(f) - want) < 0) {
+            if (clock64() - t0 > (1ll << 31)) {
+                s_ok = 0;
+                atomicExch(p.xch_status, 70 + tid);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const float *buf =
+        p.xch_gather[p.xch_rank] + (size_t)(xch_step & 1u) * world * p.xch_rank_stride;
+    const int d = tid % HD;
+    for (int row = tid / HD; row < rows_here; row += RSTEP) {
+        float mi[LLMTIE_MAX_RANKS], li[LLMTIE_MAX_RANKS], oi[LLMTIE_MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < LLMTIE_MAX_RANKS; r++) {
+            const int rr = min(r, world - 1);
+            const float *pr = buf + (size_t)rr * p.xch_rank_stride +
+                              (size_t)(row0 + row) * (HD + 2);
+            mi[r] = __ldcg(pr + HD);
+            li[r] = __ldcg(pr + HD + 1);
+            oi[r] = __ldcg(pr + d);
+        }
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int r = 0; r < LLMTIE_MAX_RANKS; r++) M = fmaxf(M, mi[r]);
+        float O = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int r = 0; r < LLMTIE_MAX_RANKS; r++) {
+            if (r < world) {
+                const float f = (mi[r] == -CUDART_INF_F) ? 0.0f : __expf(mi[r] - M);
+                O += f * oi[r];
+                L += f * li[r];
+            }
+        }
+        p.xch_out[(size_t)(row0 + row) * HD + d] = L > 0.0f ? O / L : 0.0f;
     }
 }
 
@@ -230,14 +332,18 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     constexpr int VBYTES = HD * 64;         // the same block of the transposed values
     constexpr int STAGE = KBYTES + VBYTES;
     constexpr int KCH = KROW / 16;          // 16-byte chunks in a key row
-    constexpr float kLn2 = 0.6931471805599453f;
 
     extern __shared__ __align__(128) unsigned char ring_all[];
-    __shared__ float sm_o[kWarps][kRows][HD];
+    __shared__ __align__(16) float sm_o[kWarps][kRows][HD + 8];   // +8: rows 0-3 and 4-7 tile the banks
     __shared__ float sm_m[kWarps][kRows];
     __shared__ float sm_l[kWarps][kRows];
-    __shared__ float sm_M[kRows];
     __shared__ int sm_last;
+    constexpr int kMineMax = 16;
+    __shared__ int sm_mine[kMineMax][3];   // pairs this block finished: pair, first row, rows
+    int nmine = 0;                         // (the same in every thread)
+    // The cut of the grid, out of the parameter bank (where every probe of a
+    // search would be a cold miss) into shared memory once.
+    __shared__ int sm_ustart[LLMTIE_STREAM_MAX_BLOCKS + 1];
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -251,54 +357,34 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     // have finished the launch and advanced it.
     const unsigned xch_step = p.xch_world ? *(volatile const unsigned *)p.xch_step : 0u;
 
-    const long long W = p.total_units;
-    const long long G = gridDim.x;
-    const long long u0 = (long long)blockIdx.x * W / G;
-    const long long u1 = (long long)(blockIdx.x + 1) * W / G;
-    const int inner_pairs = p.kv_heads * p.row_chunks;
+    const int G = gridDim.x;
+    const int u0 = p.ustart[blockIdx.x];
+    const int u1 = p.ustart[blockIdx.x + 1];
+    for (int i = threadIdx.x; i <= G; i += kThreads) sm_ustart[i] = p.ustart[i];
+    // (the first segment's barriers order these stores before their first use)
 
-    long long u = u0;
+    int u = u0;
     while (u < u1) {
         // ---- which pair this unit lies in, and how much of it is ours ---------
         int b = 0;
-        while (b + 1 < p.nseq && u >= p.unit0[b + 1]) b++;
+        while (b + 1 < p.nseq && u >= (int)p.unit0[b + 1]) b++;
         const int tk = p.seq[b].tk;
         const int cap = p.seq[b].cap;
         const int n_units = (tk + 127) >> 7;                 // units of one pair
-        const long long rel = u - p.unit0[b];
-        const int inner = (int)(rel / n_units);              // rc * kv_heads + kh
-        const int off = (int)(rel % n_units);
+        const int rel = u - (int)p.unit0[b];
+        const int inner = rel / n_units;                     // rc * kv_heads + kh
+        const int off = rel - inner * n_units;
         const int rc = inner / p.kv_heads;
         const int kh = inner % p.kv_heads;
-        const int seg_end = (int)min((long long)n_units, off + (u1 - u));
+        const int seg_end = min(n_units, off + (u1 - u));
         const int k_begin = off * 128;
         const int k_end = min(tk, seg_end * 128);
         const bool whole = (off == 0 && seg_end == n_units);
-        const long long pair_u0 = p.unit0[b] + (long long)inner * n_units;
+        const int pair_u0 = (int)p.unit0[b] + inner * n_units;
         const int pair = p.pair0[b] + inner;
         const uint16_t *kbase = p.seq[b].k + (size_t)kh * cap * HD;
         const uint16_t *vbase = p.seq[b].v + (size_t)kh * HD * cap;
         const int rows_here = min(kRows, p.rows - rc * kRows);
-
-        // ---- query fragments, permuted as the key loads are, split hi / lo ------
-        uint32_t qa[KI][2][4];
-        {
-            const float *qrow = p.q + (long long)b * p.q_seq + (long long)kh * p.q_kv +
-                                (long long)(rc * kRows + g) * p.q_row;
-            const bool live = g < rows_here;
-#pragma unroll
-            for (int i = 0; i < KI; i++) {
-#pragma unroll
-                for (int uu = 0; uu < 2; uu++) {
-                    const int at = 32 * i + 8 * c + 4 * uu;
-                    float x[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) x[e] = live ? qrow[at + e] * p.q_scale : 0.0f;
-                    split_pair(x[0], x[1], qa[i][uu][0], qa[i][uu][1]);
-                    split_pair(x[2], x[3], qa[i][uu][2], qa[i][uu][3]);
-                }
-            }
-        }
 
         float m = -CUDART_INF_F;
         float l = 0.0f;
@@ -335,6 +421,26 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
         };
 
+        // The query row goes out first, ahead of the ring's first copies in the
+        // load pipe, and is consumed after them: the two latencies overlap.
+        float qx[KI][2][4];
+        {
+            const float *qrow = p.q + (long long)b * p.q_seq + (long long)kh * p.q_kv +
+                                (long long)(rc * kRows + g) * p.q_row;
+            const bool live = g < rows_here;
+#pragma unroll
+            for (int i = 0; i < KI; i++) {
+#pragma unroll
+                for (int uu = 0; uu < 2; uu++) {
+                    const int at = 32 * i + 8 * c + 4 * uu;
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        qx[i][uu][e] = live ? __ldg(qrow + at + e) * p.q_scale : 0.0f;
+                    }
+                }
+            }
+        }
+
         // This warp's blocks: k_begin + (warp + kWarps * i) * 32.
         const int first = k_begin + warp * 32;
         const int nblk = first < k_end ? (k_end - first + kWarps * 32 - 1) / (kWarps * 32) : 0;
@@ -342,6 +448,17 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         for (int s = 0; s < kStages - 1; s++) {
             if (s < nblk) issue(first + s * kWarps * 32, s);
             cp_async_commit();
+        }
+
+        // ---- query fragments, permuted as the key loads are, split hi / lo ------
+        uint32_t qa[KI][2][4];
+#pragma unroll
+        for (int i = 0; i < KI; i++) {
+#pragma unroll
+            for (int uu = 0; uu < 2; uu++) {
+                split_pair(qx[i][uu][0], qx[i][uu][1], qa[i][uu][0], qa[i][uu][1]);
+                split_pair(qx[i][uu][2], qx[i][uu][3], qa[i][uu][2], qa[i][uu][3]);
+            }
         }
 
         for (int i = 0; i < nblk; i++) {
@@ -451,8 +568,8 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         }
 #pragma unroll
         for (int j = 0; j < NT; j++) {
-            sm_o[warp][g][8 * j + 2 * c] = o[j][0] + o[j][2];
-            sm_o[warp][g][8 * j + 2 * c + 1] = o[j][1] + o[j][3];
+            *reinterpret_cast<float2 *>(&sm_o[warp][g][8 * j + 2 * c]) =
+                make_float2(o[j][0] + o[j][2], o[j][1] + o[j][3]);
         }
         __syncthreads();
 
@@ -471,6 +588,28 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             if (p.xch_world == 0) return;
             __threadfence_system();
             __syncthreads();
+            if (p.xch_fused) {
+                // This pair's triple is on its way to every rank: raise the
+                // pair's flag there, and remember the pair for the merge
+                // this block owes it before it exits.
+                if (tid < p.xch_world) {
+                    __threadfence_system();
+                    *(volatile unsigned *)(p.xch_pflags[tid] + (size_t)pair * p.xch_world +
+                                           p.xch_rank) = xch_step + 1u;
+                }
+                const int row0 = (int)(ooff / (HD + 2));
+                if (nmine < kMineMax) {
+                    if (tid == 0) {
+                        sm_mine[nmine][0] = pair;
+                        sm_mine[nmine][1] = row0;
+                        sm_mine[nmine][2] = rows_here;
+                    }
+                    nmine++;
+                } else {
+                    cross_merge<HD>(p, pair, row0, rows_here, xch_step);
+                }
+                return;
+            }
             if (tid == 0) {
                 const unsigned prev = atomicAdd(p.xch_done, 1u);
                 if (prev == (unsigned)(p.xch_pairs - 1)) {
@@ -512,8 +651,8 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         if (whole) pair_done();
         if (!whole) {
             // ---- the last block of this pair to arrive merges every partial -------------
-            const int c_first = covering(pair_u0, W, G);
-            const int c_last = covering(pair_u0 + n_units - 1, W, G);
+            const int c_first = block_of(sm_ustart, pair_u0, G);
+            const int c_last = block_of(sm_ustart, pair_u0 + n_units - 1, G);
             const int count = c_last - c_first + 1;
             __threadfence();
             __syncthreads();
@@ -523,14 +662,33 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
             __syncthreads();
             if (sm_last) {
-                __threadfence();
-                merge_pair<HD>(p, pair_u0, c_first, c_last, rows_here, W, G, ooff, xch_step);
+                // No second fence: the merge reads the partials from L2 (ld.cg /
+                // cp.async.cg), after the barrier that followed the counter's
+                // answer, so it cannot see anything older than their fences.
+                merge_pair<HD>(p, ring_all, sm_ustart, pair_u0, c_first, c_last, rows_here, ooff, xch_step);
                 pair_done();
                 if (tid == 0) p.ctr[pair] = 0u;   // at rest again for the next call
             }
         }
         __syncthreads();   // shared memory is reused by the next segment
         u += seg_end - off;
+    }
+
+    if (p.xch_fused) {
+        // The pairs this block finished on this rank: merge each across the
+        // ranks. Then count the block out; the last one advances the step.
+        for (int i = 0; i < nmine; i++) {
+            cross_merge<HD>(p, sm_mine[i][0], sm_mine[i][1], sm_mine[i][2], xch_step);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned prev = atomicAdd(p.xch_done, 1u);
+            if (prev == (unsigned)(G - 1)) {
+                *p.xch_done = 0u;
+                __threadfence();
+                *(volatile unsigned *)p.xch_step = xch_step + 1u;
+            }
+        }
     }
 }
 
@@ -545,8 +703,55 @@ const KernelReg reg_s64("attn_decode_h64_run", (const void *)decode_stream_kerne
 
 }  // namespace
 
-cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid)
+// Cuts the launch's units into one contiguous run a block.
+//
+// A block pays a fixed price for every (sequence, KV head) pair it touches -
+// a drained ring to refill, a partial to publish, an arrival to count - worth
+// a few units of streaming. A block whose run crosses from one pair into the
+// next pays it twice, and the launch ends when the slowest block does. So the
+// cut is even not in units but in units plus `ov` virtual ones at the head of
+// every pair: a run that crosses a pair boundary swallows that pair's virtual
+// units and carries that many fewer real ones.
+static void stream_partition(DecodeStreamParams &p, int hd, int grid)
 {
+    static const int forced = [] {
+        const char *e = getenv("LLMTIE_B200_DECODE_OV");
+        return e ? atoi(e) : -1;
+    }();
+    const long long ov = forced >= 0 ? forced : (hd == 128 ? 3 : 6);
+    const int inner = p.kv_heads * p.row_chunks;
+    const long long W = p.total_units;
+    const long long V = W + ov * (long long)p.nseq * inner;
+    bool ok = ov > 0;
+    if (ok) {
+        int b = 0;
+        for (int c = 0; c < grid; c++) {
+            const long long v = (long long)c * V / grid;
+            while (b + 1 < p.nseq && v >= p.unit0[b + 1] + ov * p.pair0[b + 1]) b++;
+            const long long n = (p.seq[b].tk + 127) / 128;
+            const long long rel = v - (p.unit0[b] + ov * p.pair0[b]);
+            const long long i = rel / (n + ov);
+            const long long r = rel % (n + ov);
+            p.ustart[c] = (int)(p.unit0[b] + i * n + (r > ov ? r - ov : 0));
+        }
+        p.ustart[grid] = (int)W;
+        for (int c = 0; c < grid; c++) ok = ok && p.ustart[c] < p.ustart[c + 1];
+        ok = ok && p.ustart[0] == 0;
+    }
+    if (!ok) {
+        for (int c = 0; c <= grid; c++) p.ustart[c] = (int)((long long)c * W / grid);
+    }
+}
+
+cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in, int hd, int grid)
+{
+    if (grid < 1 || grid > LLMTIE_STREAM_MAX_BLOCKS || p_in.total_units > 0x7fffffffLL ||
+        p_in.total_units < grid) {
+        return cudaErrorInvalidValue;
+    }
+    DecodeStreamParams p = p_in;
+    stream_partition(p, hd, grid);
+
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);

@@ -92,6 +92,47 @@ __global__ void rope_cache_f16_kernel(float *q, long long q_off, const float *k,
     }
 }
 
+// rope_cache_f16_kernel for a batch of sequences decoding together: sequence
+// blockIdx.y takes row blockIdx.y of q, k and v and its own caches, position
+// and capacity. The arithmetic per element is the single-sequence kernel's.
+__global__ void rope_cache_batched_kernel(const __grid_constant__ RopeBatchParams p)
+{
+    const RopeBatchSeq &sq = p.seq[blockIdx.y];
+    const int half = p.hd >> 1;
+    const int nq = p.heads * half;
+    const int nk = p.kv_heads * half;
+    const int nv = p.kv_heads * p.hd;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    float *q = p.q + (size_t)blockIdx.y * p.heads * p.hd;
+    const float *k = p.k + (size_t)blockIdx.y * p.kv_heads * p.hd;
+    const float *v = p.v + (size_t)blockIdx.y * p.kv_heads * p.hd;
+    if (i < nq + nk) {
+        const bool is_q = i < nq;
+        const int e = is_q ? i : i - nq;
+        const int j = e % half;
+        const int h = e / half;
+        float sn, cs, lo, hi;
+        pair_sincos(p.theta, j, p.hd, p.freq_div, sq.pos, sn, cs);
+        if (is_q) {
+            const size_t base = (size_t)h * p.hd + j;
+            rotate(q[base], q[base + half], cs, sn, lo, hi);
+            q[base] = lo;
+            q[base + half] = hi;
+        } else {
+            const size_t base = (size_t)h * p.hd + j;
+            rotate(k[base], k[base + half], cs, sn, lo, hi);
+            uint16_t *d = sq.kc + ((size_t)h * sq.cap + sq.pos) * p.hd;
+            d[j] = f16_bits(lo);
+            d[j + half] = f16_bits(hi);
+        }
+    } else if (i < nq + nk + nv) {
+        const int e = i - nq - nk;
+        const int h = e / p.hd;
+        const int j = e % p.hd;
+        sq.vc[((size_t)h * p.hd + j) * sq.cap + sq.pos] = f16_bits(v[e]);
+    }
+}
+
 // src [n][kv_heads*hd] -> K layout [kv][cap][hd]. Consecutive threads take
 // consecutive source elements, which are consecutive destination elements
 // within a head row, so both sides coalesce.
@@ -357,4 +398,11 @@ void launch_varlen_rope_append(cudaStream_t st, const VarlenParams &p)
     for (int b = 0; b < p.nseq; b++) max_n = p.seq[b].n > max_n ? p.seq[b].n : max_n;
     const dim3 grid((p.kv_heads * p.hd + 31) / 32, (max_n + 31) / 32, p.nseq);
     varlen_append_v_kernel<<<grid, dim3(32, 8), 0, st>>>(p);
+}
+
+void launch_rope_cache_batched(cudaStream_t st, const RopeBatchParams &p)
+{
+    const size_t n = (size_t)p.heads * p.hd / 2 + (size_t)p.kv_heads * p.hd / 2 +
+                     (size_t)p.kv_heads * p.hd;
+    rope_cache_batched_kernel<<<dim3(flat_blocks(n, 256), p.nseq), 256, 0, st>>>(p);
 }

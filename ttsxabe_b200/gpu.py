@@ -133,11 +133,15 @@ class Exchange:
     `llmtie_lse_merge_wait` take: every rank's gather buffer and flag array as
     mapped into this process, and this rank's step counter."""
 
-    def __init__(self, world: int, rank: int, gather_ptrs, flag_ptrs, step_ptr: int) -> None:
+    def __init__(self, world: int, rank: int, gather_ptrs, flag_ptrs, step_ptr: int,
+                 pair_flag_ptrs=None) -> None:
         self.world, self.rank = world, rank
         self._gather = (C.c_void_p * world)(*gather_ptrs)
         self._flags = (C.c_void_p * world)(*flag_ptrs)
         self.struct = _ExchangeStruct(world, rank, self._gather, self._flags, step_ptr)
+        # every rank's [pairs][world] words, for the fused entry only
+        self.pair_flags = (None if pair_flag_ptrs is None
+                           else (C.c_void_p * world)(*pair_flag_ptrs))
 
     def ref(self):
         return C.byref(self.struct)
@@ -250,6 +254,14 @@ class Gpu:
         _check(self._lib.llmtie_rope_cache_f16(
             self._h, qp, ql, qo, kp, kl, ko, vp_, vl, vo, _ptr(freq_div), heads, kv_heads,
             head_dim, theta, pos, kc.data_ptr(), kc.numel(), vc.data_ptr(), vc.numel(), cap))
+
+    def rope_cache_batched(self, q, k, v, freq_div, heads, kv_heads, head_dim, theta, pos, kcs,
+                           vcs, cap) -> None:
+        """`rope_cache_f16` for a batch of sequences in one launch."""
+        _check(self._lib.llmtie_rope_cache_batched(
+            self._h, q.data_ptr(), q.numel(), k.data_ptr(), k.numel(), v.data_ptr(), v.numel(),
+            _ptr(freq_div), len(kcs), heads, kv_heads, head_dim, theta, self._i32_table(pos),
+            self._ptr_table(kcs), self._ptr_table(vcs), self._i32_table(cap)))
 
     # ---- KV cache ---------------------------------------------------------------
 
@@ -378,6 +390,21 @@ class Gpu:
             self._h, q.data_ptr(), q.numel(), self._ptr_table(ks), self._ptr_table(vs),
             self._i32_table(tk), self._i32_table(cap), len(ks), heads, kv_heads, head_dim, scale,
             int(bool(scale_q)), scratch._bind(self), xch.ref()))
+
+    def decode_batched_fused(self, q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale, scale_q,
+                             scratch: DecodeScratch, xch: Exchange, out=None) -> torch.Tensor:
+        """The sharded step in one kernel: decode, push, wait and merge
+        (see include/llmtie_b200.h). Returns the merged [batch*heads*hd]."""
+        if xch.pair_flags is None:
+            raise ValueError("the fused exchange needs per-pair flags")
+        if out is None:
+            out = self.uninit(len(ks) * heads * head_dim)
+        _check(self._lib.llmtie_decode_batched_fused(
+            self._h, q.data_ptr(), q.numel(), self._ptr_table(ks), self._ptr_table(vs),
+            self._i32_table(tk), self._i32_table(cap), len(ks), heads, kv_heads, head_dim, scale,
+            int(bool(scale_q)), scratch._bind(self), xch.ref(), xch.pair_flags, out.data_ptr(),
+            out.numel()))
+        return out
 
     def lse_merge_wait(self, xch: Exchange, rows, head_dim, out=None) -> torch.Tensor:
         if out is None:

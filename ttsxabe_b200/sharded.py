@@ -64,24 +64,43 @@ class ShardedDecode:
         self.stream = stream
         self._gathered = None
         self._fused = None
+        self.exchange = "none" if self.world == 1 else "all-gather"
 
     @classmethod
     def on_gpu(cls, gpu, ks: Sequence[torch.Tensor], vs: Sequence[torch.Tensor],
                tk: Sequence[int], cap: Sequence[int], heads: int, kv_heads: int, head_dim: int,
-               scale: float, scale_q: bool = False, group=None, p2p: bool = False
+               scale: float, scale_q: bool = False, group=None, p2p=False
                ) -> "ShardedDecode":
         """Binds the GPU entry points over this rank's caches. With `p2p` the
-        exchange is fused into the kernels: the decode kernel stores its triples
-        into every rank's gather buffer over NVLink peer memory and a waiting
-        merge kernel follows it - no collective call in the step."""
+        exchange is fused into the kernels, no collective call in the step:
+        "fused" (or True) runs the whole step as one kernel - the decode kernel
+        stores its triples into every rank's gather buffer over NVLink peer
+        memory, and the block that finished a pair waits for the other ranks'
+        triples of it and merges; "push" keeps the merge in a second, waiting
+        kernel."""
         from .gpu import DecodeScratch
 
         scratch = DecodeScratch()
         batch = len(ks)
         outs = {}
         if p2p and dist.is_initialized() and dist.get_world_size(group) > 1:
-            return cls._on_gpu_p2p(gpu, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
-                                   scale_q, group, scratch)
+            # Every rank must take the same path: if symmetric memory cannot be
+            # set up on any one of them, all fall back to the all-gather.
+            fused, why = None, ""
+            try:
+                fused = cls._on_gpu_p2p(gpu, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
+                                        scale_q, group, scratch, one_kernel=(p2p != "push"))
+            except (ImportError, RuntimeError, AttributeError) as e:
+                why = str(e)
+            ok = torch.tensor([1 if fused is not None else 0], dtype=torch.int32,
+                              device=gpu.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 1:
+                return fused
+            if dist.get_rank(group) == 0:
+                import warnings
+                warnings.warn("peer-memory exchange unavailable (%s); using the all-gather"
+                              % (why or "another rank failed"))
 
         def partial_fn(q, partial):
             width = heads * (head_dim + 2) if partial else heads * head_dim
@@ -99,11 +118,12 @@ class ShardedDecode:
 
         self = cls(heads, head_dim, group, partial_fn, merge_fn, gpu.stream)
         self._scratch = scratch
+        self.exchange = "none" if self.world == 1 else "all-gather"
         return self
 
     @classmethod
     def _on_gpu_p2p(cls, gpu, ks, vs, tk, cap, heads, kv_heads, head_dim, scale, scale_q, group,
-                    scratch) -> "ShardedDecode":
+                    scratch, one_kernel=True) -> "ShardedDecode":
         import torch.distributed._symmetric_memory as symm_mem
 
         from .gpu import Exchange
@@ -118,24 +138,34 @@ class ShardedDecode:
             gather = symm_mem.empty(2 * world * rows * (head_dim + 2), dtype=torch.float32,
                                     device=gpu.device)
             flags = symm_mem.empty(64, dtype=torch.int32, device=gpu.device)
+            pflags = symm_mem.empty(max(64, batch * kv_heads * world), dtype=torch.int32,
+                                    device=gpu.device)
             gather.zero_()
             flags.zero_()
+            pflags.zero_()
             step = torch.zeros(1, dtype=torch.int32, device=gpu.device)
             out = torch.empty(rows * head_dim, dtype=torch.float32, device=gpu.device)
         gh = symm_mem.rendezvous(gather, pg)
         fh = symm_mem.rendezvous(flags, pg)
+        ph = symm_mem.rendezvous(pflags, pg)
         torch.cuda.synchronize()
         dist.barrier(group)
         xch = Exchange(world, rank, [int(p) for p in gh.buffer_ptrs],
-                       [int(p) for p in fh.buffer_ptrs], step.data_ptr())
+                       [int(p) for p in fh.buffer_ptrs], step.data_ptr(),
+                       [int(p) for p in ph.buffer_ptrs])
 
         self = cls(heads, head_dim, group, None, None, gpu.stream)
-        self._keep = (gather, flags, step, gh, fh, xch, scratch, out)
+        self._keep = (gather, flags, pflags, step, gh, fh, ph, xch, scratch, out)
 
-        def fused(q):
-            gpu.decode_batched_push(q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
-                                    scale_q, scratch, xch)
-            return gpu.lse_merge_wait(xch, rows, head_dim, out=out)
+        if one_kernel:
+            def fused(q):
+                return gpu.decode_batched_fused(q, ks, vs, tk, cap, heads, kv_heads, head_dim,
+                                                scale, scale_q, scratch, xch, out=out)
+        else:
+            def fused(q):
+                gpu.decode_batched_push(q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
+                                        scale_q, scratch, xch)
+                return gpu.lse_merge_wait(xch, rows, head_dim, out=out)
 
         self._fused = fused
         # the attention kernel alone, for timing: triples into a local buffer
@@ -149,6 +179,7 @@ class ShardedDecode:
                                       scale_q, scratch, out=local[partial], partial=partial)
 
         self.partial_fn = partial_fn
+        self.exchange = "peer-fused" if one_kernel else "peer-push"
         return self
 
     def decode(self, q: torch.Tensor) -> torch.Tensor:
