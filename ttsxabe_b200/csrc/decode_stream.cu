@@ -586,12 +586,14 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         // the launch's last pair raises this rank's flag on every rank.
         auto pair_done = [&]() {
             if (p.xch_world == 0) return;
-            __threadfence_system();
-            __syncthreads();
             if (p.xch_fused) {
                 // This pair's triple is on its way to every rank: raise the
                 // pair's flag there, and remember the pair for the merge
-                // this block owes it before it exits.
+                // this block owes it before it exits. One fence, by the
+                // threads that raise the flags, after the barrier: it orders
+                // every store the barrier ordered before it (the pattern of a
+                // grid-wide barrier's arrival).
+                __syncthreads();
                 if (tid < p.xch_world) {
                     __threadfence_system();
                     *(volatile unsigned *)(p.xch_pflags[tid] + (size_t)pair * p.xch_world +
@@ -610,6 +612,8 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                 }
                 return;
             }
+            __threadfence_system();
+            __syncthreads();
             if (tid == 0) {
                 const unsigned prev = atomicAdd(p.xch_done, 1u);
                 if (prev == (unsigned)(p.xch_pairs - 1)) {
@@ -675,12 +679,10 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     }
 
     if (p.xch_fused) {
-        // The pairs this block finished on this rank: merge each across the
-        // ranks. Then count the block out; the last one advances the step.
-        for (int i = 0; i < nmine; i++) {
-            cross_merge<HD>(p, sm_mine[i][0], sm_mine[i][1], sm_mine[i][2], xch_step);
-        }
-        __syncthreads();
+        // Count the block out (every block has read the step by the time the
+        // last one is counted, and nothing reads it again before the next
+        // launch, so the last one may advance it now, off the critical path);
+        // then merge across the ranks the pairs this block finished.
         if (tid == 0) {
             const unsigned prev = atomicAdd(p.xch_done, 1u);
             if (prev == (unsigned)(G - 1)) {
@@ -688,6 +690,9 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                 __threadfence();
                 *(volatile unsigned *)p.xch_step = xch_step + 1u;
             }
+        }
+        for (int i = 0; i < nmine; i++) {
+            cross_merge<HD>(p, sm_mine[i][0], sm_mine[i][1], sm_mine[i][2], xch_step);
         }
     }
 }
