@@ -253,38 +253,6 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
     return d;
 }
 
-// 2^x for a packed pair without the transcendental pipe: that pipe (16 lanes
-// an SM) is what bounds the softmax, while the FMA pipe idles. x is split
-// into its nearest integer n (by adding 1.5 * 2^23, which leaves n in the low
-// mantissa bits) and f in [-0.5, 0.5]; 2^f is a degree-4 polynomial (relative
-// error 2.7e-6, well inside the f16 rounding P gets anyway); n goes into the
-// exponent with one integer multiply-add. x is clamped at -125 so that the
-// exponent cannot wrap (2^-125 is zero for every purpose here). Used for a
-// fixed share of each row's keys (kPolyOf4 of every four pairs), ex2 for the rest.
-#ifndef LLMTIE_POLY_OF_4
-#define LLMTIE_POLY_OF_4 2
-#endif
-constexpr int kPolyOf4 = LLMTIE_POLY_OF_4;
-__device__ __forceinline__ void ex2_poly2(uint64_t x, float &p0, float &p1)
-{
-    float x0, x1;
-    unpack2(x, x0, x1);
-    const uint64_t xc = pack2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
-    const uint64_t t = add2(xc, pack2(12582912.0f, 12582912.0f));
-    const uint64_t n = add2(t, pack2(-12582912.0f, -12582912.0f));
-    const uint64_t f = fma2(n, pack2(-1.0f, -1.0f), xc);
-    uint64_t r = fma2(pack2(0.009570101276040077f, 0.009570101276040077f), f,
-                      pack2(0.05591785907745361f, 0.05591785907745361f));
-    r = fma2(r, f, pack2(0.240247443318367f, 0.240247443318367f));
-    r = fma2(r, f, pack2(0.6931217908859253f, 0.6931217908859253f));
-    r = fma2(r, f, pack2(0.9999992847442627f, 0.9999992847442627f));
-    float r0, r1, t0, t1;
-    unpack2(r, r0, r1);
-    unpack2(t, t0, t1);
-    p0 = __int_as_float(__float_as_int(t0) * (1 << 23) + __float_as_int(r0));
-    p1 = __int_as_float(__float_as_int(t1) * (1 << 23) + __float_as_int(r1));
-}
-
 // Two floats to packed f16, x0 in the low half: one cvt.rn.f16x2.f32. (Two
 // scalar conversions would each take a slot of the transcendental pipe, which
 // is the pipe this kernel is bound by.)
@@ -549,13 +517,9 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                                                       __uint_as_float(s[c][2 * i + 1])),
                                                 sl2_2, neg_2);
                         float p0, p1;
-                        if ((i & 3) < kPolyOf4) {
-                            ex2_poly2(x, p0, p1);
-                        } else {
-                            unpack2(x, p0, p1);
-                            p0 = ex2(p0);
-                            p1 = ex2(p1);
-                        }
+                        unpack2(x, p0, p1);
+                        p0 = ex2(p0);
+                        p1 = ex2(p1);
                         lc[i & 3] = add2(lc[i & 3], pack2(p0, p1));
                         pk[i] = pack_f16(p0, p1);
                     }
