@@ -286,6 +286,15 @@ llmtie_status llmtie_decode_batched_push(llmtie_gpu *g, const float *q, size_t q
                                          const llmtie_exchange *xch);
 llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_exchange *xch, size_t rows,
                                     size_t head_dim, float *out, size_t out_len);
+/* How a batched decode launch over contexts tk[0..batch) would be cut over
+ * the grid (host only, no device needed; no counterpart in the reference):
+ * grid_out = blocks launched on a device of sm_count SMs, ustart[c] = the
+ * first 128-key unit of block c, ustart[grid] = all units. Units are laid end
+ * to end, sequence after sequence, KV head after KV head. For tests and for
+ * sizing scratch ahead of time (a launch uses 2*grid partial slots). */
+llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size_t kv_heads,
+                                size_t head_dim, int32_t sm_count, int32_t *ustart,
+                                size_t ustart_len, int32_t *grid_out);
 /* The whole sharded step in ONE kernel (no counterpart in the reference):
  * llmtie_decode_batched_push with the merge fused in as well. The block that
  * finishes a (sequence, KV head) pair on this rank stores the pair's triple

@@ -22,5 +22,6 @@ from .gpu import (  # noqa: F401
     RaggedBlock,
     SliceOverrun,
     UnsupportedAttention,
+    decode_cut,
 )
 from .cache import KvCache, want_capacity  # noqa: F401

@@ -27,6 +27,8 @@
 #include "common.cuh"
 
 #include <math_constants.h>
+
+#include <algorithm>
 #include <string.h>
 
 namespace {
@@ -719,16 +721,12 @@ const KernelReg reg_s64("attn_decode_h64_run", (const void *)decode_stream_kerne
 // units and carries that many fewer real ones.
 static void stream_partition(DecodeStreamParams &p, int hd, int grid)
 {
-    static const int forced = [] {
-        const char *e = getenv("LLMTIE_B200_DECODE_OV");
-        return e ? atoi(e) : -1;
-    }();
-    const long long ov = forced >= 0 ? forced : (hd == 128 ? 3 : 6);
+    const long long ov = hd == 128 ? 3 : 6;   // the same time in units of either width
     const int inner = p.kv_heads * p.row_chunks;
     const long long W = p.total_units;
     const long long V = W + ov * (long long)p.nseq * inner;
-    bool ok = ov > 0;
-    if (ok) {
+    bool ok = true;
+    {
         int b = 0;
         for (int c = 0; c < grid; c++) {
             const long long v = (long long)c * V / grid;
@@ -746,6 +744,43 @@ static void stream_partition(DecodeStreamParams &p, int hd, int grid)
     if (!ok) {
         for (int c = 0; c <= grid; c++) p.ustart[c] = (int)((long long)c * W / grid);
     }
+}
+
+extern "C" llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size_t kv_heads,
+                                           size_t head_dim, int32_t sm_count, int32_t *ustart,
+                                           size_t ustart_len, int32_t *grid_out)
+{
+    if (!tk || !ustart || !grid_out || batch == 0 || batch > LLMTIE_DECODE_MAX_SEQ ||
+        kv_heads == 0 || sm_count < 1 || (head_dim != 64 && head_dim != 128)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "a malformed decode description");
+    }
+    DecodeStreamParams p;
+    memset(&p, 0, sizeof(p));
+    p.nseq = (int)batch;
+    p.kv_heads = (int)kv_heads;
+    p.row_chunks = 1;
+    long long units = 0;
+    for (size_t b = 0; b < batch; b++) {
+        if (tk[b] <= 0) return llmtie_fail(LLMTIE_ERR_INVALID, "an empty context");
+        p.seq[b].tk = tk[b];
+        p.unit0[b] = units;
+        p.pair0[b] = (int)(b * kv_heads);
+        units += (long long)((tk[b] + 127) / 128) * (long long)kv_heads;
+    }
+    p.unit0[batch] = units;
+    p.pair0[batch] = (int)(batch * kv_heads);
+    p.total_units = units;
+    if (units > 0x7fffffffLL) return llmtie_fail(LLMTIE_ERR_INVALID, "too many keys for one launch");
+    const int grid = (int)std::min<long long>(std::min(sm_count, LLMTIE_STREAM_MAX_BLOCKS),
+                                              std::max<long long>(1, units / 4));
+    if (ustart_len < (size_t)grid + 1) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %d in a buffer of %zu", grid + 1,
+                           ustart_len);
+    }
+    stream_partition(p, (int)head_dim, grid);
+    for (int c = 0; c <= grid; c++) ustart[c] = p.ustart[c];
+    *grid_out = grid;
+    return LLMTIE_OK;
 }
 
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in, int hd, int grid)

@@ -69,7 +69,8 @@ enum Bar {
     S_FULL = 10,   // +t
     P_FULL = 12,   // +t
     O_DONE = 14,   // +t
-    NBARS = 16
+    S_FREE = 16,   // +t (head_dim 64 only)
+    NBARS = 18
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
@@ -343,8 +344,15 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     auto q_smem = [base](int t) { return base + (uint32_t)t * TILE_QK; };
     auto k_smem = [base](int s) { return base + (uint32_t)(2 + s) * TILE_QK; };
     auto v_smem = [base](int s) { return base + (uint32_t)(4 * TILE_QK) + (uint32_t)s * TILE_V; };
+    // Tensor memory: S_A, S_B (128 columns each), then O_A, O_B (HD each). At
+    // head_dim 128 that is all 512 columns and P overwrites its S; at head_dim 64
+    // the last 128 columns are free and P gets them, so that S of the next step
+    // can be issued as soon as the softmax has read this step's S into registers
+    // instead of after this step's P.V: the softmax then never waits for an MMA.
+    constexpr bool kSplit = (HD == 64);
     auto s_col = [](int t) { return (uint32_t)t * 128u; };
-    auto o_col = [](int t) { return 256u + (uint32_t)t * 128u; };
+    auto o_col = [](int t) { return 256u + (uint32_t)t * (uint32_t)HD; };
+    auto p_col = [](int t) { return kSplit ? 384u + (uint32_t)t * 64u : (uint32_t)t * 128u; };
 
     if (tid == 0) {
         // a block that finds the status word set (an earlier block gave up)
@@ -361,6 +369,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             mbar_init(BAR(S_FULL + s), 1);
             mbar_init(BAR(P_FULL + s), 4);
             mbar_init(BAR(O_DONE + s), 1);
+            mbar_init(BAR(S_FREE + s), 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -451,6 +460,16 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
 #pragma unroll
                 for (int c = 0; c < 4; c++) tmem_ld32(lane_addr + s_col(t) + 32 * c, s[c]);
                 tmem_wait_ld();
+                if (kSplit) {
+                    // S is in registers: its columns may take the next step's scores
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(S_FREE + t));
+                }
+                // With P apart, P.V of the previous step must be done before this
+                // step rescales O or overwrites P: one barrier phase a step,
+                // looked at as late as possible (the step's maxima come first).
+                bool pv_done = !kSplit || j == 0;
 
                 // -- mask the tiles that reach past what this row may see -----------------
                 const int key0 = j * BN;
@@ -485,8 +504,16 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                     if (__any_sync(0xffffffffu, move)) {
                         const float m_new = move ? mt : m_ref;
                         const float f = ex2((m_ref - m_new) * sl2);
-                        // PV of the previous step is complete (S of this step was
-                        // committed after it), so O may be rescaled in place.
+                        // O may be rescaled in place once P.V of the previous step is
+                        // complete. With P over S that is implied (this step's S was
+                        // committed after it).
+                        if (!pv_done) {
+                            ok = mbar_wait(BAR(O_DONE + t), (uint32_t)((j - 1) & 1), abort_flag,
+                                           p.status, 22 + t);
+                            if (!ok) break;
+                            tc_fence_after();
+                            pv_done = true;
+                        }
 #pragma unroll
                         for (int c = 0; c < HD / 32; c++) {
                             uint32_t o[32];
@@ -502,6 +529,13 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         l *= f;
                         m_ref = m_new;
                     }
+                }
+
+                if (!pv_done) {
+                    ok = mbar_wait(BAR(O_DONE + t), (uint32_t)((j - 1) & 1), abort_flag, p.status,
+                                   22 + t);
+                    if (!ok) break;
+                    tc_fence_after();
                 }
 
                 // -- probabilities: l from the un-rounded values, P rounded to f16 -----------
@@ -523,7 +557,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         lc[i & 3] = add2(lc[i & 3], pack2(p0, p1));
                         pk[i] = pack_f16(p0, p1);
                     }
-                    tmem_st16(lane_addr + s_col(t) + 16 * c, pk);
+                    tmem_st16(lane_addr + p_col(t) + 16 * c, pk);
                 }
                 {
                     float a0, a1, b0, b1;
@@ -538,7 +572,10 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             }
 
             // -- epilogue: O / l to global ------------------------------------------------
-            if (ok) ok = mbar_wait(BAR(O_DONE + t), 0u, abort_flag, p.status, 20 + t);
+            if (ok) {
+                ok = mbar_wait(BAR(O_DONE + t), kSplit ? (uint32_t)((me.n - 1) & 1) : 0u, abort_flag,
+                               p.status, 20 + t);
+            }
             if (ok) {
                 tc_fence_after();
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -626,10 +663,10 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ks++) {
                     const uint64_t off = (uint64_t)(ks >> 2) * kSubVStep + (uint64_t)(ks & 3) * 2;
-                    mma_ts(tmem + o_col(t), tmem + s_col(t) + 8 * ks, b + off, kIdescPV,
+                    mma_ts(tmem + o_col(t), tmem + p_col(t) + 8 * ks, b + off, kIdescPV,
                            (first && ks == 0) ? 0u : 1u);
                 }
-                if (last) tc_commit(BAR(O_DONE + t));
+                if (last || kSplit) tc_commit(BAR(O_DONE + t));
             };
             if (ok) ok = mbar_wait(BAR(K_FULL + 0), 0u, abort_flag, p.status, 42);
             if (ok) {
@@ -642,9 +679,31 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             for (int j = 0; j < n_max && ok; j++) {
                 const int s = j & 1;
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
+                bool k_ready = false;
+                if (kSplit) {
+                    // The next step's scores first, each as soon as its softmax
+                    // has taken this step's out of tensor memory.
+                    for (int t = 0; t < 2 && ok; t++) {
+                        if (j + 1 < n_of(t)) {
+                            ok = mbar_wait(BAR(S_FREE + t), (uint32_t)(j & 1), abort_flag, p.status,
+                                           47 + t);
+                            if (!ok) break;
+                            if (!k_ready) {
+                                ok = mbar_wait(BAR(K_FULL + (s ^ 1)),
+                                               (uint32_t)(((j + 1) >> 1) & 1), abort_flag, p.status,
+                                               44);
+                                if (!ok) break;
+                                k_ready = true;
+                            }
+                            tc_fence_after();
+                            issue_s(t, s ^ 1);
+                        }
+                    }
+                    if (!ok) break;
+                    if (j + 1 < n_max) tc_commit(BAR(K_EMPTY + (s ^ 1)));
+                }
                 ok = mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 43);
                 if (!ok) break;
-                bool k_ready = false;
                 for (int t = 0; t < 2 && ok; t++) {
                     if (j < n_of(t)) {
                         ok = mbar_wait(BAR(P_FULL + t), (uint32_t)(j & 1), abort_flag, p.status, 45 + t);
@@ -652,7 +711,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         tc_fence_after();
                         issue_pv(t, s, j == 0, j == n_of(t) - 1);
                     }
-                    if (j + 1 < n_of(t)) {
+                    if (!kSplit && j + 1 < n_of(t)) {
                         if (!k_ready) {
                             ok = mbar_wait(BAR(K_FULL + (s ^ 1)), (uint32_t)(((j + 1) >> 1) & 1),
                                            abort_flag, p.status, 44);
@@ -665,7 +724,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 }
                 if (!ok) break;
                 tc_commit(BAR(V_EMPTY + s));
-                if (j + 1 < n_max) tc_commit(BAR(K_EMPTY + (s ^ 1)));
+                if (!kSplit && j + 1 < n_max) tc_commit(BAR(K_EMPTY + (s ^ 1)));
             }
         }
     }

@@ -267,20 +267,48 @@ __global__ void varlen_rope_kernel(const __grid_constant__ VarlenParams p)
     const int ti = row - sq.row0;
     float sn, cs, lo, hi;
     pair_sincos(p.theta, j, p.hd, p.freq_div, sq.past + ti, sn, cs);
+    // Eight heads at a time, every load of a batch issued before its first
+    // store: a plain load-rotate-store loop over the heads keeps one access
+    // in flight a thread and runs at a third of the memory system's speed.
+    constexpr int kBatch = 8;
     float *xq = p.q + (size_t)row * p.heads * p.hd + j;
-    for (int h = 0; h < p.heads; h++) {
-        rotate(xq[0], xq[half], cs, sn, lo, hi);
-        xq[0] = lo;
-        xq[half] = hi;
-        xq += p.hd;
+    for (int h0 = 0; h0 < p.heads; h0 += kBatch) {
+        float a[kBatch], b[kBatch];
+#pragma unroll
+        for (int e = 0; e < kBatch; e++) {
+            if (h0 + e < p.heads) {
+                a[e] = xq[(size_t)(h0 + e) * p.hd];
+                b[e] = xq[(size_t)(h0 + e) * p.hd + half];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < kBatch; e++) {
+            if (h0 + e < p.heads) {
+                rotate(a[e], b[e], cs, sn, lo, hi);
+                xq[(size_t)(h0 + e) * p.hd] = lo;
+                xq[(size_t)(h0 + e) * p.hd + half] = hi;
+            }
+        }
     }
     const float *xk = p.k + (size_t)row * p.kv_heads * p.hd + j;
-    for (int h = 0; h < p.kv_heads; h++) {
-        rotate(xk[0], xk[half], cs, sn, lo, hi);
-        uint16_t *d = sq.k + ((size_t)h * sq.cap + sq.past + ti) * p.hd;
-        d[j] = f16_bits(lo);
-        d[j + half] = f16_bits(hi);
-        xk += p.hd;
+    for (int h0 = 0; h0 < p.kv_heads; h0 += kBatch) {
+        float a[kBatch], b[kBatch];
+#pragma unroll
+        for (int e = 0; e < kBatch; e++) {
+            if (h0 + e < p.kv_heads) {
+                a[e] = xk[(size_t)(h0 + e) * p.hd];
+                b[e] = xk[(size_t)(h0 + e) * p.hd + half];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < kBatch; e++) {
+            if (h0 + e < p.kv_heads) {
+                rotate(a[e], b[e], cs, sn, lo, hi);
+                uint16_t *d = sq.k + ((size_t)(h0 + e) * sq.cap + sq.past + ti) * p.hd;
+                d[j] = f16_bits(lo);
+                d[j + half] = f16_bits(hi);
+            }
+        }
     }
 }
 

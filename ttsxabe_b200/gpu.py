@@ -147,6 +147,17 @@ class Exchange:
         return C.byref(self.struct)
 
 
+def decode_cut(tk, kv_heads: int, head_dim: int, sm_count: int = 148) -> list[int]:
+    """How a batched decode over contexts `tk` is cut over the grid: the first
+    128-key unit of every block, then the total (host only, no device)."""
+    lib = _lib.load()
+    table = (C.c_int32 * 161)()
+    grid = C.c_int32(0)
+    _check(lib.llmtie_decode_cut((C.c_int32 * len(tk))(*tk), len(tk), kv_heads, head_dim, sm_count,
+                                 table, len(table), C.byref(grid)))
+    return list(table[:grid.value + 1])
+
+
 class Gpu:
     """One device handle with its own stream (device.rs:737-842)."""
 
