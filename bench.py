@@ -276,10 +276,13 @@ def decode128k(args, world, rank, local):
     pos = tk - 1          # the step's new token lands in the last cache slot
     esz = 4
 
+    pos_t, cap_t = gpu.i32_table([pos] * batch), gpu.i32_table([cap] * batch)
+    ks_t, vs_t = gpu.ptr_table(ks), gpu.ptr_table(vs)
+
     def e2e_step():
         lib.llmtie_upload(h, dqkv.data_ptr(), hqkv.data_ptr(), batch * (nq + 2 * nkv) * esz)
-        gpu.rope_cache_batched(dq, dk, dv, None, HEADS, KV_HEADS, HD, 10000.0, [pos] * batch,
-                               ks, vs, [cap] * batch)
+        gpu.rope_cache_batched(dq, dk, dv, None, HEADS, KV_HEADS, HD, 10000.0, pos_t, ks_t, vs_t,
+                               cap_t)
         out = sd.decode(dqkv)          # q is the first batch*nq floats
         lib.llmtie_download(h, hout.data_ptr(), out.data_ptr(), batch * nq * esz)
 
@@ -614,7 +617,7 @@ def main():
     ap.add_argument("--context", type=int, default=131072)
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--exchange", default="fused", choices=["fused", "push", "nccl"],
+    ap.add_argument("--exchange", default="push", choices=["push", "fused", "nccl"],
                     help="how the ranks exchange their triples: everything in the decode "
                          "kernel over peer memory (fused), the push in the kernel and the merge "
                          "in a second waiting kernel (push), or an NCCL all-gather (nccl)")

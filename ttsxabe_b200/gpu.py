@@ -372,13 +372,23 @@ class Gpu:
 
     # ---- batched / sharded supersets -------------------------------------------------------
 
+    # The batched entries take HOST tables. A caller that makes the same call
+    # every step can build them once (`ptr_table`, `i32_table`) and pass the
+    # tables where the lists would go.
     @staticmethod
     def _ptr_table(tensors) -> C.Array:
+        if isinstance(tensors, C.Array):
+            return tensors
         return (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
 
     @staticmethod
     def _i32_table(xs) -> C.Array:
+        if isinstance(xs, C.Array):
+            return xs
         return (C.c_int32 * len(xs))(*[int(x) for x in xs])
+
+    ptr_table = _ptr_table
+    i32_table = _i32_table
 
     def decode_batched(self, q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale, scale_q,
                        scratch: DecodeScratch, out=None, partial=False) -> torch.Tensor:
