@@ -43,11 +43,11 @@ FALLBACK_TFLOPS = 1590.0
 # DRAM traffic of the dominant kernel from the ncu captures summarised under
 # profiles/. The decode entry is dram__bytes_read.sum + dram__bytes_write.sum
 # per algorithmic byte, captured on a batch 8 x 16384-key launch (537.30 MB read
-# + 5.59 MB written for 536.87 MB of KV) and scaled to the launch at hand, since
+# + 4.54 MB written for 536.87 MB of KV) and scaled to the launch at hand, since
 # traffic grows in proportion to the keys streamed; a full-size launch is too
 # large to capture.
 NCU_TRAFFIC = {
-    "decode128k": (537.295e6 + 5.589e6) / 536.870912e6,
+    "decode128k": (537.303e6 + 4.539e6) / 536.870912e6,
     "prefill8k": None,
 }
 
