@@ -201,6 +201,21 @@ llmtie_status llmtie_attn_decode_f16(llmtie_gpu *g, const float *q, size_t q_len
                                      size_t cap, float scale, int32_t scale_q,
                                      llmtie_decode_scratch *scratch, float *out,
                                      size_t out_len, size_t out_off);
+/* Gpu::attn_decode_f16_q / attn_decode_f16_q_row (device.rs:5973-6038): the
+ * same, and the context's int8 "twin" beside it, made by the kernel on the
+ * row it just produced (ad_emit, kernels.rs:5755-5773 = quantize_q8's
+ * arithmetic): per 32 consecutive elements scale = max|y| / 127 and code =
+ * round-to-nearest-even(y / scale) (0 when the group is all zero). codes int8
+ * [rows][heads*hd] and scales f32 [rows][heads*hd/32] are written from
+ * element out_off and out_off/32, as out is from out_off. */
+llmtie_status llmtie_attn_decode_f16_q(llmtie_gpu *g, const float *q, size_t q_len,
+                                       size_t q_off, const uint16_t *k, size_t k_len,
+                                       const uint16_t *v, size_t v_len, size_t heads,
+                                       size_t kv_heads, size_t head_dim, size_t tk, size_t cap,
+                                       float scale, int32_t scale_q,
+                                       llmtie_decode_scratch *scratch, float *out,
+                                       size_t out_len, size_t out_off, int8_t *codes,
+                                       size_t codes_len, float *scales, size_t scales_len);
 /* Gpu::attn_decode (device.rs:6132-6168): the same off f32 caches, head_dim 64
  * (the Whisper decoder's self-attention). */
 llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_t q_len, size_t q_off,

@@ -352,6 +352,25 @@ void orc_decode_f64(const float *q, const uint16_t *k, const uint16_t *v,
 }
 
 /* crates/llmtie-cuda/src/kernels.rs:5836-5879 */
+void orc_quantize_q8(const float *x, size_t n, int8_t *codes, float *scales)
+{
+    for (size_t g = 0; g < n / 32; g++) {
+        float mx = 0.0f;
+        for (size_t i = 0; i < 32; i++) {
+            const float a = fabsf(x[g * 32 + i]);
+            if (a > mx) mx = a;
+        }
+        const float d = mx * (1.0f / 127.0f);
+        const float inv = d > 0.0f ? 1.0f / d : 0.0f;
+        for (size_t i = 0; i < 32; i++) {
+            /* rintf under the default rounding mode is round-half-even, what
+             * __float2int_rn does */
+            codes[g * 32 + i] = (int8_t)(int)rintf(x[g * 32 + i] * inv);
+        }
+        scales[g] = d;
+    }
+}
+
 void orc_lse_merge(const float *o, const float *m, const float *l,
                    size_t parts, size_t rows, size_t hd, float *out)
 {

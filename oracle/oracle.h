@@ -118,6 +118,13 @@ void orc_decode_f64(const float *q, const uint16_t *k, const uint16_t *v,
                     size_t t1, size_t cap, float scale, int scale_q,
                     float *out, float *o_un, float *m_out, float *l_out);
 
+/* The activation quantiser whose output the decode attention's int8 "twin" must
+ * equal (crates/llmtie-cuda/src/kernels.rs:693-719, and ad_emit :5755-5773):
+ * per group of 32 consecutive values d = max|x| * (1/127) in f32, code =
+ * round-to-nearest-even(x * (1/d)) (0 when d is 0), scale = d. n a multiple
+ * of 32; codes [n], scales [n/32]. */
+void orc_quantize_q8(const float *x, size_t n, int8_t *codes, float *scales);
+
 /* Log-sum-exp merge of `parts` un-normalised triples
  * (crates/llmtie-cuda/src/kernels.rs:5836-5879):
  * M = max m_i, f_i = exp(m_i - M), out = (sum o_i f_i) / (sum l_i f_i).

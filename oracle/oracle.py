@@ -56,6 +56,7 @@ def lib() -> C.CDLL:
         L.orc_decode_f64.argtypes = [vp, vp, vp, sz, sz, sz, sz, sz, sz, f32, i32, vp, vp, vp,
                                      vp]
         L.orc_lse_merge.argtypes = [vp, vp, vp, sz, sz, sz, vp]
+        L.orc_quantize_q8.argtypes = [vp, sz, vp, vp]
         L.orc_decode_fast.restype = i32
         L.orc_decode_fast.argtypes = [vp, vp, vp, sz, sz, sz, sz, sz, f32, i32, vp, i32]
         L.orc_max_threads.restype = i32
@@ -182,6 +183,15 @@ def lse_merge(o, m, l, parts, rows, hd) -> np.ndarray:
     out = np.empty(rows * hd, dtype=np.float32)
     lib().orc_lse_merge(_p(o), _p(m), _p(l), parts, rows, hd, _p(out))
     return out
+
+
+def quantize_q8(x):
+    """(codes int8 [n], scales f32 [n/32]) of x, n a multiple of 32."""
+    x = _f32(x).reshape(-1)
+    codes = np.empty(x.size, dtype=np.int8)
+    scales = np.empty(x.size // 32, dtype=np.float32)
+    lib().orc_quantize_q8(_p(x), x.size, _p(codes), _p(scales))
+    return codes, scales
 
 
 def decode_fast(q, k, v, heads, kv_heads, hd, tk, cap, scale, scale_q, threads=0):

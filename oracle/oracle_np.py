@@ -97,3 +97,13 @@ def decode(q, k, v, heads, kv_heads, hd, tk, cap, scale, scale_q):
         e = np.exp(s - s.max())
         out[qh] = ((V[h, :, :tk] @ e) / e.sum()).astype(np.float32)
     return out.reshape(-1)
+
+
+def quantize_q8(x):
+    """kernels.rs:693-719 in numpy: (codes, scales) per group of 32, all f32."""
+    x = np.asarray(x, dtype=np.float32).reshape(-1, 32)
+    d = (np.abs(x).max(axis=1) * np.float32(1.0 / 127.0)).astype(np.float32)
+    inv = np.where(d > 0, np.float32(1.0) / np.where(d > 0, d, np.float32(1.0)), np.float32(0.0))
+    inv = inv.astype(np.float32)
+    codes = np.rint((x * inv[:, None]).astype(np.float32)).astype(np.int8)
+    return codes.reshape(-1), d

@@ -291,3 +291,63 @@ def test_fused_exchange_with_a_world_of_one(gpu, shape):
         assert_close_to(f"fused step {s}", want, got, 1e-5)
         assert int(step.item()) == s + 1
         assert int(pflags.min().item()) == s + 1
+
+
+@pytest.mark.parametrize("shape", [
+    # the reference's three (tests/kernels.rs:2072-2130), then a capacity whose
+    # value rows are only 8-byte aligned (the register-fed kernel) and a long
+    # context cut over many blocks
+    (8, 2, 128, 40, 64), (8, 2, 128, 1000, 1024), (4, 4, 64, 300, 512),
+    (20, 20, 64, 1500, 1500), (32, 8, 128, 40000, 40960),
+])
+def test_the_decode_twin_is_the_quantiser_over_its_output(gpu, shape):
+    """attn_decode_f16_q: the context is bit for bit what attn_decode_f16
+    gives, and the int8 twin is quantize_q8 over that context, held at exact
+    equality as the reference holds it (the group maximum associates)."""
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, kv, hd, tk, cap = shape
+    q = O.seq(heads * hd, 61)
+    dk = gpu.upload_f16(O.seq(kv * cap * hd, 62))
+    dv = gpu.upload_f16(O.seq(kv * cap * hd, 63))
+    dq = gpu.upload(q)
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    scratch = DecodeScratch()
+    plain = gpu.download(gpu.attn_decode_f16(dq, dk, dv, heads, kv, hd, tk, cap, scale, True,
+                                             scratch))
+    out, (codes, scales) = gpu.attn_decode_f16_q(dq, dk, dv, heads, kv, hd, tk, cap, scale, True,
+                                                 scratch)
+    out = gpu.download(out)
+    assert np.array_equal(plain, out), "the context differs with the twin asked for"
+    want_c, want_s = O.quantize_q8(out)
+    assert np.array_equal(codes.cpu().numpy(), want_c)
+    assert np.array_equal(scales.cpu().numpy(), want_s)
+
+
+def test_the_twin_row_variant_fills_one_row_and_refuses_short_buffers(gpu):
+    from ttsxabe_b200 import DecodeScratch, SliceOverrun
+
+    heads, kv, hd, tk, cap, rows = 8, 2, 128, 300, 512, 3
+    n = heads * hd
+    q = O.seq(rows * n, 64)
+    dk = gpu.upload_f16(O.seq(kv * cap * hd, 65))
+    dv = gpu.upload_f16(O.seq(kv * cap * hd, 66))
+    dq = gpu.upload(q)
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    scratch = DecodeScratch()
+    out = gpu.zeros(rows * n)
+    twin = gpu.q8_zeros(rows, n)
+    gpu.attn_decode_f16_q_row(dq, n, dk, dv, heads, kv, hd, tk, cap, scale, False, scratch, out,
+                              twin, 1)
+    gpu.synchronize()
+    got = gpu.download(out).reshape(rows, n)
+    codes = twin[0].cpu().numpy().reshape(rows, n)
+    scales = twin[1].cpu().numpy().reshape(rows, n // 32)
+    assert not got[0].any() and not got[2].any() and got[1].any()
+    assert not codes[0].any() and not codes[2].any() and not scales[0].any() and not scales[2].any()
+    want_c, want_s = O.quantize_q8(got[1])
+    assert np.array_equal(codes[1], want_c) and np.array_equal(scales[1], want_s)
+    short = gpu.q8_zeros(1, n)
+    with pytest.raises(SliceOverrun):
+        gpu.attn_decode_f16_q_row(dq, n, dk, dv, heads, kv, hd, tk, cap, scale, False, scratch, out,
+                                  short, 1)

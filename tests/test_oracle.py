@@ -197,3 +197,28 @@ def test_golden_fixtures():
         want = g[name]
         assert got.shape == want.shape
         assert np.abs(got - want).max() <= 1e-6, name
+
+
+def test_quantize_q8_known_answers_and_numpy_twin():
+    """The activation quantiser behind the decode twin (kernels.rs:693-719):
+    the group maximum maps to +-127 exactly, an all-zero group to zero codes and
+    a zero scale, halves round to even, and the C and numpy restatements agree
+    bit for bit on the reference's generator."""
+    from oracle import oracle_np as N
+
+    x = np.zeros(96, dtype=np.float32)
+    x[0:32] = np.linspace(-1.0, 1.0, 32, dtype=np.float32)
+    x[32] = 254.0
+    x[33], x[34], x[35] = 1.0, 3.0, -5.0       # scale 2: 0.5, 1.5, -2.5 -> 0, 2, -2
+    codes, scales = O.quantize_q8(x)
+    assert codes[0] == -127 and codes[31] == 127
+    assert scales[0] == np.float32(1.0) * np.float32(1.0 / 127.0)
+    assert codes[32] == 127 and scales[1] == np.float32(254.0) * np.float32(1.0 / 127.0)
+    assert list(codes[33:36]) == [0, 2, -2]
+    assert not codes[64:].any() and scales[2] == 0.0
+    y = O.seq(32 * 257, 33)
+    c1, s1 = O.quantize_q8(y)
+    c2, s2 = N.quantize_q8(y)
+    assert np.array_equal(c1, c2) and np.array_equal(s1, s2)
+    back = c1.reshape(-1, 32).astype(np.float32) * s1[:, None]
+    assert np.abs(back.reshape(-1) - y).max() <= 0.5 * s1.max() * 1.0001

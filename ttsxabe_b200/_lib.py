@@ -57,6 +57,9 @@ PROTOTYPES = {
     "llmtie_decode_scratch_free": (None, [vp, vp]),
     "llmtie_attn_decode_f16": (
         i32, [vp, vp, sz, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, i32, vp, vp, sz, sz]),
+    "llmtie_attn_decode_f16_q": (
+        i32, [vp, vp, sz, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, i32, vp, vp, sz, sz,
+              vp, sz, vp, sz]),
     "llmtie_attn_decode": (
         i32, [vp, vp, sz, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, i32, vp, vp, sz, sz]),
     "llmtie_attn_decode_f16_noalloc": (

@@ -843,6 +843,8 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         sp.partial = p.partial;
         sp.q_scale = p.q_scale;
         sp.sl2 = p.sl2;
+        sp.twin_q = p.twin_q;
+        sp.twin_s = p.twin_s;
         // One block per SM, but never fewer than four units (512 keys) a block:
         // a short context cut any finer spends longer merging partials than
         // it saved streaming them.
@@ -890,13 +892,15 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
     return ls.done();
 }
 
-extern "C" llmtie_status llmtie_attn_decode_f16(llmtie_gpu *g, const float *q, size_t q_len,
-                                                size_t q_off, const uint16_t *k, size_t k_len,
-                                                const uint16_t *v, size_t v_len, size_t heads,
-                                                size_t kv_heads, size_t head_dim, size_t tk,
-                                                size_t cap, float scale, int32_t scale_q,
-                                                llmtie_decode_scratch *scratch, float *out,
-                                                size_t out_len, size_t out_off)
+static llmtie_status attn_decode_f16_impl(llmtie_gpu *g, const float *q, size_t q_len,
+                                          size_t q_off, const uint16_t *k, size_t k_len,
+                                          const uint16_t *v, size_t v_len, size_t heads,
+                                          size_t kv_heads, size_t head_dim, size_t tk, size_t cap,
+                                          float scale, int32_t scale_q,
+                                          llmtie_decode_scratch *scratch, float *out,
+                                          size_t out_len, size_t out_off, int8_t *codes,
+                                          size_t codes_len, float *scales, size_t scales_len,
+                                          bool twin)
 {
     NEED_HANDLE(g);
     if (!scratch) return llmtie_fail(LLMTIE_ERR_INVALID, "null decode scratch");
@@ -960,8 +964,47 @@ extern "C" llmtie_status llmtie_attn_decode_f16(llmtie_gpu *g, const float *q, s
     p.partial = 0;
     p.q_scale = scale_q ? scale : 1.0f;
     p.sl2 = (scale_q ? 1.0f : scale) * kLog2e;
+    if (twin) {
+        if (!codes || !scales) return llmtie_fail(LLMTIE_ERR_INVALID, "null twin buffers");
+        if (codes_len < out_off + n) {
+            return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                               out_off + n, codes_len);
+        }
+        if (scales_len < (out_off + n) / 32) {
+            return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                               (out_off + n) / 32, scales_len);
+        }
+        // indexed as `out` is, from the same offset (out_off is a multiple of 32)
+        p.twin_q = (signed char *)codes + out_off;
+        p.twin_s = scales + out_off / 32;
+    }
     return decode_launch(g, head_dim == 128 ? "attn_decode_h128" : "attn_decode_h64", p,
                          (int)head_dim, scratch);
+}
+
+extern "C" llmtie_status llmtie_attn_decode_f16(llmtie_gpu *g, const float *q, size_t q_len,
+                                                size_t q_off, const uint16_t *k, size_t k_len,
+                                                const uint16_t *v, size_t v_len, size_t heads,
+                                                size_t kv_heads, size_t head_dim, size_t tk,
+                                                size_t cap, float scale, int32_t scale_q,
+                                                llmtie_decode_scratch *scratch, float *out,
+                                                size_t out_len, size_t out_off)
+{
+    return attn_decode_f16_impl(g, q, q_len, q_off, k, k_len, v, v_len, heads, kv_heads, head_dim,
+                                tk, cap, scale, scale_q, scratch, out, out_len, out_off, nullptr,
+                                0, nullptr, 0, false);
+}
+
+extern "C" llmtie_status llmtie_attn_decode_f16_q(
+    llmtie_gpu *g, const float *q, size_t q_len, size_t q_off, const uint16_t *k, size_t k_len,
+    const uint16_t *v, size_t v_len, size_t heads, size_t kv_heads, size_t head_dim, size_t tk,
+    size_t cap, float scale, int32_t scale_q, llmtie_decode_scratch *scratch, float *out,
+    size_t out_len, size_t out_off, int8_t *codes, size_t codes_len, float *scales,
+    size_t scales_len)
+{
+    return attn_decode_f16_impl(g, q, q_len, q_off, k, k_len, v, v_len, heads, kv_heads, head_dim,
+                                tk, cap, scale, scale_q, scratch, out, out_len, out_off, codes,
+                                codes_len, scales, scales_len, true);
 }
 
 extern "C" llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_t q_len,

@@ -118,7 +118,27 @@ struct DecodeParams {
     int partial;           // write (o, m, l) un-normalised, row stride hd + 2
     float q_scale;         // scale when it goes on q, else 1
     float sl2;             // (scale on the scores, else 1) * log2(e)
+    signed char *twin_q;   // int8 twin of the output, same indexing as out (or null)
+    float *twin_s;         //   its scales, one per 32 outputs
 };
+#ifdef __CUDACC__
+// The int8 "twin" of one context element, quantize_q8's arithmetic on the row
+// the block just produced (crates/llmtie-cuda/src/kernels.rs:5755-5773): the
+// 32 lanes of the calling warp hold 32 consecutive elements of one scale group
+// (idx a multiple of 32 at lane 0), code = rn(y * 127 / max|y|), scale =
+// max|y| / 127. Every lane of the warp must call.
+__device__ __forceinline__ void emit_twin(signed char *__restrict__ qa, float *__restrict__ asc,
+                                          long long idx, float y)
+{
+    float mx = fabsf(y);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float d = mx * (1.0f / 127.0f);
+    const float inv = d > 0.0f ? 1.0f / d : 0.0f;
+    qa[idx] = (signed char)__float2int_rn(y * inv);
+    if ((threadIdx.x & 31) == 0) asc[idx >> 5] = d;
+}
+#endif
 // hd is 64 or 128. Returns the cudaError of the launch.
 cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd);
 // How many blocks of the decode kernel fit the device at once.
@@ -157,6 +177,8 @@ struct DecodeStreamParams {
     unsigned *xch_pflags[LLMTIE_MAX_RANKS];  // every rank's pair flags [pairs][world]
     float *xch_out;                          // [rows][hd], this rank's merged result
     int *xch_status;                         // set when a bounded wait gave up
+    signed char *twin_q;                     // int8 twin of the output (or null), as in DecodeParams
+    float *twin_s;
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,

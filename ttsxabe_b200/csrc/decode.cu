@@ -300,7 +300,9 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p)
                     orow[HD + 1] = L;
                 }
             } else {
-                orow[d] = L > 0.0f ? O / L : 0.0f;
+                const float y = L > 0.0f ? O / L : 0.0f;
+                orow[d] = y;
+                if (p.twin_q) emit_twin(p.twin_q, p.twin_s, (orow - p.out) + d, y);
             }
         } else {
             float *pr = part + row * (HD + 2);
@@ -351,7 +353,9 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p)
                 orow[HD + 1] = L;
             }
         } else {
-            orow[d] = L > 0.0f ? O / L : 0.0f;
+            const float y = L > 0.0f ? O / L : 0.0f;
+            orow[d] = y;
+            if (p.twin_q) emit_twin(p.twin_q, p.twin_s, (orow - p.out) + d, y);
         }
     }
     if (tid == 0) p.ctr[pair] = 0u;   // at rest again for the next call

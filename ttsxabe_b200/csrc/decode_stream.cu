@@ -115,7 +115,9 @@ __device__ __forceinline__ void emit_value(const DecodeStreamParams &p, long lon
     constexpr float kLn2 = 0.6931471805599453f;
     const long long at = ooff + (long long)row * p.out_row;
     if (!p.partial) {
-        p.out[at + d] = L > 0.0f ? O / L : 0.0f;
+        const float y = L > 0.0f ? O / L : 0.0f;
+        p.out[at + d] = y;
+        if (p.twin_q) emit_twin(p.twin_q, p.twin_s, at + d, y);   // whole warps get here
     } else if (p.xch_world == 0) {
         p.out[at + d] = O;
         if (d == 0) {

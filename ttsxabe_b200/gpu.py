@@ -347,6 +347,34 @@ class Gpu:
             v.numel(), heads, kv_heads, head_dim, tk, cap, scale, int(bool(scale_q)),
             scratch._bind(self), out.data_ptr(), out.numel(), row * heads * head_dim))
 
+    def q8_zeros(self, rows: int, width: int):
+        """An empty int8 twin for `rows` rows of `width` (device.rs `q8_zeros`):
+        codes int8 [rows*width] and scales f32 [rows*width/32]."""
+        with torch.cuda.stream(self.stream):
+            return (torch.zeros(rows * width, dtype=torch.int8, device=self.device),
+                    torch.zeros(rows * width // 32, dtype=torch.float32, device=self.device))
+
+    def attn_decode_f16_q(self, q, k, v, heads, kv_heads, head_dim, tk, cap, scale, scale_q,
+                          scratch: DecodeScratch):
+        """`attn_decode_f16_q` (device.rs:5973-5991): the context and its int8
+        twin (codes, scales)."""
+        out = self.uninit(heads * head_dim)
+        twin = self.q8_zeros(1, heads * head_dim)
+        self.attn_decode_f16_q_row(q, 0, k, v, heads, kv_heads, head_dim, tk, cap, scale, scale_q,
+                                   scratch, out, twin, 0)
+        return out, twin
+
+    def attn_decode_f16_q_row(self, q, q_off, k, v, heads, kv_heads, head_dim, tk, cap, scale,
+                              scale_q, scratch: DecodeScratch, out, twin, row) -> None:
+        """`attn_decode_f16_q_row` (device.rs:6001-6038): row `row` of `out` and of
+        the twin, which are shared by the batch and filled a row at a time."""
+        codes, scales = twin
+        _check(self._lib.llmtie_attn_decode_f16_q(
+            self._h, q.data_ptr(), q.numel(), q_off, k.data_ptr(), k.numel(), v.data_ptr(),
+            v.numel(), heads, kv_heads, head_dim, tk, cap, scale, int(bool(scale_q)),
+            scratch._bind(self), out.data_ptr(), out.numel(), row * heads * head_dim,
+            codes.data_ptr(), codes.numel(), scales.data_ptr(), scales.numel()))
+
     def attn_decode_f16_noalloc(self, q, k, v, heads, kv_heads, head_dim, tk, cap, scale,
                                 scale_q, out=None) -> torch.Tensor:
         """`attn_decode_f16` for callers that cannot allocate: no DecodeScratch,
