@@ -33,6 +33,13 @@ CASES = [
     (40, 40, 128, 1500, 1536, True, False),
     (20, 20, 64, 1500, 1500, True, True),
     (8, 8, 64, 5000, 5056, False, True),
+    # groups that are not powers of two, and the widest a 64-wide head takes:
+    # the speech LM of crates/llmtie-cosy (14 query / 2 KV heads: group 7,
+    # src/llm.rs:448-475) and its neighbours
+    (14, 2, 64, 700, 1024, True, False),
+    (16, 2, 64, 333, 512, True, False),
+    (12, 4, 128, 500, 512, True, False),
+    (14, 2, 64, 9000, 9004, True, True),
 ]
 
 

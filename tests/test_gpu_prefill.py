@@ -26,6 +26,12 @@ SIZED = [
     (4, 4, 128, True, 200, 40, 256, True),
     (4, 2, 128, True, 130, 5, 138, True),
     (4, 4, 64, False, 300, 0, 300, False),
+    # crates/llmtie-cosy's callers, both off f32 caches: the speech LM's prefill
+    # (14 / 2 heads, a group of 7; src/llm.rs:448-475) and the flow model's
+    # non-causal 16-head attention (src/flow.rs:545-572)
+    (14, 2, 64, True, 300, 20, 320, False),
+    (14, 2, 64, True, 130, 0, 256, False),
+    (16, 16, 64, False, 257, 0, 258, False),
 ]
 
 
