@@ -165,6 +165,35 @@ def test_config2_ragged_batched_prefill(gpu):
     assert_parity("config 2 sequence 0 (f64 oracle)", want64, got[:n].reshape(-1))
 
 
+def test_ragged_prefill_of_more_sequences_than_one_launch_maps(gpu):
+    """Eleven sequences: the tensor-core kernel carries eight tensor maps a
+    launch, so the batch goes in groups; the second group holds a 40-token
+    sequence, too short for a 128-key box, and takes the general kernel."""
+    heads, kv, hd = 8, 2, 128
+    rng = np.random.default_rng(12)
+    lens = [int(x) for x in rng.integers(130, 300, size=11)]
+    lens[9] = 40
+    batch = len(lens)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    total = int(cu[-1])
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, total * heads * hd)
+    k = normal_f16(rng, total * kv * hd)
+    v = normal_f16(rng, total * kv * hd)
+    cap = 304
+    kcs = [gpu.zeros_f16(kv * cap * hd) for _ in range(batch)]
+    vcs = [gpu.zeros_f16(kv * cap * hd) for _ in range(batch)]
+    out = gpu.prefill_varlen(gpu.upload(q), gpu.upload(k), gpu.upload(v), cu, kcs, vcs,
+                             [0] * batch, [cap] * batch, None, heads, kv, hd, 10000.0, scale)
+    got = gpu.download(out).reshape(total, heads * hd)
+    for b in range(batch):
+        n, r0 = lens[b], int(cu[b])
+        qr = O.rope(q.reshape(total, -1)[r0:r0 + n].reshape(-1), n, heads, hd, 10000.0, 0)
+        want = O.prefill(qr, gpu.download_u16(kcs[b]), gpu.download_u16(vcs[b]), n, 0, heads, kv,
+                         hd, cap, scale, True, fast=True)
+        assert_parity(f"sequence {b} of 11 ({n} tokens)", want, got[r0:r0 + n].reshape(-1))
+
+
 def test_whisper_encoder_rows(gpu):
     """BASELINE config 4, encoder: non-causal self-attention over 1500 frames,
     20 heads, hd 64, scale 1/8 on q, context f16 [t, d] from one [t, 3d]

@@ -1368,13 +1368,21 @@ extern "C" llmtie_status llmtie_prefill_varlen(
         pp.causal = 1;
         pp.q_scale = 1.0f;
         pp.sl2 = scale * kLog2e;
-        LaunchScope ls(g, "flash_attn_h");
-        const cudaError_t e = use_tc(pp, (int)head_dim)
-                                  ? launch_prefill_tc(g->stream, pp, (int)head_dim, g->timeout_flag)
-                                  : launch_prefill_mma(g->stream, pp, (int)head_dim);
-        if (e != cudaSuccess) return driver_fail("flash_attn_h", e);
-        const llmtie_status s = ls.done();
-        if (s != LLMTIE_OK) return s;
+        // The tensor-core kernel carries a tensor map per sequence and so at
+        // most LLMTIE_TC_MAX_SEQ of them a launch: a longer batch goes in groups.
+        for (int s0 = 0; s0 < pp.nseq; s0 += LLMTIE_TC_MAX_SEQ) {
+            PrefillParams part = pp;
+            part.nseq = std::min(LLMTIE_TC_MAX_SEQ, pp.nseq - s0);
+            for (int b = 0; b < part.nseq; b++) part.seq[b] = pp.seq[s0 + b];
+            LaunchScope ls(g, "flash_attn_h");
+            const cudaError_t e =
+                use_tc(part, (int)head_dim)
+                    ? launch_prefill_tc(g->stream, part, (int)head_dim, g->timeout_flag)
+                    : launch_prefill_mma(g->stream, part, (int)head_dim);
+            if (e != cudaSuccess) return driver_fail("flash_attn_h", e);
+            const llmtie_status s = ls.done();
+            if (s != LLMTIE_OK) return s;
+        }
     }
     return LLMTIE_OK;
 }
