@@ -178,6 +178,14 @@ llmtie_status llmtie_flash_attn_rows(llmtie_gpu *g, const float *qkv, size_t qkv
                                      uint16_t *out, size_t out_len, size_t t,
                                      size_t heads, size_t head_dim, float scale,
                                      void *work, size_t work_bytes);
+/* llmtie_flash_attn_rows for `batch` utterances of the same length in two
+ * launches (the reference has no batch here: the encoder calls once per
+ * utterance, crates/llmtie-asr/src/model.rs:792-822). qkv f32 [batch][t][3*d],
+ * out f16 [batch][t][d]; `work` NULL or batch times the single-utterance size. */
+llmtie_status llmtie_flash_attn_rows_batched(llmtie_gpu *g, const float *qkv, size_t qkv_len,
+                                             uint16_t *out, size_t out_len, size_t batch,
+                                             size_t t, size_t heads, size_t head_dim,
+                                             float scale, void *work, size_t work_bytes);
 size_t llmtie_flash_rows_work_bytes(size_t t, size_t heads, size_t head_dim);
 
 /* ---- decode attention ------------------------------------------------------- */

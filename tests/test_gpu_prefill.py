@@ -213,6 +213,30 @@ def test_whisper_encoder_rows(gpu):
     assert np.linalg.norm(want - got) / np.linalg.norm(want) <= 1e-3 + 2.0 ** -11
 
 
+@pytest.mark.parametrize("batch,t", [(3, 200), (8, 1500), (10, 130)])
+def test_batched_encoder_rows_equal_one_call_per_utterance(gpu, batch, t):
+    """BASELINE config 4 at batch 8 in two launches: bit for bit what one
+    flash_attn_rows call per utterance returns (the reference's way,
+    crates/llmtie-asr/src/model.rs:792-822); also a batch longer than one
+    attention launch carries, and a caller-owned staging buffer."""
+    import torch
+
+    heads, hd = 20, 64
+    d = heads * hd
+    rng = np.random.default_rng(40 + batch)
+    qkv = normal_f16(rng, batch * t * 3 * d)
+    dq = gpu.upload(qkv)
+    nbytes = batch * gpu._lib.llmtie_flash_rows_work_bytes(t, heads, hd)
+    work = gpu._empty(nbytes // 2, torch.float16)
+    got = gpu.download_u16(gpu.flash_attn_rows_batched(dq, batch, t, heads, hd, 0.125, work=work))
+    got2 = gpu.download_u16(gpu.flash_attn_rows_batched(dq, batch, t, heads, hd, 0.125))
+    assert np.array_equal(got, got2)
+    for b in range(batch):
+        one = gpu.upload(qkv[b * t * 3 * d:(b + 1) * t * 3 * d])
+        want = gpu.download_u16(gpu.flash_attn_rows(one, t, heads, hd, 0.125))
+        assert np.array_equal(got[b * t * d:(b + 1) * t * d], want), f"utterance {b}"
+
+
 @pytest.mark.parametrize("n", [1, 2, 5, 8, 16, 32])
 def test_whisper_cross_attention(gpu, n):
     """BASELINE config 4, decoder cross-attention: 1 to 32 query tokens over

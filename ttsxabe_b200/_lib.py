@@ -52,6 +52,7 @@ PROTOTYPES = {
     "llmtie_flash_attn": (
         i32, [vp, vp, sz, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, sz, f32, i32]),
     "llmtie_flash_attn_rows": (i32, [vp, vp, sz, vp, sz, sz, sz, sz, f32, vp, sz]),
+    "llmtie_flash_attn_rows_batched": (i32, [vp, vp, sz, vp, sz, sz, sz, sz, sz, f32, vp, sz]),
     "llmtie_flash_rows_work_bytes": (sz, [sz, sz, sz]),
     "llmtie_decode_scratch_new": (i32, [vp, pvp]),
     "llmtie_decode_scratch_free": (None, [vp, vp]),

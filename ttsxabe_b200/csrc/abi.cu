@@ -629,29 +629,30 @@ extern "C" size_t llmtie_flash_rows_work_bytes(size_t t, size_t heads, size_t he
     return 2 * heads * rows_pad(t) * head_dim * sizeof(uint16_t);
 }
 
-extern "C" llmtie_status llmtie_flash_attn_rows(llmtie_gpu *g, const float *qkv, size_t qkv_len,
-                                                uint16_t *out, size_t out_len, size_t t,
-                                                size_t heads, size_t head_dim, float scale,
-                                                void *work, size_t work_bytes)
+static llmtie_status flash_rows_impl(llmtie_gpu *g, const float *qkv, size_t qkv_len,
+                                     uint16_t *out, size_t out_len, size_t batch, size_t t,
+                                     size_t heads, size_t head_dim, float scale, void *work,
+                                     size_t work_bytes)
 {
     NEED_HANDLE(g);
     if (head_dim != 64) return unsupported(head_dim, heads, heads);
     const size_t d = heads * head_dim;
-    if (qkv_len < t * 3 * d) {
+    if (qkv_len < batch * t * 3 * d) {
         return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
-                           t * 3 * d, qkv_len);
+                           batch * t * 3 * d, qkv_len);
     }
-    if (out_len < t * d) {
-        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", t * d,
-                           out_len);
+    if (out_len < batch * t * d) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           batch * t * d, out_len);
     }
     if (((uintptr_t)qkv & 15u) != 0) return misaligned("the stacked product", qkv, 16);
     if (((uintptr_t)out & 3u) != 0) return misaligned("the output", out, 4);
-    if (!fits_i32(t) || !fits_i32(3 * d)) {
+    if (!fits_i32(batch * t) || !fits_i32(3 * d) || batch > 65535) {
         return llmtie_fail(LLMTIE_ERR_INVALID, "attention geometry does not fit 32 bits");
     }
-    if (t == 0 || heads == 0) return LLMTIE_OK;
-    const size_t need = llmtie_flash_rows_work_bytes(t, heads, head_dim);
+    if (t == 0 || heads == 0 || batch == 0) return LLMTIE_OK;
+    const size_t one = llmtie_flash_rows_work_bytes(t, heads, head_dim);
+    const size_t need = batch * one;
     void *own = nullptr;
     if (work) {
         if (work_bytes < need) {
@@ -670,21 +671,27 @@ extern "C" llmtie_status llmtie_flash_attn_rows(llmtie_gpu *g, const float *qkv,
     llmtie_status st;
     {
         LaunchScope ls(g, "rows_stage");
-        launch_rows_stage(g->stream, qkv, ks, vs, (int)t, (int)tp, (int)heads, (int)head_dim);
+        launch_rows_stage(g->stream, qkv, ks, vs, (int)t, (int)tp, (int)heads, (int)head_dim,
+                          (int)batch);
         st = ls.done();
     }
-    if (st == LLMTIE_OK) {
+    // the attention kernel carries LLMTIE_TC_MAX_SEQ utterances a launch
+    for (size_t b0 = 0; b0 < batch && st == LLMTIE_OK; b0 += LLMTIE_TC_MAX_SEQ) {
+        const size_t nb = std::min<size_t>(LLMTIE_TC_MAX_SEQ, batch - b0);
         PrefillParams p;
         memset(&p, 0, sizeof(p));
-        p.nseq = 1;
-        p.seq[0].k = ks;
-        p.seq[0].v = vs;
-        p.seq[0].tq = (int)t;
-        p.seq[0].cap = (int)tp;
-        p.seq[0].tk = (int)t;
-        p.q = qkv;
+        p.nseq = (int)nb;
+        for (size_t b = 0; b < nb; b++) {
+            p.seq[b].k = ks + (b0 + b) * (one / sizeof(uint16_t));
+            p.seq[b].v = vs + (b0 + b) * (one / sizeof(uint16_t));
+            p.seq[b].row0 = (int)(b * t);
+            p.seq[b].tq = (int)t;
+            p.seq[b].cap = (int)tp;
+            p.seq[b].tk = (int)t;
+        }
+        p.q = qkv + b0 * t * 3 * d;
         p.q_stride = (long long)(3 * d);
-        p.out = out;
+        p.out = out + b0 * t * d;
         p.out_stride = (long long)d;
         p.heads = (int)heads;
         p.kv_heads = (int)heads;
@@ -700,6 +707,23 @@ extern "C" llmtie_status llmtie_flash_attn_rows(llmtie_gpu *g, const float *qkv,
     }
     if (own) llmtie_free(g, own);
     return st;
+}
+
+extern "C" llmtie_status llmtie_flash_attn_rows(llmtie_gpu *g, const float *qkv, size_t qkv_len,
+                                                uint16_t *out, size_t out_len, size_t t,
+                                                size_t heads, size_t head_dim, float scale,
+                                                void *work, size_t work_bytes)
+{
+    return flash_rows_impl(g, qkv, qkv_len, out, out_len, 1, t, heads, head_dim, scale, work,
+                           work_bytes);
+}
+
+extern "C" llmtie_status llmtie_flash_attn_rows_batched(
+    llmtie_gpu *g, const float *qkv, size_t qkv_len, uint16_t *out, size_t out_len, size_t batch,
+    size_t t, size_t heads, size_t head_dim, float scale, void *work, size_t work_bytes)
+{
+    return flash_rows_impl(g, qkv, qkv_len, out, out_len, batch, t, heads, head_dim, scale, work,
+                           work_bytes);
 }
 
 // ---- decode attention -----------------------------------------------------------

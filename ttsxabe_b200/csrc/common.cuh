@@ -84,9 +84,10 @@ void launch_cache_grow(cudaStream_t st, const void *src, void *dst, long long ro
                        long long len, long long src_stride, long long dst_stride, int esize);
 void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n);
 // Whisper encoder staging: qkv f32 [t][3*heads*64] -> K f16 [heads][tp][64],
-// V f16 [heads][64][tp] (tp = padded t), zero padded.
+// V f16 [heads][64][tp] (tp = padded t), zero padded; `batch` utterances one
+// after another in qkv, each with its K then V in the staging buffer.
 void launch_rows_stage(cudaStream_t st, const float *qkv, uint16_t *k, uint16_t *v, int t,
-                       int tp, int heads, int hd);
+                       int tp, int heads, int hd, int batch);
 
 // decode.cu
 #define LLMTIE_DECODE_MAX_SEQ 32

@@ -215,6 +215,10 @@ __global__ void rows_stage_kernel(const float *__restrict__ qkv, uint16_t *__res
 {
     __shared__ float tile[32][33];
     const int d = heads * hd;
+    // blockIdx.z is the utterance: its own [t][3d] product, its own staged K and V
+    qkv += (size_t)blockIdx.z * t * 3 * d;
+    k += (size_t)blockIdx.z * 2 * heads * tp * hd;
+    v += (size_t)blockIdx.z * 2 * heads * tp * hd;
     const int c0 = blockIdx.x * 32;   // channel within d
     const int t0 = blockIdx.y * 32;
     const size_t row = (size_t)3 * d;
@@ -410,9 +414,9 @@ void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n
 }
 
 void launch_rows_stage(cudaStream_t st, const float *qkv, uint16_t *k, uint16_t *v, int t,
-                       int tp, int heads, int hd)
+                       int tp, int heads, int hd, int batch)
 {
-    const dim3 grid((heads * hd + 31) / 32, (tp + 31) / 32);
+    const dim3 grid((heads * hd + 31) / 32, (tp + 31) / 32, batch);
     const dim3 block(32, 8);
     rows_stage_kernel<<<grid, block, 0, st>>>(qkv, k, v, t, tp, heads, hd);
 }

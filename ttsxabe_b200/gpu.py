@@ -330,6 +330,17 @@ class Gpu:
             head_dim, scale, None, 0))
         return out
 
+    def flash_attn_rows_batched(self, qkv, batch, t, heads, head_dim, scale, work=None,
+                                out=None) -> torch.Tensor:
+        """`flash_attn_rows` for `batch` utterances of one length in two launches:
+        qkv f32 [batch][t][3d] -> f16 [batch][t][d]."""
+        if out is None:
+            out = self._empty(batch * t * heads * head_dim, torch.float16)
+        _check(self._lib.llmtie_flash_attn_rows_batched(
+            self._h, qkv.data_ptr(), qkv.numel(), out.data_ptr(), out.numel(), batch, t, heads,
+            head_dim, scale, _ptr(work), 0 if work is None else work.numel() * work.element_size()))
+        return out
+
     # ---- decode ----------------------------------------------------------------------
 
     def attn_decode_f16(self, q, k, v, heads, kv_heads, head_dim, tk, cap, scale, scale_q,
