@@ -1,0 +1,98 @@
+"""Seeded random shapes through the decode and prefill entry points against the
+oracle: odd lengths, ragged batches, capacities whose value rows are 16-, 8-
+or only 4-byte aligned, every head grouping the entries take, the live length
+anywhere inside the capacity with NaN bits poisoning what lies beyond."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.helpers import (assert_close_to, assert_parity, lay_caches, normal_f16,
+                           poison_f16_bits)
+
+pytestmark = pytest.mark.gpu
+
+GROUPS_128 = [(4, 4), (8, 2), (32, 8), (12, 4), (4, 1), (6, 3)]
+GROUPS_64 = [(20, 20), (14, 2), (16, 2), (6, 6), (12, 4), (8, 1)]
+
+
+def _capacity(rng, tk, step):
+    return int(-(-(tk + int(rng.integers(0, 40))) // step) * step)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_decode_cases(gpu, seed):
+    from ttsxabe_b200 import DecodeScratch
+
+    rng = np.random.default_rng(1000 + seed)
+    hd = int(rng.choice([64, 128]))
+    heads, kv = (GROUPS_128 if hd == 128 else GROUPS_64)[int(rng.integers(0, 6))]
+    tk = int(rng.choice([1, 2, 31, 127, 128, 129, 500, 1027, 2999, 6000])) + int(rng.integers(0, 3))
+    cap = _capacity(rng, tk, int(rng.choice([4, 8, 8, 16])))
+    scale_q = bool(rng.integers(0, 2))
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, heads * hd)
+    kc, vc = lay_caches(normal_f16(rng, kv * tk * hd), normal_f16(rng, kv * tk * hd), kv, tk, hd,
+                        cap)
+    kbits = poison_f16_bits(O.round_f16(kc), kv, tk, hd, cap, False)
+    vbits = poison_f16_bits(O.round_f16(vc), kv, tk, hd, cap, True)
+    scratch = DecodeScratch()
+    got = gpu.download(gpu.attn_decode_f16(gpu.upload(q), gpu.upload_u16(kbits),
+                                           gpu.upload_u16(vbits), heads, kv, hd, tk, cap, scale,
+                                           scale_q, scratch))
+    want = O.decode_f64(q, O.round_f16(kc), O.round_f16(vc), heads, kv, hd, 0, tk, cap, scale,
+                        scale_q)
+    name = f"decode {heads}/{kv} hd {hd} tk {tk} cap {cap} scale_q {scale_q}"
+    assert_close_to(name, want, got, 2e-5)
+    assert_parity(name, want, got)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_ragged_decode_batches(gpu, seed):
+    from ttsxabe_b200 import DecodeScratch
+
+    rng = np.random.default_rng(2000 + seed)
+    hd = int(rng.choice([64, 128]))
+    heads, kv = (GROUPS_128 if hd == 128 else GROUPS_64)[int(rng.integers(0, 6))]
+    batch = int(rng.integers(1, 7))
+    tks = [int(rng.integers(1, 2500)) for _ in range(batch)]
+    caps = [_capacity(rng, t, 8) for t in tks]
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, batch * heads * hd)
+    ks, vs, host = [], [], []
+    for t, c in zip(tks, caps):
+        kc, vc = lay_caches(normal_f16(rng, kv * t * hd), normal_f16(rng, kv * t * hd), kv, t, hd, c)
+        host.append((O.round_f16(kc), O.round_f16(vc)))
+        ks.append(gpu.upload_u16(poison_f16_bits(host[-1][0], kv, t, hd, c, False)))
+        vs.append(gpu.upload_u16(poison_f16_bits(host[-1][1], kv, t, hd, c, True)))
+    got = gpu.download(gpu.decode_batched(gpu.upload(q), ks, vs, tks, caps, heads, kv, hd, scale,
+                                          False, DecodeScratch())).reshape(batch, -1)
+    for b in range(batch):
+        want = O.decode_f64(q.reshape(batch, -1)[b], host[b][0], host[b][1], heads, kv, hd, 0,
+                            tks[b], caps[b], scale, False)
+        assert_close_to(f"batch {tks} sequence {b}", want, got[b], 2e-5)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_prefill_cases(gpu, seed):
+    rng = np.random.default_rng(3000 + seed)
+    half = bool(rng.integers(0, 2))
+    hd = 128 if half else int(rng.choice([64, 128]))   # f16 caches: 128 only, as the reference
+    heads, kv = (GROUPS_128 if hd == 128 else GROUPS_64)[int(rng.integers(0, 6))]
+    causal = bool(rng.integers(0, 4)) or half
+    tq = int(rng.choice([1, 7, 64, 127, 128, 129, 200, 300])) + int(rng.integers(0, 2))
+    past = int(rng.choice([0, 0, 1, 33, 128, 200]))
+    tk = past + tq
+    cap = _capacity(rng, tk, int(rng.choice([2, 8])))
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, tq * heads * hd)
+    kc, vc = lay_caches(normal_f16(rng, kv * tk * hd), normal_f16(rng, kv * tk * hd), kv, tk, hd,
+                        cap)
+    if half:
+        out = gpu.flash_attn_f16(gpu.upload(q), gpu.upload_f16(kc), gpu.upload_f16(vc), tq, past,
+                                 heads, kv, hd, cap, scale, causal)
+    else:
+        out = gpu.flash_attn(gpu.upload(q), gpu.upload(kc), gpu.upload(vc), tq, past, heads, kv, hd,
+                             cap, scale, causal)
+    want = O.prefill(q, kc, vc, tq, past, heads, kv, hd, cap, scale, causal)
+    assert_parity(f"prefill {heads}/{kv} hd {hd} tq {tq} past {past} cap {cap} causal {causal} "
+                  f"f16 {half}", want, gpu.download(out))
