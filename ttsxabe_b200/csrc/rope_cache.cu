@@ -207,40 +207,64 @@ __global__ void round_f16_kernel(const float *__restrict__ src, uint16_t *__rest
     if (i < n) dst[i] = f16_bits(src[i]);
 }
 
-// Whisper encoder staging. qkv is [t][3*d] f32 with d = heads*hd: keys are
-// the column block [d, 2d), values [2d, 3d). Keys go to [heads][tp][hd] f16,
-// values transposed to [heads][hd][tp] f16; positions t..tp are zero.
-__global__ void rows_stage_kernel(const float *__restrict__ qkv, uint16_t *__restrict__ k,
-                                  uint16_t *__restrict__ v, int t, int tp, int heads, int hd)
+// Whisper encoder staging (hd 64): the k and v column blocks of qkv f32
+// [t][3*heads*64] go to K f16 [heads][tp][64] and V f16 [heads][64][tp], zero
+// padded to tp. One block = one head x 64 frames: every global access is a
+// whole 128-byte line or more (float4 loads of a frame's 64 channels, 8-byte
+// stores of four halves), the value tile is transposed through shared memory.
+// blockIdx.z is the utterance: its own [t][3d] product, its own staged K and V.
+__global__ void __launch_bounds__(256)
+rows_stage_kernel(const float *__restrict__ qkv, uint16_t *__restrict__ k,
+                  uint16_t *__restrict__ v, int t, int tp, int heads, int hd)
 {
-    __shared__ float tile[32][33];
+    __shared__ float tile[64][65];
     const int d = heads * hd;
-    // blockIdx.z is the utterance: its own [t][3d] product, its own staged K and V
     qkv += (size_t)blockIdx.z * t * 3 * d;
     k += (size_t)blockIdx.z * 2 * heads * tp * hd;
     v += (size_t)blockIdx.z * 2 * heads * tp * hd;
-    const int c0 = blockIdx.x * 32;   // channel within d
-    const int t0 = blockIdx.y * 32;
+    const int h = blockIdx.x;
+    const int t0 = blockIdx.y * 64;
     const size_t row = (size_t)3 * d;
-    // keys: straight copy with a cast
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int ti = t0 + r, c = c0 + threadIdx.x;
-        if (ti < tp && c < d) {
-            const float x = ti < t ? qkv[(size_t)ti * row + d + c] : 0.0f;
-            const int h = c / hd, j = c % hd;
-            k[((size_t)h * tp + ti) * hd + j] = f16_bits(x);
+    const int tid = threadIdx.x;
+    const int c4 = tid & 15;          // which float4 of the head's 64 channels
+    const int f0 = tid >> 4;          // frame within a pass of 16
+    // keys: cast and copy; values: into the tile
+#pragma unroll
+    for (int pass = 0; pass < 4; pass++) {
+        const int f = pass * 16 + f0;
+        const int ti = t0 + f;
+        float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), vx = kx;
+        if (ti < t) {
+            const float *src = qkv + (size_t)ti * row + (size_t)h * hd + 4 * c4;
+            kx = __ldg((const float4 *)(src + d));
+            vx = __ldg((const float4 *)(src + 2 * d));
         }
-    }
-    // values: transpose through the tile
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int ti = t0 + r, c = c0 + threadIdx.x;
-        tile[r][threadIdx.x] = (ti < t && c < d) ? qkv[(size_t)ti * row + 2 * d + c] : 0.0f;
+        if (ti < tp) {
+            uint2 o;
+            o.x = (uint32_t)f16_bits(kx.x) | ((uint32_t)f16_bits(kx.y) << 16);
+            o.y = (uint32_t)f16_bits(kx.z) | ((uint32_t)f16_bits(kx.w) << 16);
+            *(uint2 *)(k + ((size_t)h * tp + ti) * hd + 4 * c4) = o;
+        }
+        tile[f][4 * c4 + 0] = vx.x;
+        tile[f][4 * c4 + 1] = vx.y;
+        tile[f][4 * c4 + 2] = vx.z;
+        tile[f][4 * c4 + 3] = vx.w;
     }
     __syncthreads();
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int c = c0 + r, ti = t0 + threadIdx.x;
-        if (c < d && ti < tp) {
-            v[(size_t)c * tp + ti] = f16_bits(tile[threadIdx.x][r]);
+    // values, transposed: thread = (channel, four consecutive frames)
+    const int f4 = tid & 15;
+    const int ch0 = tid >> 4;
+#pragma unroll
+    for (int pass = 0; pass < 4; pass++) {
+        const int ch = pass * 16 + ch0;
+        const int ti = t0 + 4 * f4;
+        if (ti < tp) {   // tp is a multiple of 128: four frames are in or out together
+            uint2 o;
+            o.x = (uint32_t)f16_bits(tile[4 * f4 + 0][ch]) |
+                  ((uint32_t)f16_bits(tile[4 * f4 + 1][ch]) << 16);
+            o.y = (uint32_t)f16_bits(tile[4 * f4 + 2][ch]) |
+                  ((uint32_t)f16_bits(tile[4 * f4 + 3][ch]) << 16);
+            *(uint2 *)(v + ((size_t)h * hd + ch) * tp + ti) = o;
         }
     }
 }
@@ -416,9 +440,8 @@ void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n
 void launch_rows_stage(cudaStream_t st, const float *qkv, uint16_t *k, uint16_t *v, int t,
                        int tp, int heads, int hd, int batch)
 {
-    const dim3 grid((heads * hd + 31) / 32, (tp + 31) / 32, batch);
-    const dim3 block(32, 8);
-    rows_stage_kernel<<<grid, block, 0, st>>>(qkv, k, v, t, tp, heads, hd);
+    const dim3 grid(heads, (tp + 63) / 64, batch);   // hd is 64: a block is one head x 64 frames
+    rows_stage_kernel<<<grid, 256, 0, st>>>(qkv, k, v, t, tp, heads, hd);
 }
 
 void launch_varlen_rope_append(cudaStream_t st, const VarlenParams &p)
