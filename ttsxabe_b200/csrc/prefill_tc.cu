@@ -579,37 +579,83 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             if (ok) {
                 tc_fence_after();
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                const long long orow = (long long)(sq.row0 + me.r0 + row) * p.out_stride + me.head * HD;
+                // A thread holds a row, and rows lie heads*hd elements apart: stored
+                // straight from the registers every 16-byte store of a warp would
+                // open its own line. So each warp turns its 32 rows through shared
+                // memory - its quarter of the
+                // tile's Q, which no MMA reads any more - and stores whole row
+                // segments of RB bytes, a row per LPR lanes. 16-byte chunks are
+                // swizzled by the row so that neither side has bank conflicts.
+                constexpr int RB = HD * 2;                 // bytes of a row a pass moves
+                constexpr int LPR = RB / 16;               // lanes to a row on the way out
+                constexpr int RPI = 32 / LPR;              // rows an instruction stores
+                const uint32_t scratch = q_smem(t) + (uint32_t)(warp & 3) * (32u * RB);
+                const int esize = p.out_f16 ? 2 : 4;
+                const int passes = HD * esize / RB;        // 1 for f16, 2 for f32
+                unsigned char *obase = (unsigned char *)p.out +
+                                       ((long long)(sq.row0 + me.r0 + 32 * (warp & 3)) * p.out_stride +
+                                        me.head * HD) * esize;
+                for (int ps = 0; ps < passes; ps++) {
+                    // ---- registers -> shared: this lane's row, RB bytes of it ------------
+                    if (p.out_f16) {
 #pragma unroll
-                for (int c = 0; c < HD / 32; c++) {
-                    uint32_t o[32];
-                    tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
-                    tmem_wait_ld();
-                    if (me.r0 + row < sq.tq) {
-                        if (p.out_f16) {
-                            uint16_t *dst = (uint16_t *)p.out + orow + 32 * c;
+                        for (int c = 0; c < HD / 32; c++) {
+                            uint32_t o[32];
+                            tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
+                            tmem_wait_ld();
 #pragma unroll
                             for (int i = 0; i < 4; i++) {
-                                uint4 v;
-                                v.x = pack_f16(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-                                v.y = pack_f16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-                                v.z = pack_f16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-                                v.w = pack_f16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-                                *(uint4 *)(dst + 8 * i) = v;
+                                uint32_t v0 = pack_f16(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+                                uint32_t v1 = pack_f16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+                                uint32_t v2 = pack_f16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+                                uint32_t v3 = pack_f16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+                                const int k = 4 * c + i;   // 16-byte chunk of the row
+                                const uint32_t dst = scratch + (uint32_t)lane * RB +
+                                                     (uint32_t)((k ^ (lane & (LPR - 1))) << 4);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                             "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                                             : "memory");
                             }
-                        } else {
-                            float *dst = (float *)p.out + orow + 32 * c;
+                        }
+                    } else {
+#pragma unroll
+                        for (int cc = 0; cc < HD / 64; cc++) {
+                            const int c = ps * (HD / 64) + cc;
+                            uint32_t o[32];
+                            tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
+                            tmem_wait_ld();
 #pragma unroll
                             for (int i = 0; i < 8; i++) {
-                                float4 v;
-                                v.x = __uint_as_float(o[4 * i]) * inv;
-                                v.y = __uint_as_float(o[4 * i + 1]) * inv;
-                                v.z = __uint_as_float(o[4 * i + 2]) * inv;
-                                v.w = __uint_as_float(o[4 * i + 3]) * inv;
-                                *(float4 *)(dst + 4 * i) = v;
+                                const int k = 8 * cc + i;
+                                const uint32_t dst = scratch + (uint32_t)lane * RB +
+                                                     (uint32_t)((k ^ (lane & (LPR - 1))) << 4);
+                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                             "f"(__uint_as_float(o[4 * i]) * inv),
+                                             "f"(__uint_as_float(o[4 * i + 1]) * inv),
+                                             "f"(__uint_as_float(o[4 * i + 2]) * inv),
+                                             "f"(__uint_as_float(o[4 * i + 3]) * inv)
+                                             : "memory");
                             }
                         }
                     }
+                    __syncwarp();
+                    // ---- shared -> global: whole row segments ----------------------------
+                    const int k = lane % LPR;
+#pragma unroll
+                    for (int it = 0; it < 32 / RPI; it++) {
+                        const int r = it * RPI + lane / LPR;
+                        uint4 v;
+                        const uint32_t src = scratch + (uint32_t)r * RB +
+                                             (uint32_t)((k ^ (r & (LPR - 1))) << 4);
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                     : "r"(src));
+                        if (me.r0 + 32 * (warp & 3) + r < sq.tq) {
+                            *(uint4 *)(obase + (long long)r * p.out_stride * esize + ps * RB +
+                                       k * 16) = v;
+                        }
+                    }
+                    __syncwarp();
                 }
             }
             tc_fence_before();
@@ -790,7 +836,7 @@ bool prefill_tc_eligible(const PrefillParams &p, int hd)
     if ((hd != 128 && hd != 64) || p.kv_f32) return false;
     if (p.nseq > LLMTIE_TC_MAX_SEQ) return false;
     if (((uintptr_t)p.q & 15u) != 0 || (p.q_stride & 3) != 0) return false;
-    if (((uintptr_t)p.out & 15u) != 0 || (p.out_stride & 3) != 0) return false;
+    if (((uintptr_t)p.out & 15u) != 0 || (p.out_stride & (p.out_f16 ? 7 : 3)) != 0) return false;
     for (int b = 0; b < p.nseq; b++) {
         if (p.seq[b].cap % 8 != 0) return false;
         // short sequences stay with the general kernel (a box wider than the tensor)
