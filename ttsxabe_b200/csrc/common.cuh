@@ -226,6 +226,7 @@ cudaError_t launch_prefill_mma(cudaStream_t st, const PrefillParams &p, int hd);
 struct PrefillTcSeq {
     int row0, tq, past, tk;   // tk: keys the sequence holds (past + tq when causal)
 };
+#define LLMTIE_TC_MAX_ORDER 256
 struct PrefillTcParams {
     alignas(64) CUtensorMap kmap[LLMTIE_TC_MAX_SEQ];
     alignas(64) CUtensorMap vmap[LLMTIE_TC_MAX_SEQ];
@@ -240,6 +241,11 @@ struct PrefillTcParams {
     int pair_rows;            // pair two row blocks of one head instead of two heads of a group
     float q_scale, sl2;
     int *status;              // set to a site code when a bounded wait gives up
+    // Ragged batches: the (sequence, row block) of grid row blockIdx.y, longest
+    // first over the whole batch and without the empty ones; n_order == 0 means
+    // blockIdx.z is the sequence and blockIdx.y the row block.
+    int n_order;
+    uint16_t order[LLMTIE_TC_MAX_ORDER];   // sequence << 8 | row-block slot
 };
 bool prefill_tc_eligible(const PrefillParams &p, int hd);
 cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, int *status);

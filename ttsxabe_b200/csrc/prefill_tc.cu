@@ -38,6 +38,9 @@
 #include "common.cuh"
 
 #include <math_constants.h>
+
+#include <algorithm>
+#include <vector>
 #include <stdlib.h>
 
 namespace {
@@ -304,7 +307,10 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     const int lane = tid & 31;
 
     // ---- which two tiles this block carries ------------------------------------------
-    const PrefillTcSeq sq = p.seq[blockIdx.z];
+    // which sequence and which of its row-block slots (0 = the longest rows)
+    const int seq_i = p.n_order ? (int)(p.order[blockIdx.y] >> 8) : (int)blockIdx.z;
+    const int slot_y = p.n_order ? (int)(p.order[blockIdx.y] & 255u) : (int)blockIdx.y;
+    const PrefillTcSeq sq = p.seq[seq_i];
     const int group = p.heads / p.kv_heads;
     const int row_blocks = (sq.tq + BM - 1) / BM;
     int kh, head_a, head_b, r0_a, r0_b;
@@ -313,13 +319,13 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     if (!p.pair_rows) {
         const int pairs = group >> 1;
         kh = blockIdx.x / pairs;
-        const int rb = row_blocks - 1 - (int)blockIdx.y;
+        const int rb = row_blocks - 1 - slot_y;
         head_a = kh * group + 2 * (blockIdx.x % pairs);
         head_b = head_a + 1;
         r0_a = r0_b = rb * BM;
     } else {
         kh = blockIdx.x / group;
-        const int rp = (row_blocks + 1) / 2 - 1 - (int)blockIdx.y;
+        const int rp = (row_blocks + 1) / 2 - 1 - slot_y;
         head_a = head_b = blockIdx.x;
         r0_a = 2 * rp * BM;
         r0_b = (2 * rp + 1) * BM;
@@ -663,8 +669,8 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     } else if (warp == 8) {
         // =============================== TMA producer =======================================
         if (lane == 0) {
-            const CUtensorMap *kmap = &p.kmap[blockIdx.z];
-            const CUtensorMap *vmap = &p.vmap[blockIdx.z];
+            const CUtensorMap *kmap = &p.kmap[seq_i];
+            const CUtensorMap *vmap = &p.vmap[seq_i];
             for (int j = 0; j < n_max; j++) {
                 const int s = j & 1;
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
@@ -902,6 +908,33 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, i
         grid = dim3(p.kv_heads * (group / 2), row_blocks, p.nseq);
     } else {
         grid = dim3(p.heads, (row_blocks + 1) / 2, p.nseq);
+    }
+    if (p.nseq > 1) {
+        // A ragged batch: one grid row per (sequence, row-block slot) that has
+        // work, the slots with the most key tiles first over the whole batch,
+        // so that the SMs' last blocks are the short ones.
+        struct Item { int keys, seq, slot; };
+        std::vector<Item> items;
+        for (int b = 0; b < p.nseq; b++) {
+            const PrefillSeq &s = p.seq[b];
+            const int rbs = (s.tq + BM - 1) / BM;
+            const int slots = tp.pair_rows ? (rbs + 1) / 2 : rbs;
+            for (int y = 0; y < slots; y++) {
+                const int top = tp.pair_rows ? std::min(rbs, 2 * (slots - 1 - y) + 2)
+                                             : rbs - y;          // row blocks up to and with it
+                const int keys = p.causal ? s.past + std::min(s.tq, top * BM) : s.tk;
+                items.push_back({keys, b, y});
+            }
+        }
+        if (!items.empty() && items.size() <= LLMTIE_TC_MAX_ORDER) {
+            std::stable_sort(items.begin(), items.end(),
+                             [](const Item &a, const Item &b) { return a.keys > b.keys; });
+            tp.n_order = (int)items.size();
+            for (size_t i = 0; i < items.size(); i++) {
+                tp.order[i] = (uint16_t)((items[i].seq << 8) | items[i].slot);
+            }
+            grid = dim3(grid.x, (unsigned)items.size(), 1);
+        }
     }
     if (hd == 128) {
         prefill_tc_kernel<128><<<grid, kThreads, Geo<128>::SMEM, st>>>(tp);
