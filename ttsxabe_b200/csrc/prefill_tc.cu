@@ -548,31 +548,28 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 const uint64_t sl2_2 = pack2(sl2, sl2);
                 const uint64_t neg_2 = pack2(-m_ref * sl2, -m_ref * sl2);
                 uint64_t lc[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of partial sums
-                // two 32-key chunks at a time: the stores to tensor memory fence the
-                // compiler's scheduling, and 32 independent pairs hide the latency of
-                // ex2 and the conversions better than 16 do
+                // All 64 pairs first, the four stores to tensor memory after them:
+                // a store fences the compiler's scheduling, and the more independent
+                // pairs it may interleave, the better the latency of ex2 and of the
+                // conversions is hidden (one warp has the scheduler almost to itself).
+                uint32_t pk[4][16];
 #pragma unroll
-                for (int c2 = 0; c2 < 2; c2++) {
-                    uint32_t pk[2][16];
+                for (int c = 0; c < 4; c++) {
 #pragma unroll
-                    for (int cc = 0; cc < 2; cc++) {
-#pragma unroll
-                        for (int i = 0; i < 16; i++) {
-                            const int c = 2 * c2 + cc;
-                            const uint64_t x = fma2(pack2(__uint_as_float(s[c][2 * i]),
-                                                          __uint_as_float(s[c][2 * i + 1])),
-                                                    sl2_2, neg_2);
-                            float p0, p1;
-                            unpack2(x, p0, p1);
-                            p0 = ex2(p0);
-                            p1 = ex2(p1);
-                            lc[i & 3] = add2(lc[i & 3], pack2(p0, p1));
-                            pk[cc][i] = pack_f16(p0, p1);
-                        }
+                    for (int i = 0; i < 16; i++) {
+                        const uint64_t x = fma2(pack2(__uint_as_float(s[c][2 * i]),
+                                                      __uint_as_float(s[c][2 * i + 1])),
+                                                sl2_2, neg_2);
+                        float p0, p1;
+                        unpack2(x, p0, p1);
+                        p0 = ex2(p0);
+                        p1 = ex2(p1);
+                        lc[i & 3] = add2(lc[i & 3], pack2(p0, p1));
+                        pk[c][i] = pack_f16(p0, p1);
                     }
-                    tmem_st16(lane_addr + p_col(t) + 32 * c2, pk[0]);
-                    tmem_st16(lane_addr + p_col(t) + 32 * c2 + 16, pk[1]);
                 }
+#pragma unroll
+                for (int c = 0; c < 4; c++) tmem_st16(lane_addr + p_col(t) + 16 * c, pk[c]);
                 {
                     float a0, a1, b0, b1;
                     unpack2(add2(lc[0], lc[1]), a0, a1);
