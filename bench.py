@@ -18,6 +18,13 @@ q/k/v projections copied from pinned host memory, RoPE and the cache write,
 attention, and the context read back. The CPU arm (`--impl reference`, and the
 `cpu_baseline` object of the default arm) times the C restatement of the
 reference's own scalar attention on the host cores.
+
+The same line carries a `prefill` object: the causal 8192-position prefill of
+the same contract, split by KV head over the N GPUs with no exchange, in
+TFLOP/s against the tensor-pipe roofline, with its own end-to-end and CPU
+figures; a few of its rows are checked against the CPU oracle before it is
+timed. `sustained` repeats the decode step for at least two seconds, the
+regime in which the part runs into its power cap.
 """
 from __future__ import annotations
 
@@ -39,6 +46,11 @@ HEADS, KV_HEADS, HD = 32, 8, 128
 SCALE = float(np.float32(HD) ** np.float32(-0.5))
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1590.0
+FALLBACK_TFLOPS_SUSTAINED = 1400.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one prefill_tc_kernel<128>
+# launch at 8192 positions, from the capture summarised in
+# profiles/prefill_tc_kernel_seq8192.md (None until one has been taken).
+PREFILL_DRAM_BYTES_8K = None
 
 # DRAM traffic of the dominant kernel from the ncu captures summarised under
 # profiles/. The decode entry is dram__bytes_read.sum + dram__bytes_write.sum
@@ -48,7 +60,9 @@ FALLBACK_TFLOPS = 1590.0
 # large to capture.
 NCU_TRAFFIC = {
     "decode128k": (537.303e6 + 4.539e6) / 536.870912e6,
-    "prefill8k": None,
+    # bytes per launch of the 8192-position prefill on one GPU (32 / 8 heads),
+    # captured at that size; a rank holding fewer KV heads moves that share
+    "prefill8k": PREFILL_DRAM_BYTES_8K,
 }
 
 
@@ -60,6 +74,14 @@ def measured_peaks():
         return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, FALLBACK_TFLOPS, "fallback"
+
+
+def measured_sustained_tflops():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        return FALLBACK_TFLOPS_SUSTAINED
 
 
 class ClockSampler:
@@ -196,6 +218,42 @@ def time_steps(gpu, fn, steps: int, warmup: int) -> float:
 
 # ---- workloads ------------------------------------------------------------------
 
+def oracle_check_sharded_decode(gpu, q, out, ks, vs, tk, ctx, world, rank):
+    """The merged output of the sharded step against the CPU oracle: every
+    rank's slice of sequence 0, KV head 0 (keys [tk][hd], values [hd][tk]) is
+    gathered, rank 0 lays them end to end (67 MB at 131072 keys) and runs the
+    f64 oracle on that KV head's four query heads. Returns max-abs on rank 0,
+    None elsewhere (and None when the slices are not all the same length)."""
+    import torch
+    import torch.distributed as dist
+
+    from oracle import oracle as O
+
+    group = HEADS // KV_HEADS
+    if world > 1 and ctx % (8 * world) != 0:
+        return None
+    with torch.cuda.stream(gpu.stream):
+        kslice = ks[0][:tk * HD].contiguous()                         # head 0: [tk][hd]
+        vslice = vs[0][:HD * tk].contiguous()                         # head 0: [hd][tk]
+        mine = torch.cat([kslice, vslice])
+        if world > 1:
+            allk = torch.empty(world * mine.numel(), dtype=mine.dtype, device=mine.device)
+            dist.all_gather_into_tensor(allk, mine)
+        else:
+            allk = mine
+        gpu.synchronize()
+        host = allk.cpu().view(torch.int16).numpy().view(np.uint16).reshape(world, 2, tk * HD)
+        got = out[:group * HD].cpu().numpy()
+        hq = q[:group * HD].cpu().numpy()
+    if rank != 0:
+        return None
+    kfull = np.ascontiguousarray(host[:, 0, :].reshape(world * tk, HD)).reshape(-1)
+    vfull = np.ascontiguousarray(
+        host[:, 1, :].reshape(world, HD, tk).transpose(1, 0, 2)).reshape(-1)
+    want = O.decode_f64(hq, kfull, vfull, group, 1, HD, 0, world * tk, world * tk, SCALE, False)
+    return float(np.abs(want - got).max())
+
+
 def decode128k(args, world, rank, local):
     """Config 5, decode: batch 8 x 131072 context, KV split over the ranks."""
     import torch
@@ -219,15 +277,21 @@ def decode128k(args, world, rank, local):
                               SCALE, p2p=False if args.exchange == "nccl" else args.exchange)
     gpu.synchronize()
 
-    # The sharded paths have no single-GPU test to stand on, so the fused
-    # exchange is checked here against the all-gather path on the same inputs.
+    # The sharded paths have no single-GPU test to stand on, so the step is
+    # checked here: against the CPU oracle on one KV head of one sequence, and
+    # the fused exchange against the all-gather path on the same inputs.
     exchange_err = None
     fused_exchange = sd.exchange.startswith("peer-")
+    with torch.cuda.stream(gpu.stream):
+        first = sd.decode(q).clone()
+    oracle_err = oracle_check_sharded_decode(gpu, q, first, ks, vs, tk, ctx, world, rank)
+    if oracle_err is not None and not (oracle_err < 2e-5 * 4.0):
+        raise SystemExit("decode disagrees with the CPU oracle: max-abs %g" % oracle_err)
     if fused_exchange:
         ref = ShardedDecode.on_gpu(gpu, ks, vs, [tk] * batch, [cap] * batch, HEADS, KV_HEADS, HD,
                                    SCALE, p2p=False)
         with torch.cuda.stream(gpu.stream):   # the copies must queue behind the kernels
-            a = sd.decode(q).clone()
+            a = first
             b = sd.decode(q).clone()      # a second step: the other gather buffer
             c = ref.decode(q).clone()
             gpu.synchronize()
@@ -279,12 +343,32 @@ def decode128k(args, world, rank, local):
     pos_t, cap_t = gpu.i32_table([pos] * batch), gpu.i32_table([cap] * batch)
     ks_t, vs_t = gpu.ptr_table(ks), gpu.ptr_table(vs)
 
-    def e2e_step():
+    def e2e_enqueue():
         lib.llmtie_upload(h, dqkv.data_ptr(), hqkv.data_ptr(), batch * (nq + 2 * nkv) * esz)
         gpu.rope_cache_batched(dq, dk, dv, None, HEADS, KV_HEADS, HD, 10000.0, pos_t, ks_t, vs_t,
                                cap_t)
-        out = sd.decode(dqkv)          # q is the first batch*nq floats
+        return sd.decode(dqkv)         # q is the first batch*nq floats
+
+    def e2e_step():
+        out = e2e_enqueue()
         lib.llmtie_download(h, hout.data_ptr(), out.data_ptr(), batch * nq * esz)
+
+    e2e_graph = bool(world > 1 and not args.no_graph)
+    if e2e_graph:
+        # The same calls - the copy in from pinned host memory, RoPE and the
+        # cache write, attention, exchange and merge, the copy out - recorded
+        # once and replayed; the step ends with the handle's synchronize.
+        e2e_step()
+        torch.cuda.synchronize()
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=gpu.stream):
+            out = e2e_enqueue()
+            hout.copy_(out, non_blocking=True)
+
+        def e2e_step():
+            with torch.cuda.stream(gpu.stream):
+                g2.replay()
+            gpu.synchronize()
 
     for _ in range(max(1, args.warmup)):
         e2e_step()
@@ -296,6 +380,11 @@ def decode128k(args, world, rank, local):
     e2e_secs = max_over_ranks((time.perf_counter() - w0), gpu.device) / args.steps
     clocks.__exit__()
     clk = clocks.summary()
+
+    # ---- the same step for at least two seconds: the power-capped regime --------
+    sus_steps = max(200, int(2.2 / max(secs / args.steps, 1e-6)))
+    with ClockSampler(local) as sus_clocks:
+        sus_secs = time_steps(gpu, step, sus_steps, 3)
 
     hbm, _, which = measured_peaks()
     per_step = secs / args.steps
@@ -314,9 +403,7 @@ def decode128k(args, world, rank, local):
         "dtype": "f16 KV cache, f32 accumulate",
         "data": "synthetic",
         "config": {
-            "workload": "config 5 decode: batch %d, context %d per sequence, 32 Q / 8 KV heads, "
-                        "head_dim 128, f16 KV ~N(0,1), KV sequence split evenly over the GPUs, "
-                        "all-gather of (O, max, sum), LSE merge" % (batch, ctx),
+            "workload": WORKLOAD % (batch, ctx),
             "global_batch": batch,
             "context": ctx,
             "parallelism": "kv-seq-shard x%d" % world,
@@ -330,6 +417,7 @@ def decode128k(args, world, rank, local):
             "ms_per_step": e2e_secs * 1e3,
             "h2d_bytes_per_step": batch * (nq + 2 * nkv) * esz,
             "d2h_bytes_per_step": batch * nq * esz,
+            "cuda_graph": e2e_graph,
         },
         "gpu_launches": int(launches),
         "cuda_graph": bool(world > 1 and not args.no_graph),
@@ -339,6 +427,16 @@ def decode128k(args, world, rank, local):
                      "peer-fused": "peer-memory push, wait and merge all fused into the decode "
                                    "kernel"}[sd.exchange],
         "exchange_max_abs_vs_allgather": exchange_err,
+        "exchange_max_abs_vs_oracle": oracle_err,
+        "sustained": {
+            "steps": sus_steps,
+            "seconds": sus_secs,
+            "ms_per_step": sus_secs / sus_steps * 1e3,
+            "value": kv_bytes_total / (sus_secs / sus_steps) / 1e9,
+            "unit": "GB/s",
+            "frac_of_hbm_peak_per_gpu": kv_bytes_rank / (sus_secs / sus_steps) / 1e9 / hbm,
+            "clocks": sus_clocks.summary(),
+        },
         "roofline": {
             "bound": "hbm",
             "achieved": achieved,
@@ -354,68 +452,161 @@ def decode128k(args, world, rank, local):
             "frac_of_nominal_8tbs": achieved / 8000.0,
         },
     }
+    # free the 4.3 GB of cache before the prefill leg
+    del sd, ks, vs
     return gpu, line
 
 
-def prefill8k(args, world, rank, local):
-    """Config 5, prefill: causal, 8192 positions, split by KV head, no exchange."""
+WORKLOAD = ("config 5 decode: batch %d, context %d per sequence, 32 Q / 8 KV heads, "
+            "head_dim 128, f16 KV ~N(0,1), KV sequence split evenly over the GPUs, "
+            "all-gather of (O, max, sum), LSE merge")
+
+
+def cpu_prefill_sample(q_rows, kc, vc, rows, past, heads, kv, cap):
+    """Times the oracle's threaded prefill on the last `rows` query rows of the
+    sequence, every head. Returns (TFLOP/s, threads, seconds, output)."""
+    from oracle import oracle as O
+
+    t0 = time.perf_counter()
+    out = np.empty(rows * heads * HD, dtype=np.float32)
+    used = O.lib().orc_prefill_fast(q_rows.ctypes.data, heads * HD, kc.ctypes.data,
+                                    vc.ctypes.data, 1, rows, past, 0, heads, kv, HD, cap, SCALE, 1,
+                                    0, out.ctypes.data, heads * HD, 0)
+    dt = time.perf_counter() - t0
+    pairs = sum(past + r + 1 for r in range(rows))
+    return 4.0 * HD * heads * pairs / dt / 1e12, int(used), dt, out
+
+
+def prefill_leg(args, gpu, world, rank, local):
+    """Config 5, prefill: causal, 8192 positions, split by KV head, no
+    exchange. Returns the `prefill` object of the bench line."""
     import torch
 
-    from ttsxabe_b200 import Gpu
+    from oracle import oracle as O
     from ttsxabe_b200.sharded import kv_head_shard
 
     tq = args.seq
-    gpu = Gpu.open(local)
     h0, h1 = kv_head_shard(KV_HEADS, world, rank)
     kv = h1 - h0
     heads = kv * (HEADS // KV_HEADS)
     cap = tq
     kc = device_normal_f16(gpu, kv * cap * HD, 11 + rank)
     vc = device_normal_f16(gpu, kv * cap * HD, 13 + rank)
-    with torch.cuda.stream(gpu.stream):
-        q = torch.randn(tq * heads * HD, device=gpu.device).to(torch.float16).to(torch.float32)
-    out = gpu.uninit(tq * heads * HD)
+    n = tq * heads * HD
+    hq = torch.randn(n).to(torch.float16).to(torch.float32).pin_memory()
+    hout = torch.empty(n).pin_memory()
+    q = gpu.uninit(n)
+    out = gpu.uninit(n)
     lib, h = gpu._lib, gpu._h
+    with torch.cuda.stream(gpu.stream):
+        q.copy_(hq, non_blocking=True)
 
     def step():
         lib.llmtie_flash_attn_f16(h, q.data_ptr(), q.numel(), kc.data_ptr(), kc.numel(),
                                   vc.data_ptr(), vc.numel(), out.data_ptr(), out.numel(), tq, 0,
                                   heads, kv, HD, cap, SCALE, 1)
 
+    # ---- a few rows against the CPU oracle before anything is timed -------------
+    step()
+    gpu.synchronize()
+    parity = None
+    cpu = None
+    if rank == 0:
+        hk = kc.cpu().view(torch.int16).numpy().view(np.uint16)
+        hv = vc.cpu().view(torch.int16).numpy().view(np.uint16)
+        got = out.cpu().numpy().reshape(tq, heads * HD)
+        hq2 = hq.numpy().reshape(tq, heads * HD)
+        worst_abs, worst_rel = 0.0, 0.0
+        for r0 in sorted({0, tq // 2 - 1, tq - 16}):
+            want = O.prefill(np.ascontiguousarray(hq2[r0:r0 + 16]), hk, hv, 16, r0, heads, kv, HD,
+                             cap, SCALE, True)
+            g16 = got[r0:r0 + 16].reshape(-1)
+            worst_abs = max(worst_abs, float(np.abs(want - g16).max()))
+            worst_rel = max(worst_rel, float(np.linalg.norm(want - g16) / np.linalg.norm(want)))
+        parity = {"rows_checked": "16 rows from each of 0, %d and %d, every head, f64 oracle"
+                                  % (tq // 2 - 1, tq - 16),
+                  "max_abs": worst_abs, "rel_l2": worst_rel}
+        if not (worst_abs <= 2e-3 and worst_rel <= 1e-3):
+            raise SystemExit("prefill disagrees with the CPU oracle: %s" % parity)
+        if world == 1 and not args.no_cpu:
+            rows = min(256, tq)
+            tf_cpu, used, dt, cpu_out = cpu_prefill_sample(
+                np.ascontiguousarray(hq2[tq - rows:]), hk, hv, rows, tq - rows, heads, kv, cap)
+            cpu = {"value": tf_cpu, "unit": "TFLOP/s", "cores": used, "kind": "port",
+                   "sample": "the last %d of the %d query rows, every head (%.2f s); the C "
+                             "restatement of the reference's scalar attention, threaded over "
+                             "heads and row blocks" % (rows, tq, dt)}
+
     launches0 = gpu.launch_count()
     with ClockSampler(local) as clocks:
         secs = time_steps(gpu, step, args.steps, args.warmup)
     launches = gpu.launch_count() - launches0 - args.warmup
+
+    # ---- end to end: q from pinned host memory, the context back -----------------
+    def e2e_step():
+        lib.llmtie_upload(h, q.data_ptr(), hq.data_ptr(), n * 4)
+        step()
+        lib.llmtie_download(h, hout.data_ptr(), out.data_ptr(), n * 4)
+
+    e2e_step()
+    barrier_sync(gpu)
+    e2e_n = max(3, min(args.steps, 10))
+    w0 = time.perf_counter()
+    for _ in range(e2e_n):
+        e2e_step()
+    barrier_sync(gpu)
+    e2e_secs = max_over_ranks(time.perf_counter() - w0, gpu.device) / e2e_n
+
     flops_total = 4.0 * HD * HEADS * (tq * (tq + 1) / 2)
     flops_rank = 4.0 * HD * heads * (tq * (tq + 1) / 2)
     _, tf, which = measured_peaks()
+    tf_sus = measured_sustained_tflops()
     per_step = secs / args.steps
     achieved = flops_rank / per_step / 1e12
-    line = {
+    traffic = NCU_TRAFFIC["prefill8k"]
+    if traffic is not None:
+        traffic = traffic * heads / HEADS * (tq / 8192.0)
+    res = {
         "metric": "attn prefill TFLOP/s",
         "value": flops_total / per_step / 1e12,
         "unit": "TFLOP/s",
-        "n_gpus": world,
-        "steps": args.steps,
-        "warmup": args.warmup,
         "ms_per_step": per_step * 1e3,
-        "higher_is_better": True,
-        "scaling": "strong",
-        "vs_baseline": None,
-        "dtype": "f16 operands, f32 accumulate",
-        "data": "synthetic",
-        "config": {"workload": "config 5 prefill: causal, seq %d, 32 Q / 8 KV heads, head_dim "
-                               "128, sharded by KV head" % tq,
-                   "seq_len": tq, "parallelism": "kv-head-shard x%d" % world,
-                   "l2": "flushed by the %d MB output written each step" % (out.numel() * 4 >> 20)},
+        "steps": args.steps,
         "tokens_per_s": tq / per_step,
+        "scaling": "strong, kv-head-shard x%d, no exchange" % world,
+        "config": {"workload": "config 5 prefill: causal, seq %d, 32 Q / 8 KV heads, head_dim "
+                               "128, f16 K/V ~N(0,1), sharded by KV head" % tq,
+                   "seq_len": tq,
+                   "l2": "flushed by the %d MB output written each step" % (n * 4 >> 20)},
+        "dtype": "f16 operands, f32 accumulate",
         "clocks": clocks.summary(),
         "gpu_launches": int(launches),
+        "parity_vs_oracle": parity,
+        "e2e": {"value": flops_total / e2e_secs / 1e12, "unit": "TFLOP/s",
+                "ms_per_step": e2e_secs * 1e3, "h2d_bytes_per_step": n * 4,
+                "d2h_bytes_per_step": n * 4},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf, "unit": "TFLOP/s",
-                     "frac": achieved / tf, "traffic": NCU_TRAFFIC["prefill8k"],
-                     "peak_source": "of " + which,
+                     "frac": achieved / tf, "frac_of_sustained": achieved / tf_sus,
+                     "traffic": traffic, "peak_source": "of " + which,
+                     "kernel": "prefill_tc_kernel<128>", "kernel_ms": per_step * 1e3,
+                     "algorithmic_flops_per_launch": flops_rank,
                      "frac_of_nominal_2250": achieved / 2250.0},
     }
+    if cpu is not None:
+        res["cpu_baseline"] = cpu
+    return res
+
+
+def prefill8k(args, world, rank, local):
+    """The prefill leg on its own, as a bench line."""
+    from ttsxabe_b200 import Gpu
+
+    gpu = Gpu.open(local)
+    res = prefill_leg(args, gpu, world, rank, local)
+    line = dict(res)
+    line.update({"n_gpus": world, "warmup": args.warmup, "higher_is_better": True,
+                 "scaling": "strong", "vs_baseline": None, "data": "synthetic"})
+    line["config"] = dict(res["config"], parallelism="kv-head-shard x%d" % world)
     return gpu, line
 
 
@@ -547,16 +738,30 @@ def other_configs(args, world, rank, local):
 
 # ---- CPU arms ---------------------------------------------------------------------
 
+def host_normal_f16(n: int, seed: int) -> np.ndarray:
+    """n i.i.d. N(0,1) values rounded to f16 (as bits), made on the host cores."""
+    import torch
+
+    gen = torch.Generator()
+    gen.manual_seed(seed)
+    out = np.empty(n, dtype=np.uint16)
+    step = 1 << 26
+    for a in range(0, n, step):
+        b = min(n, a + step)
+        out[a:b] = torch.randn(b - a, generator=gen).to(torch.float16).view(torch.int16) \
+            .numpy().view(np.uint16)
+    return out
+
+
 def cpu_decode_sample(context: int, reps: int, threads: int = 0):
     """Times the oracle's threaded decode on one sequence of the workload
     (1 of 8; every sequence is the same amount of work). Returns GB/s."""
     from oracle import oracle as O
 
-    rng = np.random.default_rng(0)
     n = KV_HEADS * context * HD
-    k = rng.integers(0, 0x3C00, size=n, dtype=np.uint16)   # finite positive halves
-    v = rng.integers(0, 0x3C00, size=n, dtype=np.uint16)
-    q = rng.standard_normal(HEADS * HD).astype(np.float32)
+    k = host_normal_f16(n, 1)
+    v = host_normal_f16(n, 2)
+    q = np.random.default_rng(0).standard_normal(HEADS * HD).astype(np.float32)
     best = None
     used = 0
     for _ in range(reps):
@@ -571,42 +776,45 @@ def cpu_decode_sample(context: int, reps: int, threads: int = 0):
 
 def reference_arm(args):
     """The reference's own CPU attention (its scalar decode restated in C,
-    threaded over heads and key slabs) on the host cores, on a bounded sample
-    of the same workload: one sequence of the eight per step."""
+    threaded over heads and key slabs) on the host cores, on the same
+    workload as the GPU arm: every one of the batch's sequences each step,
+    f16 K/V drawn N(0,1). A step is a few tenths of a second."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import oracle as O
 
-    ctx = args.context
-    times = []
-    rng = np.random.default_rng(0)
+    ctx, batch = args.context, args.batch
     n = KV_HEADS * ctx * HD
-    k = rng.integers(0, 0x3C00, size=n, dtype=np.uint16)
-    v = rng.integers(0, 0x3C00, size=n, dtype=np.uint16)
-    q = rng.standard_normal(HEADS * HD).astype(np.float32)
+    ks = [host_normal_f16(n, 1000 + 17 * b) for b in range(batch)]
+    vs = [host_normal_f16(n, 5000 + 17 * b) for b in range(batch)]
+    q = np.random.default_rng(7).standard_normal((batch, HEADS * HD)).astype(np.float32)
+    q = q.astype(np.float16).astype(np.float32)
     used = 0
+    times = []
     for i in range(args.warmup + args.steps):
         t0 = time.perf_counter()
-        _, used = O.decode_fast(q, k, v, HEADS, KV_HEADS, HD, ctx, ctx, SCALE, False, 0)
+        for b in range(batch):
+            _, used = O.decode_fast(q[b], ks[b], vs[b], HEADS, KV_HEADS, HD, ctx, ctx, SCALE,
+                                    False, 0)
         if i >= args.warmup:
             times.append(time.perf_counter() - t0)
     per = float(np.mean(times))
-    bytes_one = 2 * KV_HEADS * ctx * HD * 2
-    gbs = bytes_one / per / 1e9
-    sample = ("1 of the %d sequences per step (%d keys x 8 KV heads, %.0f MB of KV); "
-              "GB/s is per byte of KV read, so it scales to the full batch" %
-              (args.batch, ctx, bytes_one / 1e6))
+    bytes_step = batch * 2 * KV_HEADS * ctx * HD * 2
+    gbs = bytes_step / per / 1e9
+    sample = ("the whole step: all %d sequences (%d keys x 8 KV heads each, %.0f MB of KV a "
+              "step), %d host threads" % (batch, ctx, bytes_step / 1e6, used))
     print(json.dumps({
         "impl": "reference",
         "metric": "decode KV GB/s", "value": gbs, "unit": "GB/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": per * 1e3 * args.batch,
+        "warmup": args.warmup, "ms_per_step": per * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16 KV cache, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "config 5 decode: batch %d, context %d per sequence, 32 Q / 8 KV "
-                               "heads, head_dim 128 (CPU: bounded sample)" % (args.batch, ctx),
-                   "global_batch": args.batch, "context": ctx},
+        "config": {"workload": WORKLOAD % (batch, ctx),
+                   "global_batch": batch, "context": ctx,
+                   "parallelism": "host threads x%d" % used},
+        "tokens_per_s": batch / per,
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": used, "kind": "port",
                          "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -627,7 +835,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=131072)
     ap.add_argument("--seq", type=int, default=8192)
-    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline legs")
+    ap.add_argument("--no-prefill", action="store_true",
+                    help="leave the prefill object out of the decode line")
     ap.add_argument("--exchange", default="push", choices=["push", "fused", "nccl"],
                     help="how the ranks exchange their triples: everything in the decode "
                          "kernel over peer memory (fused), the push in the kernel and the merge "
@@ -653,6 +863,11 @@ def main():
     fn = {"decode128k": decode128k, "prefill8k": prefill8k, "configs": other_configs}[
         args.workload]
     gpu, line = fn(args, world, rank, local)
+    if args.workload == "decode128k" and not args.no_prefill:
+        import torch
+
+        torch.cuda.empty_cache()
+        line["prefill"] = prefill_leg(args, gpu, world, rank, local)
     sys.stdout.flush()
     os.dup2(real_stdout, 1)
     os.close(real_stdout)
@@ -661,9 +876,10 @@ def main():
             gbs, used, secs = cpu_decode_sample(args.context, reps=40)
             line["cpu_baseline"] = {
                 "value": gbs, "unit": "GB/s", "cores": used, "kind": "port",
-                "sample": "1 of the %d sequences, best of 40 passes (%.2f s each); the C restatement of "
-                          "the reference's scalar decode, threaded over heads and key slabs"
-                          % (args.batch, secs)}
+                "sample": "1 of the %d sequences (f16 K/V ~N(0,1)), best of 40 passes (%.2f s "
+                          "each), %d host threads; the C restatement of the reference's scalar "
+                          "decode, threaded over heads and key slabs"
+                          % (args.batch, secs, used)}
         print(json.dumps(line))
     import torch.distributed as dist
 

@@ -18,7 +18,8 @@
  *     projections may alias one allocation (device.rs:2909-2913);
  *   - all work is asynchronous on the handle's own non-blocking stream and
  *     stream-ordered; nothing here synchronises the host except
- *     llmtie_synchronize, llmtie_download and llmtie_kprof_report;
+ *     llmtie_synchronize, llmtie_download and llmtie_kprof_report (and every
+ *     launch while kprof is on);
  *   - a call that is refused returns a non-zero status, launches nothing and
  *     leaves a message for llmtie_last_error() (thread-local).
  *
@@ -71,15 +72,25 @@ const char *llmtie_last_error(void);
 void *llmtie_stream(llmtie_gpu *g);
 int32_t llmtie_ordinal(llmtie_gpu *g);
 /* Gpu::synchronize (device.rs:1433-1440). Also surfaces LLMTIE_ERR_TIMEOUT if
- * a kernel's bounded wait gave up since the last call. */
+ * a kernel's bounded wait gave up since the last report (llmtie_download
+ * reports it as well). A timeout is reported once; reporting it clears the
+ * arrival counters of every decode scratch of the handle, so the next call
+ * starts clean. What the kernel that gave up should have written is
+ * undefined. */
 llmtie_status llmtie_synchronize(llmtie_gpu *g);
+/* How long a device-side wait (an mbarrier of the tensor-memory prefill, a
+ * flag another GPU raises) may spin before it gives up, in SM cycles. The
+ * default, also restored by cycles <= 0, is 2^31: about a second. No
+ * counterpart in the reference, whose kernels never wait on one another. */
+llmtie_status llmtie_set_wait_limit_cycles(llmtie_gpu *g, int64_t cycles);
 
 /* Gpu::uninit / zeros / zeros_f16 (device.rs:937-983): stream-ordered. */
 llmtie_status llmtie_alloc(llmtie_gpu *g, size_t bytes, void **dptr);
 llmtie_status llmtie_zeros(llmtie_gpu *g, size_t bytes, void **dptr);
 llmtie_status llmtie_free(llmtie_gpu *g, void *dptr);
 /* Gpu::upload / download (device.rs:898-935): host <-> device on the stream;
- * download waits for the stream. */
+ * download waits for the stream, and returns LLMTIE_ERR_TIMEOUT (the bytes
+ * are copied all the same) if a kernel's bounded wait gave up before it. */
 llmtie_status llmtie_upload(llmtie_gpu *g, void *dst, const void *src, size_t bytes);
 llmtie_status llmtie_download(llmtie_gpu *g, void *dst, const void *src, size_t bytes);
 /* Gpu::upload_f16 (device.rs:1422-1431): f32 on the device -> f16 bits, RNE. */

@@ -1,0 +1,138 @@
+"""What stands around the kernels: the bounded device waits and how a wait
+that runs out reaches the host, the per-kernel profile and the kernel
+resource query (crates/llmtie-cuda/src/device.rs:1458-1465, :1490-1565).
+
+Nothing here faults or hangs a device: the one wait that runs out is a wait
+for a flag that nothing raises, given a limit of about a millisecond, after
+which the kernel returns normally.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.helpers import assert_close_to, lay_caches
+
+pytestmark = pytest.mark.gpu
+
+
+def _exchange_of_one_device(gpu, world, rows, hd, step_value):
+    """An exchange descriptor whose every "rank" is a plain buffer of this one
+    device (no peer or symmetric memory): gather [2][world][rows][hd+2], flags
+    [world] and the step counter, all zero but the step."""
+    import torch
+
+    from ttsxabe_b200.gpu import Exchange
+
+    with torch.cuda.stream(gpu.stream):
+        gather = torch.zeros(2 * world * rows * (hd + 2), dtype=torch.float32, device=gpu.device)
+        flags = torch.zeros(64, dtype=torch.int32, device=gpu.device)
+        step = torch.full((1,), step_value, dtype=torch.int32, device=gpu.device)
+    xch = Exchange(world, 0, [gather.data_ptr()] * world, [flags.data_ptr()] * world,
+                   step.data_ptr())
+    return xch, gather, flags, step
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_handle_stays_usable(gpu):
+    """The merge of a sharded step waits for every rank's flag. Here rank 1's
+    flag is never raised and the limit is about a millisecond: the kernel
+    returns, the next synchronize raises DeviceTimeout - once -, a download
+    reports it just the same, and a decode on the same handle afterwards is
+    correct."""
+    import torch
+
+    from ttsxabe_b200 import DecodeScratch, DeviceTimeout
+
+    world, rows, hd = 2, 32, 128
+    xch, gather, flags, step = _exchange_of_one_device(gpu, world, rows, hd, step_value=1)
+    with torch.cuda.stream(gpu.stream):
+        flags[0] = 1            # rank 0 has delivered, rank 1 never does
+    gpu.synchronize()
+    gpu.set_wait_limit_cycles(2_000_000)
+    try:
+        gpu.lse_merge_wait(xch, rows, hd)
+        with pytest.raises(DeviceTimeout, match="site 61"):
+            gpu.synchronize()
+        gpu.synchronize()       # reported once
+        out = gpu.lse_merge_wait(xch, rows, hd)
+        with pytest.raises(DeviceTimeout):
+            gpu.download(out)   # what it copied is what the kernel never wrote
+        gpu.synchronize()
+    finally:
+        gpu.set_wait_limit_cycles(0)
+
+    # both flags up: the same call merges (two equal triples merge to their value)
+    rng = np.random.default_rng(5)
+    tri = rng.standard_normal((rows, hd + 2)).astype(np.float32)
+    tri[:, hd] = 0.25                      # m
+    tri[:, hd + 1] = np.abs(tri[:, hd + 1]) + 1.0   # l
+    both = np.concatenate([tri.reshape(-1), tri.reshape(-1)])
+    with torch.cuda.stream(gpu.stream):
+        gather[:both.size] = torch.from_numpy(both).to(gpu.device)
+        flags[:2] = 1
+    got = gpu.download(gpu.lse_merge_wait(xch, rows, hd)).reshape(rows, hd)
+    want = tri[:, :hd] / tri[:, hd + 1:hd + 2]
+    assert np.abs(got - want).max() <= 1e-6 * np.abs(want).max()
+
+    # and the handle decodes as before
+    heads, kv, tk, cap = 8, 2, 3000, 3072
+    q = O.seq(heads * hd, 900)
+    k0, v0 = O.seq(kv * cap * hd, 901), O.seq(kv * hd * cap, 902)
+    scratch = DecodeScratch()
+    dec = gpu.download(gpu.attn_decode_f16(gpu.upload(q), gpu.upload_f16(k0), gpu.upload_f16(v0),
+                                           heads, kv, hd, tk, cap, 0.11, False, scratch))
+    want = O.decode_f64(q, O.round_f16(k0), O.round_f16(v0), heads, kv, hd, 0, tk, cap, 0.11, False)
+    assert_close_to("decode after a reported timeout", want, dec, 2e-5)
+
+
+def test_kprof_charges_each_launch_to_its_kernel(gpu):
+    """With the profile on, a known sequence of calls shows up under the
+    kernels' names with their counts, the most expensive first; the
+    tensor-memory prefill and the general one are told apart."""
+    heads, kv, hd, tq = 8, 2, 128, 256
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = O.seq(tq * heads * hd, 1)
+    dq = gpu.upload(q)
+    # capacity 256: aligned rows, the tensor-memory kernel; 138: the general one
+    kc, vc = lay_caches(O.seq(kv * tq * hd, 2), O.seq(kv * tq * hd, 3), kv, tq, hd, 256)
+    dk, dv = gpu.upload_f16(kc), gpu.upload_f16(vc)
+    n2 = 130
+    kc2, vc2 = lay_caches(O.seq(kv * n2 * hd, 4), O.seq(kv * n2 * hd, 5), kv, n2, hd, 138)
+    dk2, dv2 = gpu.upload_f16(kc2), gpu.upload_f16(vc2)
+    gpu.synchronize()
+    gpu.kprof_reset()
+    gpu.kprof_enable(True)
+    try:
+        gpu.rope(dq, 0, tq, heads, hd, 10000.0, 0)
+        gpu.rope(dq, 0, tq, heads, hd, 10000.0, 0)
+        gpu.flash_attn_f16(dq, dk, dv, tq, 0, heads, kv, hd, 256, scale, True)
+        gpu.flash_attn_f16(dq, dk2, dv2, n2, 0, heads, kv, hd, 138, scale, True)
+        rep = gpu.kprof_report()
+    finally:
+        gpu.kprof_enable(False)
+    assert rep["rope"][0] == 2
+    assert rep["flash_attn_h_tc"][0] == 1
+    assert rep["flash_attn_h"][0] == 1
+    assert all(ms > 0.0 for _, ms in rep.values())
+    assert list(rep.values()) == sorted(rep.values(), key=lambda e: -e[1])
+    gpu.kprof_reset()
+    assert gpu.kprof_report() == {}
+    # off again: nothing is charged
+    gpu.rope(dq, 0, tq, heads, hd, 10000.0, 0)
+    assert gpu.kprof_report() == {}
+
+
+def test_kernel_resources_are_what_the_compiler_gave(gpu):
+    """(registers a thread, local bytes a thread, static shared bytes a block)
+    per kernel name; None for a name that is not in the library."""
+    seen = {}
+    for name in ("flash_attn_h_tc", "flash_attn_64_tc", "attn_decode_h128_run",
+                 "attn_decode_h64_run", "attn_decode_h128", "attn_decode_f64", "lse_merge",
+                 "lse_merge_wait"):
+        res = gpu.kernel_resources(name)
+        assert res is not None, name
+        regs, local, smem = res
+        assert 0 < regs <= 255 and local >= 0 and smem >= 0, (name, res)
+        seen[name] = res
+    # the key loop of the ring kernel must not spill
+    assert seen["attn_decode_h128_run"][1] == 0
+    assert gpu.kernel_resources("no_such_kernel") is None

@@ -1,0 +1,165 @@
+"""Parity at depth: the tensor-memory prefill over tens of key tiles and the
+long-context decode at the benchmark's full size, against the CPU oracle.
+
+The oracle is scalar, so a whole 8192-position prefill (0.55 TFLOP) is out of
+its reach; what it checks instead are windows of 16 query rows spread over the
+sequence - the first rows, the rows either side of a 128-row tile boundary, a
+row in the middle, the last rows - each against every key it may see and on
+every head. The shape and the peaked-softmax trick (q x 100) are those of the
+reference's `fused_attention_sized` and its (32, 8, 128, 8192) decode case
+(crates/llmtie-cuda/tests/kernels.rs:2249-2374, :2782-2908).
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.helpers import assert_close_to, assert_parity, normal_f16
+
+pytestmark = pytest.mark.gpu
+
+HEADS, KV, HD = 32, 8, 128
+SCALE = float(np.float32(HD) ** np.float32(-0.5))
+
+
+def windows(tq):
+    """First rows of the 16-row windows the oracle checks."""
+    if tq <= 2048:
+        return [0, 112, 128, 1000, tq - 128, tq - 16]
+    return [0, 112, 128, 1000, 4095, tq - 128, tq - 16]
+
+
+def check_windows(gpu, name, q, kc, vc, tq, heads, kv, check):
+    """Runs flash_attn_f16 over the whole sequence and hands each window's
+    rows, with the oracle's answer for them, to `check`."""
+    dq = gpu.upload(q)
+    out = gpu.flash_attn_f16(dq, gpu.upload_u16(kc), gpu.upload_u16(vc), tq, 0, heads, kv, HD, tq,
+                             SCALE, True)
+    got = gpu.download(out).reshape(tq, heads * HD)
+    assert np.isfinite(got).all(), f"{name}: non-finite output"
+    q2 = q.reshape(tq, heads * HD)
+    for r0 in windows(tq):
+        want = O.prefill(np.ascontiguousarray(q2[r0:r0 + 16]), kc, vc, 16, r0, heads, kv, HD, tq,
+                         SCALE, True)
+        check(f"{name} rows {r0}..{r0 + 16}", r0, want, got[r0:r0 + 16].reshape(-1))
+
+
+@pytest.mark.parametrize("tq", [2048, 8192])
+def test_long_causal_prefill_normal_inputs(gpu, tq):
+    """N(0,1) inputs at 32 / 8 x 128, causal, 16 and 64 key tiles: the K/V
+    stage parities wrap many times and the accumulator in tensor memory takes
+    every tile. BASELINE's bar on every window."""
+    rng = np.random.default_rng(tq)
+    q = normal_f16(rng, tq * HEADS * HD)
+    kc = O.round_f16(rng.standard_normal(KV * tq * HD).astype(np.float32))
+    vc = O.round_f16(rng.standard_normal(KV * HD * tq).astype(np.float32))
+    check_windows(gpu, f"prefill {tq}", q, kc, vc, tq, HEADS, KV,
+                  lambda name, r0, want, got: assert_parity(name, want, got))
+
+
+def windowed_spread(q_rows, kc, vc, r0, heads, kv, tq):
+    """The spread term of the reference's prefill tolerance
+    (crates/llmtie-cuda/tests/kernels.rs:2337-2352) for 16 rows starting at r0:
+    sum_p (e_p / l) |v_p - want| over the keys a row sees. Keys whose
+    probability is below 1e-12 are left out, which can only tighten it."""
+    group = heads // kv
+    h16 = lambda x: np.asarray(x, np.float32).astype(np.float16).astype(np.float64)
+    K = O.widen_f16(kc).astype(np.float64).reshape(kv, tq, HD)
+    V = O.widen_f16(vc).astype(np.float64).reshape(kv, HD, tq)
+    qw = h16(q_rows).reshape(16, heads, HD)
+    want = np.zeros((16, heads, HD))
+    spread = np.zeros((16, heads, HD))
+    for h in range(heads):
+        kh = h // group
+        for r in range(16):
+            last = r0 + r
+            s = (K[kh, :last + 1] @ qw[r, h]) * np.float64(np.float32(SCALE))
+            e = np.exp(s - s.max())
+            l = e.sum()
+            keep = np.nonzero(e / l > 1e-12)[0]
+            vk = V[kh][:, keep]                                   # [hd][kept]
+            w = (vk @ h16(e[keep].astype(np.float32))) / l
+            want[r, h] = w
+            spread[r, h] = (np.abs(vk - w[:, None]) @ (e[keep] / l))
+    return want.reshape(-1), spread.reshape(-1)
+
+
+def test_long_causal_prefill_peaked(gpu):
+    """The reference's peaked softmax (q x 100: a permuted key shows at once)
+    at 8192 positions, 8 / 2 heads, under its own tolerance
+    2e-4 + 1e-2 |want| + 1e-2 spread with the worst error below half of it."""
+    heads, kv, tq = 8, 2, 8192
+    q = O.seq(tq * heads * HD, 71) * np.float32(100.0)
+    kc = O.round_f16(O.seq(kv * tq * HD, 72))
+    vc = O.round_f16(O.seq(kv * HD * tq, 73))
+    q2 = q.reshape(tq, heads * HD)
+    worst = [0.0]
+
+    def check(name, r0, want_c, got):
+        want, spread = windowed_spread(q2[r0:r0 + 16], kc, vc, r0, heads, kv, tq)
+        # the numpy restatement and the C oracle agree on these rows
+        assert np.abs(want - want_c).max() < 1e-5, name
+        tol = 2e-4 + 1e-2 * np.abs(want) + 1e-2 * spread
+        ratio = np.abs(want - got.astype(np.float64)) / tol
+        assert ratio.max() < 0.5, f"{name}: worst error is {ratio.max():.3f} of its tolerance"
+        worst[0] = max(worst[0], float(ratio.max()))
+
+    check_windows(gpu, "peaked prefill 8192", q, kc, vc, tq, heads, kv, check)
+
+
+def test_long_causal_prefill_rising_maximum(gpu):
+    """Scores that climb with the key position, about 12 in log2 units per
+    128-key tile: the running maximum moves on nearly every tile, so the
+    accumulator in tensor memory is rescaled tile after tile (with N(0,1)
+    inputs it almost never is). Keys carry a component along a fixed
+    direction that grows with the position; every query has a positive
+    component along it."""
+    tq = 8192
+    rng = np.random.default_rng(99)
+    u = np.ones(HD, np.float32) / np.sqrt(np.float32(HD))
+    q = rng.standard_normal((tq, HEADS, HD)).astype(np.float32) + np.float32(8.0) * u
+    ramp = (np.arange(tq, dtype=np.float32) / np.float32(128.0) * np.float32(12.0))
+    k = rng.standard_normal((KV, tq, HD)).astype(np.float32) + ramp[None, :, None] * u
+    q = O.through_f16(q.reshape(-1))
+    kc = O.round_f16(k.reshape(-1))
+    vc = O.round_f16(rng.standard_normal(KV * HD * tq).astype(np.float32))
+    check_windows(gpu, "rising-maximum prefill 8192", q, kc, vc, tq, HEADS, KV,
+                  lambda name, r0, want, got: assert_parity(name, want, got))
+
+
+def test_decode_batch8_context_131072(gpu):
+    """The benchmark's long-context decode at its full size: batch 8, 131072
+    keys a sequence, 32 / 8 x 128 (4.3 GB of cache, generated on the device
+    as the benchmark does). Two of the eight sequences are brought back and
+    checked against the f64 oracle at the reference's decode bar (2e-5 of
+    full scale) and at BASELINE's."""
+    import torch
+
+    from ttsxabe_b200 import DecodeScratch
+
+    batch, ctx = 8, 131072
+    n = KV * ctx * HD
+    with torch.cuda.stream(gpu.stream):
+        gen = torch.Generator(device=gpu.device)
+        gen.manual_seed(131072)
+        ks = [torch.randn(n, generator=gen, device=gpu.device).to(torch.float16)
+              for _ in range(batch)]
+        vs = [torch.randn(n, generator=gen, device=gpu.device).to(torch.float16)
+              for _ in range(batch)]
+        q = torch.randn(batch * HEADS * HD, generator=gen, device=gpu.device)
+        q = q.to(torch.float16).to(torch.float32)
+    scratch = DecodeScratch()
+    out = gpu.decode_batched(q, ks, vs, [ctx] * batch, [ctx] * batch, HEADS, KV, HD, SCALE, False,
+                             scratch)
+    again = gpu.decode_batched(q, ks, vs, [ctx] * batch, [ctx] * batch, HEADS, KV, HD, SCALE,
+                               False, scratch)
+    got = gpu.download(out).reshape(batch, HEADS * HD)
+    assert np.array_equal(got, gpu.download(again).reshape(batch, HEADS * HD))
+    assert np.isfinite(got).all()
+    hq = gpu.download(q).reshape(batch, HEADS * HD)
+    for b in (0, 5):
+        want = O.decode_f64(hq[b], gpu.download_u16(ks[b]), gpu.download_u16(vs[b]), HEADS, KV, HD,
+                            0, ctx, ctx, SCALE, False)
+        assert_close_to(f"decode 8 x 131072, sequence {b}", want, got[b], 2e-5)
+        assert_parity(f"decode 8 x 131072, sequence {b}", want, got[b])
+    del ks, vs
+    torch.cuda.empty_cache()

@@ -27,6 +27,7 @@ PROTOTYPES = {
     "llmtie_stream": (vp, [vp]),
     "llmtie_ordinal": (i32, [vp]),
     "llmtie_synchronize": (i32, [vp]),
+    "llmtie_set_wait_limit_cycles": (i32, [vp, C.c_int64]),
     "llmtie_alloc": (i32, [vp, sz, pvp]),
     "llmtie_zeros": (i32, [vp, sz, pvp]),
     "llmtie_free": (i32, [vp, vp]),

@@ -143,8 +143,13 @@ static llmtie_status open_impl(int32_t ordinal, void *stream, bool adopt, llmtie
         uint64_t keep = UINT64_MAX;
         cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
     }
-    e = cudaMalloc(&g->timeout_flag, sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(g->timeout_flag, 0, sizeof(int));
+    e = cudaHostAlloc((void **)&g->timeout_host, sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        *g->timeout_host = 0;
+        e = cudaHostGetDevicePointer((void **)&g->timeout_site, g->timeout_host, 0);
+    }
+    if (e == cudaSuccess) e = cudaMalloc(&g->abort_epoch, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(g->abort_epoch, 0, sizeof(int));
     if (e != cudaSuccess) {
         llmtie_close(g);
         return driver_fail("allocating the status word", e);
@@ -168,7 +173,8 @@ extern "C" void llmtie_close(llmtie_gpu *g)
     if (!g) return;
     cudaSetDevice(g->ordinal);
     if (g->stream) cudaStreamSynchronize(g->stream);
-    if (g->timeout_flag) cudaFree(g->timeout_flag);
+    if (g->abort_epoch) cudaFree(g->abort_epoch);
+    if (g->timeout_host) cudaFreeHost(g->timeout_host);
     if (g->ev0) cudaEventDestroy(g->ev0);
     if (g->ev1) cudaEventDestroy(g->ev1);
     if (g->owns_stream && g->stream) cudaStreamDestroy(g->stream);
@@ -178,18 +184,44 @@ extern "C" void llmtie_close(llmtie_gpu *g)
 extern "C" void *llmtie_stream(llmtie_gpu *g) { return g ? (void *)g->stream : nullptr; }
 extern "C" int32_t llmtie_ordinal(llmtie_gpu *g) { return g ? g->ordinal : -1; }
 
+// After the stream has been waited for: whether a bounded device wait gave up
+// since the last report. The word is host memory the kernels write through a
+// mapping, so looking at it costs nothing. A timeout is reported once; the
+// words are cleared, and so are the arrival counters of every DecodeScratch
+// of this handle, which a launch that gave up may have left mid-count.
+static llmtie_status report_device_timeout(llmtie_gpu *g)
+{
+    const int site = *(volatile int *)g->timeout_host;
+    if (site == 0) return LLMTIE_OK;
+    *(volatile int *)g->timeout_host = 0;
+    cudaMemsetAsync(g->abort_epoch, 0, sizeof(int), g->stream);
+    for (llmtie_decode_scratch *s : g->scratches) {
+        if (s->ctr) cudaMemsetAsync(s->ctr, 0, s->ctr_words * sizeof(unsigned), g->stream);
+    }
+    return llmtie_fail(LLMTIE_ERR_TIMEOUT, "a bounded device wait gave up (site %d)", site);
+}
+
 extern "C" llmtie_status llmtie_synchronize(llmtie_gpu *g)
 {
     NEED_HANDLE(g);
     const cudaError_t e = cudaStreamSynchronize(g->stream);
     if (e != cudaSuccess) return driver_fail("synchronizing", e);
-    int flag = 0;
-    cudaMemcpy(&flag, g->timeout_flag, sizeof(int), cudaMemcpyDeviceToHost);
-    if (flag != 0) {
-        cudaMemset(g->timeout_flag, 0, sizeof(int));
-        return llmtie_fail(LLMTIE_ERR_TIMEOUT, "a bounded device wait gave up (site %d)", flag);
-    }
+    return report_device_timeout(g);
+}
+
+extern "C" llmtie_status llmtie_set_wait_limit_cycles(llmtie_gpu *g, int64_t cycles)
+{
+    NEED_HANDLE(g);
+    g->wait_cycles = cycles > 0 ? (long long)cycles : (1ll << 31);
     return LLMTIE_OK;
+}
+
+// What a tensor-memory prefill launch is given for its bounded waits; every
+// launch gets a number of its own.
+static WaitCtl next_wait_ctl(llmtie_gpu *g)
+{
+    g->epoch = g->epoch == 0x7fffffff ? 1 : g->epoch + 1;
+    return WaitCtl{g->timeout_site, g->abort_epoch, g->epoch, g->wait_cycles};
 }
 
 extern "C" llmtie_status llmtie_alloc(llmtie_gpu *g, size_t bytes, void **dptr)
@@ -234,7 +266,8 @@ extern "C" llmtie_status llmtie_download(llmtie_gpu *g, void *dst, const void *s
     cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(g->stream);
     if (e != cudaSuccess) return driver_fail("downloading", e);
-    return LLMTIE_OK;
+    // What was just copied may be what a kernel that gave up never wrote.
+    return report_device_timeout(g);
 }
 
 extern "C" llmtie_status llmtie_round_f16(llmtie_gpu *g, const float *src, uint16_t *dst,
@@ -441,10 +474,21 @@ extern "C" llmtie_status llmtie_rope_cache_f16(llmtie_gpu *g, float *q, size_t q
     if (!fits_i32(cap) || !fits_i32(heads * head_dim)) {
         return llmtie_fail(LLMTIE_ERR_INVALID, "cache geometry does not fit 32 bits");
     }
+    // a batch of one through the batched kernel
+    RopeBatchParams p;
+    memset(&p, 0, sizeof(p));
+    p.nseq = 1;
+    p.seq[0] = {kc, vc, (int)pos, (int)cap, (long long)q_off, (long long)k_off, (long long)v_off};
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.freq_div = freq_div;
+    p.heads = (int)heads;
+    p.kv_heads = (int)kv_heads;
+    p.hd = (int)head_dim;
+    p.theta = theta;
     LaunchScope ls(g, "rope_cache_f16");
-    launch_rope_cache_f16(g->stream, q, (long long)q_off, k, (long long)k_off, v,
-                          (long long)v_off, freq_div, (int)heads, (int)kv_heads, (int)head_dim,
-                          theta, (int)pos, kc, vc, (int)cap);
+    launch_rope_cache_batched(g->stream, p);
     return ls.done();
 }
 
@@ -485,7 +529,9 @@ extern "C" llmtie_status llmtie_rope_cache_batched(
         memset(&p, 0, sizeof(p));
         p.nseq = (int)nb;
         for (size_t b = 0; b < nb; b++) {
-            p.seq[b] = {kc_ptrs[b0 + b], vc_ptrs[b0 + b], pos[b0 + b], cap[b0 + b]};
+            p.seq[b] = {kc_ptrs[b0 + b], vc_ptrs[b0 + b], pos[b0 + b], cap[b0 + b],
+                        (long long)(b * heads * head_dim), (long long)(b * kv_heads * head_dim),
+                        (long long)(b * kv_heads * head_dim)};
         }
         p.q = q + b0 * heads * head_dim;
         p.k = k + b0 * kv_heads * head_dim;
@@ -586,9 +632,12 @@ static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q,
     p.out_f16 = 0;
     p.q_scale = 1.0f;
     p.sl2 = scale * kLog2e;
-    LaunchScope ls(g, name);
-    const cudaError_t e = use_tc(p, (int)hd) ? launch_prefill_tc(g->stream, p, (int)hd, g->timeout_flag)
-                                             : launch_prefill_mma(g->stream, p, (int)hd);
+    // kprof tells the two kernels apart: the tensor-memory one (f16 caches
+    // only, so `name` is "flash_attn_h" then) is charged to "flash_attn_h_tc"
+    const bool tc = use_tc(p, (int)hd);
+    LaunchScope ls(g, tc ? "flash_attn_h_tc" : name);
+    const cudaError_t e = tc ? launch_prefill_tc(g->stream, p, (int)hd, next_wait_ctl(g))
+                             : launch_prefill_mma(g->stream, p, (int)hd);
     if (e != cudaSuccess) return driver_fail(name, e);
     return ls.done();
 }
@@ -700,9 +749,10 @@ static llmtie_status flash_rows_impl(llmtie_gpu *g, const float *qkv, size_t qkv
         p.out_f16 = 1;
         p.q_scale = scale;   // on q before it is rounded, as the encoder does
         p.sl2 = kLog2e;
-        LaunchScope ls(g, "flash_attn_64_rows");
-        const cudaError_t e = use_tc(p, 64) ? launch_prefill_tc(g->stream, p, 64, g->timeout_flag)
-                                            : launch_prefill_mma(g->stream, p, 64);
+        const bool tc = use_tc(p, 64);
+        LaunchScope ls(g, tc ? "flash_attn_64_rows_tc" : "flash_attn_64_rows");
+        const cudaError_t e = tc ? launch_prefill_tc(g->stream, p, 64, next_wait_ctl(g))
+                                 : launch_prefill_mma(g->stream, p, 64);
         st = (e != cudaSuccess) ? driver_fail("flash_attn_64_rows", e) : ls.done();
     }
     if (own) llmtie_free(g, own);
@@ -734,6 +784,7 @@ extern "C" llmtie_status llmtie_decode_scratch_new(llmtie_gpu *g, llmtie_decode_
     if (!out) return llmtie_fail(LLMTIE_ERR_INVALID, "null output pointer");
     *out = new (std::nothrow) llmtie_decode_scratch();
     if (!*out) return llmtie_fail(LLMTIE_ERR_DRIVER, "allocating the scratch");
+    g->scratches.push_back(*out);
     return LLMTIE_OK;
 }
 
@@ -743,6 +794,8 @@ extern "C" void llmtie_decode_scratch_free(llmtie_gpu *g, llmtie_decode_scratch 
     if (g) {
         if (s->part) cudaFreeAsync(s->part, g->stream);
         if (s->ctr) cudaFreeAsync(s->ctr, g->stream);
+        g->scratches.erase(std::remove(g->scratches.begin(), g->scratches.end(), s),
+                           g->scratches.end());
     }
     delete s;
 }
@@ -895,7 +948,8 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
                 sp.xch_fused = 1;
                 for (int r = 0; r < xch->world; r++) sp.xch_pflags[r] = fused->pair_flags[r];
                 sp.xch_out = fused->out;
-                sp.xch_status = g->timeout_flag;
+                sp.xch_status = g->timeout_site;
+                sp.xch_wait_cycles = g->wait_cycles;
             }
         }
         LaunchScope ls(g, name);
@@ -1224,7 +1278,8 @@ extern "C" llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_excha
     if (rows == 0) return LLMTIE_OK;
     LaunchScope ls(g, "lse_merge_wait");
     launch_lse_merge_wait(g->stream, xch->gather[xch->rank], xch->flags[xch->rank], xch->step,
-                          xch->world, (int)rows, (int)head_dim, out, g->timeout_flag);
+                          xch->world, (int)rows, (int)head_dim, out, g->timeout_site,
+                          g->wait_cycles);
     return ls.done();
 }
 
@@ -1398,11 +1453,11 @@ extern "C" llmtie_status llmtie_prefill_varlen(
             PrefillParams part = pp;
             part.nseq = std::min(LLMTIE_TC_MAX_SEQ, pp.nseq - s0);
             for (int b = 0; b < part.nseq; b++) part.seq[b] = pp.seq[s0 + b];
-            LaunchScope ls(g, "flash_attn_h");
+            const bool tc = use_tc(part, (int)head_dim);
+            LaunchScope ls(g, tc ? "flash_attn_h_tc" : "flash_attn_h");
             const cudaError_t e =
-                use_tc(part, (int)head_dim)
-                    ? launch_prefill_tc(g->stream, part, (int)head_dim, g->timeout_flag)
-                    : launch_prefill_mma(g->stream, part, (int)head_dim);
+                tc ? launch_prefill_tc(g->stream, part, (int)head_dim, next_wait_ctl(g))
+                   : launch_prefill_mma(g->stream, part, (int)head_dim);
             if (e != cudaSuccess) return driver_fail("flash_attn_h", e);
             const llmtie_status s = ls.done();
             if (s != LLMTIE_OK) return s;
@@ -1426,8 +1481,12 @@ extern "C" void llmtie_kprof_reset(llmtie_gpu *g)
 extern "C" size_t llmtie_kprof_report(llmtie_gpu *g, char *buf, size_t cap)
 {
     if (!g) return 0;
+    // most expensive first, as the reference's report is (device.rs:1556-1563)
+    std::vector<std::pair<std::string, KprofEntry>> rows(g->prof.begin(), g->prof.end());
+    std::stable_sort(rows.begin(), rows.end(),
+                     [](const auto &x, const auto &y) { return x.second.ms > y.second.ms; });
     std::string s;
-    for (const auto &kv : g->prof) {
+    for (const auto &kv : rows) {
         char line[256];
         snprintf(line, sizeof(line), "%s %llu %.6f\n", kv.first.c_str(),
                  (unsigned long long)kv.second.count, kv.second.ms);

@@ -28,8 +28,23 @@ struct llmtie_gpu {
     bool kprof = false;
     std::map<std::string, KprofEntry> prof;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    // One word the kernels' bounded waits set when they give up.
-    int *timeout_flag = nullptr;
+    // Where a bounded device wait that gave up leaves its site code: one word
+    // of pinned host memory mapped into the device, so that the host reads it
+    // after any stream synchronisation without a copy. `timeout_site` is the
+    // device's view of the same word.
+    int *timeout_host = nullptr;
+    int *timeout_site = nullptr;
+    // A device word holding the number (`epoch`) of the tensor-memory prefill
+    // launch that gave up, zero at rest: blocks of that same launch that start
+    // later leave at once; other launches are not affected.
+    int *abort_epoch = nullptr;
+    int epoch = 0;
+    // How long a device-side wait may spin, in SM cycles (about a second).
+    long long wait_cycles = 1ll << 31;
+    // Every DecodeScratch made through this handle: their arrival counters
+    // are cleared when a timeout is reported, since a launch that gave up may
+    // have left them mid-count.
+    std::vector<llmtie_decode_scratch *> scratches;
 };
 
 struct llmtie_decode_scratch {
@@ -57,21 +72,18 @@ struct LaunchScope {
 // rope_cache.cu
 void launch_rope(cudaStream_t st, float *x, long long off, const float *freq_div, int t,
                  int heads, int hd, float theta, int first);
-void launch_rope_cache_f16(cudaStream_t st, float *q, long long q_off, const float *k,
-                           long long k_off, const float *v, long long v_off,
-                           const float *freq_div, int heads, int kv_heads, int hd,
-                           float theta, int pos, uint16_t *kc, uint16_t *vc, int cap);
 struct RopeBatchSeq {
     uint16_t *kc;
     uint16_t *vc;
     int pos, cap;
+    long long q_off, k_off, v_off;   // where this sequence's rows start in q, k and v
 };
 struct RopeBatchParams {
     RopeBatchSeq seq[32];
     int nseq;
-    float *q;              // [nseq][heads*hd], rotated in place
-    const float *k;        // [nseq][kv_heads*hd]
-    const float *v;
+    float *q;              // heads*hd floats at seq[b].q_off, rotated in place
+    const float *k;        // kv_heads*hd floats at seq[b].k_off
+    const float *v;        //   (q, k and v may be one allocation)
     const float *freq_div;
     int heads, kv_heads, hd;
     float theta;
@@ -123,6 +135,21 @@ struct DecodeParams {
     float *twin_s;         //   its scales, one per 32 outputs
 };
 #ifdef __CUDACC__
+// Records that a bounded wait gave up at `site` (host-mapped word: a plain
+// store and a system-wide fence; whichever site wins a race is as good).
+__device__ __forceinline__ void report_timeout(int *site_word, int site)
+{
+    *(volatile int *)site_word = site;
+    __threadfence_system();
+}
+// Acquire load at system scope: the consumer's half of a flag another GPU
+// raised after its own system-wide fence.
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 // The int8 "twin" of one context element, quantize_q8's arithmetic on the row
 // the block just produced (crates/llmtie-cuda/src/kernels.rs:5755-5773): the
 // 32 lanes of the calling warp hold 32 consecutive elements of one scale group
@@ -178,6 +205,7 @@ struct DecodeStreamParams {
     unsigned *xch_pflags[LLMTIE_MAX_RANKS];  // every rank's pair flags [pairs][world]
     float *xch_out;                          // [rows][hd], this rank's merged result
     int *xch_status;                         // set when a bounded wait gave up
+    long long xch_wait_cycles;               // how long such a wait may spin
     signed char *twin_q;                     // int8 twin of the output (or null), as in DecodeParams
     float *twin_s;
 };
@@ -191,7 +219,7 @@ void launch_lse_merge(cudaStream_t st, const float *parts_buf, int parts, int ro
 // merges the gather buffer the step filled.
 void launch_lse_merge_wait(cudaStream_t st, const float *gather, const unsigned *flags,
                            const unsigned *step, int world, int rows, int hd, float *out,
-                           int *status);
+                           int *status, long long wait_cycles);
 
 // prefill_mma.cu
 #define LLMTIE_PREFILL_MAX_SEQ 32
@@ -241,6 +269,9 @@ struct PrefillTcParams {
     int pair_rows;            // pair two row blocks of one head instead of two heads of a group
     float q_scale, sl2;
     int *status;              // set to a site code when a bounded wait gives up
+    int *abort_epoch;         // set to `epoch` then: later blocks of this launch leave at once
+    int epoch;
+    long long wait_cycles;    // how long a wait on a barrier may spin
     // Ragged batches: the (sequence, row block) of grid row blockIdx.y, longest
     // first over the whole batch and without the empty ones; n_order == 0 means
     // blockIdx.z is the sequence and blockIdx.y the row block.
@@ -248,7 +279,14 @@ struct PrefillTcParams {
     uint16_t order[LLMTIE_TC_MAX_ORDER];   // sequence << 8 | row-block slot
 };
 bool prefill_tc_eligible(const PrefillParams &p, int hd);
-cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, int *status);
+// What a launch needs of the handle for its bounded waits.
+struct WaitCtl {
+    int *status;
+    int *abort_epoch;
+    int epoch;
+    long long cycles;
+};
+cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, const WaitCtl &w);
 
 // rope_cache.cu: packed ragged sequences, RoPE on q (in place) and k (into
 // the f16 K caches), v transposed into the f16 V caches.

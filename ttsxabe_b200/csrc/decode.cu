@@ -510,7 +510,8 @@ int resident(int nb)
 // system-wide. Layout: gather [2][world][rows][hd + 2], flags [world].
 __global__ void lse_merge_wait_kernel(const float *__restrict__ gather,
                                       const unsigned *flags, const unsigned *step, int world,
-                                      int rows, int hd, float *__restrict__ out, int *status)
+                                      int rows, int hd, float *__restrict__ out, int *status,
+                                      long long wait_cycles)
 {
     __shared__ unsigned s_expected;
     __shared__ int s_ok;
@@ -518,11 +519,13 @@ __global__ void lse_merge_wait_kernel(const float *__restrict__ gather,
         const unsigned expected = *(volatile const unsigned *)step;
         const long long t0 = clock64();
         int ok = 1;
+        // The flags are raised by other GPUs after a system-wide fence: the
+        // consumer's half of that is an acquire at system scope.
         for (int r = 0; r < world && ok; r++) {
-            while ((int)(*(volatile const unsigned *)(flags + r) - expected) < 0) {
-                if (clock64() - t0 > (1ll << 31)) {   // about a second
+            while ((int)(ld_acquire_sys(flags + r) - expected) < 0) {
+                if (clock64() - t0 > wait_cycles) {
                     ok = 0;
-                    atomicExch(status, 60 + r);
+                    report_timeout(status, 60 + r);
                     break;
                 }
             }
@@ -532,7 +535,6 @@ __global__ void lse_merge_wait_kernel(const float *__restrict__ gather,
     }
     __syncthreads();
     if (!s_ok) return;
-    __threadfence();
     const int row = blockIdx.x;
     const int stride = hd + 2;
     const float *buf = gather + (size_t)((s_expected - 1u) & 1u) * world * rows * stride;
@@ -559,9 +561,10 @@ const KernelReg reg_merge_wait("lse_merge_wait", (const void *)lse_merge_wait_ke
 
 void launch_lse_merge_wait(cudaStream_t st, const float *gather, const unsigned *flags,
                            const unsigned *step, int world, int rows, int hd, float *out,
-                           int *status)
+                           int *status, long long wait_cycles)
 {
-    lse_merge_wait_kernel<<<rows, hd, 0, st>>>(gather, flags, step, world, rows, hd, out, status);
+    lse_merge_wait_kernel<<<rows, hd, 0, st>>>(gather, flags, step, world, rows, hd, out, status,
+                                               wait_cycles);
 }
 
 cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd)

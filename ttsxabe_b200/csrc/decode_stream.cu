@@ -258,43 +258,37 @@ __device__ __noinline__ void merge_pair(const DecodeStreamParams &p, unsigned ch
     }
 }
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p)
-{
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
 // The cross-rank half of a fused step: waits until every rank has delivered
 // its triple of `pair` for this step into this rank's gather buffer (each
 // rank raises the pair's flag after a system-wide fence), then merges the
 // `world` triples of each of the pair's rows into xch_out, normalised. The
 // wait is bounded (about a second); when it runs out the status word is set
-// and the pair is left unmerged, so the launch still ends.
+// and the pair is left unmerged, so the launch still ends. `s_dead` is the
+// block's own flag (shared memory, zero at the start of the block): once one
+// wait of the block has run out, its later pairs are not waited for again.
 template <int HD>
 __device__ __noinline__ void cross_merge(const DecodeStreamParams &p, int pair, int row0,
-                                         int rows_here, unsigned xch_step)
+                                         int rows_here, unsigned xch_step, int *s_dead)
 {
     constexpr int RSTEP = kThreads / HD;
-    __shared__ int s_ok;
     const int tid = threadIdx.x;
     const int world = p.xch_world;
     const unsigned want = xch_step + 1u;
-    if (tid == 0) s_ok = 1;
     __syncthreads();
+    if (*(volatile int *)s_dead) return;
     if (tid < world) {
         const unsigned *f = p.xch_pflags[p.xch_rank] + (size_t)pair * world + tid;
         const long long t0 = clock64();
         while ((int)(ld_acquire_sys(f) - want) < 0) {
-            if (clock64() - t0 > (1ll << 31)) {
-                s_ok = 0;
-                atomicExch(p.xch_status, 70 + tid);
+            if (clock64() - t0 > p.xch_wait_cycles) {
+                *(volatile int *)s_dead = 1;
+                report_timeout(p.xch_status, 70 + tid);
                 break;
             }
         }
     }
     __syncthreads();
-    if (!s_ok) return;
+    if (*(volatile int *)s_dead) return;
     const float *buf =
         p.xch_gather[p.xch_rank] + (size_t)(xch_step & 1u) * world * p.xch_rank_stride;
     const int d = tid % HD;
@@ -342,6 +336,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     __shared__ float sm_m[kWarps][kRows];
     __shared__ float sm_l[kWarps][kRows];
     __shared__ int sm_last;
+    __shared__ int sm_dead;                // a cross-rank wait of this block ran out
     constexpr int kMineMax = 16;
     __shared__ int sm_mine[kMineMax][3];   // pairs this block finished: pair, first row, rows
     int nmine = 0;                         // (the same in every thread)
@@ -361,6 +356,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     // have finished the launch and advanced it.
     const unsigned xch_step = p.xch_world ? *(volatile const unsigned *)p.xch_step : 0u;
 
+    if (threadIdx.x == 0) sm_dead = 0;
     const int G = gridDim.x;
     const int u0 = p.ustart[blockIdx.x];
     const int u1 = p.ustart[blockIdx.x + 1];
@@ -612,7 +608,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                     }
                     nmine++;
                 } else {
-                    cross_merge<HD>(p, pair, row0, rows_here, xch_step);
+                    cross_merge<HD>(p, pair, row0, rows_here, xch_step, &sm_dead);
                 }
                 return;
             }
@@ -696,7 +692,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
         }
         for (int i = 0; i < nmine; i++) {
-            cross_merge<HD>(p, sm_mine[i][0], sm_mine[i][1], sm_mine[i][2], xch_step);
+            cross_merge<HD>(p, sm_mine[i][0], sm_mine[i][1], sm_mine[i][2], xch_step, &sm_dead);
         }
     }
 }

@@ -61,7 +61,6 @@ struct Geo {
     static constexpr int TILE_V = 2 * SUBV;
     static constexpr int SMEM = 2 * TILE_QK + 2 * TILE_QK + 2 * TILE_V + 1024;
 };
-constexpr long long kWaitCycles = 1ll << 31;   // about a second
 
 enum Bar {
     Q_FULL = 0,    // +t
@@ -117,20 +116,27 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 // SM cycles, checked every 256 polls together with the block's abort flag.
 // Returns false once the deadline passed or another role gave up; the caller
 // then leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          int *status, int site)
+struct Waiter {
+    volatile int *abort_flag;   // the block's own (shared memory)
+    int *status;                // the handle's site word
+    int *abort_epoch;           // the handle's word naming the launch that gave up
+    int epoch;
+    long long cycles;
+};
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Waiter &w, int site)
 {
     if (mbar_try(bar, parity)) return true;
     const long long start = clock64();
     for (uint32_t it = 1;; it++) {
         if (mbar_try(bar, parity)) return true;
         if ((it & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - start > kWaitCycles) break;
+            if (*w.abort_flag) return false;
+            if (clock64() - start > w.cycles) break;
         }
     }
-    *abort_flag = 1;
-    atomicExch(status, site);
+    *w.abort_flag = 1;
+    atomicExch(w.abort_epoch, w.epoch);
+    report_timeout(w.status, site);
     return false;
 }
 
@@ -301,6 +307,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag_s;
     volatile int *abort_flag = &abort_flag_s;
+    const Waiter wt = {abort_flag, p.status, p.abort_epoch, p.epoch, p.wait_cycles};
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -361,9 +368,9 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     auto p_col = [](int t) { return kSplit ? 384u + (uint32_t)t * 64u : (uint32_t)t * 128u; };
 
     if (tid == 0) {
-        // a block that finds the status word set (an earlier block gave up)
-        // does nothing but allocate and free
-        abort_flag_s = (*(volatile int *)p.status != 0) ? 1 : 0;
+        // a block that starts after a block of this same launch gave up does
+        // nothing but allocate and free
+        abort_flag_s = (*(volatile int *)p.abort_epoch == p.epoch) ? 1 : 0;
         // the softmax warpgroups arrive once per warp (lane 0 after a __syncwarp)
         mbar_init(BAR(Q_FULL + 0), 4);
         mbar_init(BAR(Q_FULL + 1), 4);
@@ -459,7 +466,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             bool ok = true;
 
             for (int j = 0; j < me.n && ok; j++) {
-                ok = mbar_wait(BAR(S_FULL + t), (uint32_t)(j & 1), abort_flag, p.status, 10 + t);
+                ok = mbar_wait(BAR(S_FULL + t), (uint32_t)(j & 1), wt, 10 + t);
                 if (!ok) break;
                 tc_fence_after();
                 uint32_t s[4][32];
@@ -514,8 +521,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         // complete. With P over S that is implied (this step's S was
                         // committed after it).
                         if (!pv_done) {
-                            ok = mbar_wait(BAR(O_DONE + t), (uint32_t)((j - 1) & 1), abort_flag,
-                                           p.status, 22 + t);
+                            ok = mbar_wait(BAR(O_DONE + t), (uint32_t)((j - 1) & 1), wt, 22 + t);
                             if (!ok) break;
                             tc_fence_after();
                             pv_done = true;
@@ -538,8 +544,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 }
 
                 if (!pv_done) {
-                    ok = mbar_wait(BAR(O_DONE + t), (uint32_t)((j - 1) & 1), abort_flag, p.status,
-                                   22 + t);
+                    ok = mbar_wait(BAR(O_DONE + t), (uint32_t)((j - 1) & 1), wt, 22 + t);
                     if (!ok) break;
                     tc_fence_after();
                 }
@@ -584,8 +589,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
 
             // -- epilogue: O / l to global ------------------------------------------------
             if (ok) {
-                ok = mbar_wait(BAR(O_DONE + t), kSplit ? (uint32_t)((me.n - 1) & 1) : 0u, abort_flag,
-                               p.status, 20 + t);
+                ok = mbar_wait(BAR(O_DONE + t), kSplit ? (uint32_t)((me.n - 1) & 1) : 0u, wt, 20 + t);
             }
             if (ok) {
                 tc_fence_after();
@@ -679,13 +683,13 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             for (int j = 0; j < n_max; j++) {
                 const int s = j & 1;
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
-                if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1u, abort_flag, p.status, 30)) break;
+                if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1u, wt, 30)) break;
                 mbar_expect_tx(BAR(K_FULL + s), TILE_QK);
 #pragma unroll
                 for (int kt = 0; kt < KT; kt++) {
                     tma_load_3d(k_smem(s) + kt * SUB, kmap, BAR(K_FULL + s), 64 * kt, j * BN, kh);
                 }
-                if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1u, abort_flag, p.status, 31)) break;
+                if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1u, wt, 31)) break;
                 mbar_expect_tx(BAR(V_FULL + s), TILE_V);
                 tma_load_3d(v_smem(s), vmap, BAR(V_FULL + s), j * BN, 0, kh);
                 tma_load_3d(v_smem(s) + SUBV, vmap, BAR(V_FULL + s), j * BN + 64, 0, kh);
@@ -696,7 +700,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
         if (lane == 0) {
             bool ok = true;
             for (int t = 0; t < 2 && ok; t++) {
-                if (n_of(t) > 0) ok = mbar_wait(BAR(Q_FULL + t), 0u, abort_flag, p.status, 40 + t);
+                if (n_of(t) > 0) ok = mbar_wait(BAR(Q_FULL + t), 0u, wt, 40 + t);
             }
             // Descriptors are built once; a k-step of 16 halves (32 bytes) adds 2
             // to the start-address field, the second 64-wide sub-tile SUB >> 4.
@@ -725,7 +729,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 }
                 if (last || kSplit) tc_commit(BAR(O_DONE + t));
             };
-            if (ok) ok = mbar_wait(BAR(K_FULL + 0), 0u, abort_flag, p.status, 42);
+            if (ok) ok = mbar_wait(BAR(K_FULL + 0), 0u, wt, 42);
             if (ok) {
                 tc_fence_after();
                 for (int t = 0; t < 2; t++) {
@@ -742,13 +746,11 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                     // has taken this step's out of tensor memory.
                     for (int t = 0; t < 2 && ok; t++) {
                         if (j + 1 < n_of(t)) {
-                            ok = mbar_wait(BAR(S_FREE + t), (uint32_t)(j & 1), abort_flag, p.status,
-                                           47 + t);
+                            ok = mbar_wait(BAR(S_FREE + t), (uint32_t)(j & 1), wt, 47 + t);
                             if (!ok) break;
                             if (!k_ready) {
                                 ok = mbar_wait(BAR(K_FULL + (s ^ 1)),
-                                               (uint32_t)(((j + 1) >> 1) & 1), abort_flag, p.status,
-                                               44);
+                                               (uint32_t)(((j + 1) >> 1) & 1), wt, 44);
                                 if (!ok) break;
                                 k_ready = true;
                             }
@@ -759,11 +761,11 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                     if (!ok) break;
                     if (j + 1 < n_max) tc_commit(BAR(K_EMPTY + (s ^ 1)));
                 }
-                ok = mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 43);
+                ok = mbar_wait(BAR(V_FULL + s), ph, wt, 43);
                 if (!ok) break;
                 for (int t = 0; t < 2 && ok; t++) {
                     if (j < n_of(t)) {
-                        ok = mbar_wait(BAR(P_FULL + t), (uint32_t)(j & 1), abort_flag, p.status, 45 + t);
+                        ok = mbar_wait(BAR(P_FULL + t), (uint32_t)(j & 1), wt, 45 + t);
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(t, s, j == 0, j == n_of(t) - 1);
@@ -771,7 +773,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                     if (!kSplit && j + 1 < n_of(t)) {
                         if (!k_ready) {
                             ok = mbar_wait(BAR(K_FULL + (s ^ 1)), (uint32_t)(((j + 1) >> 1) & 1),
-                                           abort_flag, p.status, 44);
+                                           wt, 44);
                             if (!ok) break;
                             tc_fence_after();
                             k_ready = true;
@@ -857,7 +859,7 @@ bool prefill_tc_eligible(const PrefillParams &p, int hd)
     return encode_fn() != nullptr;
 }
 
-cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, int *status)
+cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, const WaitCtl &w)
 {
     static bool configured[64] = {false};
     int dev = 0;
@@ -904,7 +906,10 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, i
     tp.causal = p.causal;
     tp.q_scale = p.q_scale;
     tp.sl2 = p.sl2;
-    tp.status = status;
+    tp.status = w.status;
+    tp.abort_epoch = w.abort_epoch;
+    tp.epoch = w.epoch;
+    tp.wait_cycles = w.cycles;
     const int group = p.heads / p.kv_heads;
     tp.pair_rows = (group % 2 != 0) ? 1 : 0;
     const int row_blocks = (max_tq + BM - 1) / BM;

@@ -31,128 +31,133 @@ __device__ __forceinline__ void pair_sincos(float theta, int j, int hd, const fl
     sincosf(__fmul_rn((float)pos, inv), &sn, &cs);
 }
 
-// One thread per rotating pair (j, j + hd/2).
+// RoPE in place over x [t][heads][hd]. The angle of a pair depends on the
+// position and on j only, so a thread takes VEC neighbouring pairs of one
+// position, works their sines and cosines out once, and walks a chunk of the
+// heads with them (blockIdx.y picks the chunk): with VEC = 4 every access is
+// a 16-byte one, and the accurate powf / sincosf, which cost more than the
+// memory traffic, are shared by the heads of the chunk.
+constexpr int kRopeHeadChunk = 8;
+
+template <int VEC>
 __global__ void rope_kernel(float *__restrict__ x, long long off,
                             const float *__restrict__ freq_div, int t, int heads, int hd,
                             float theta, int first)
 {
     const int half = hd >> 1;
+    const int per_pos = half / VEC;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)t * heads * half) return;
-    const int j = (int)(i % half);
-    const int h = (int)((i / half) % heads);
-    const int p = (int)(i / ((long long)half * heads));
-    float sn, cs;
-    pair_sincos(theta, j, hd, freq_div, first + p, sn, cs);
-    const size_t base = (size_t)off + ((size_t)p * heads + h) * hd + j;
-    float lo, hi;
-    rotate(x[base], x[base + half], cs, sn, lo, hi);
-    x[base] = lo;
-    x[base + half] = hi;
-}
-
-// One decoded position: q rotated in place, rotated k and plain v into the
-// f16 caches at `pos`. q, k and v may alias one allocation, so no restrict.
-__global__ void rope_cache_f16_kernel(float *q, long long q_off, const float *k,
-                                      long long k_off, const float *v, long long v_off,
-                                      const float *__restrict__ freq_div, int heads,
-                                      int kv_heads, int hd, float theta, int pos,
-                                      uint16_t *__restrict__ kc, uint16_t *__restrict__ vc,
-                                      int cap)
-{
-    const int half = hd >> 1;
-    const int nq = heads * half;
-    const int nk = kv_heads * half;
-    const int nv = kv_heads * hd;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < nq + nk) {
-        const bool is_q = i < nq;
-        const int e = is_q ? i : i - nq;
-        const int j = e % half;
-        const int h = e / half;
-        float sn, cs, lo, hi;
-        pair_sincos(theta, j, hd, freq_div, pos, sn, cs);
-        if (is_q) {
-            const size_t base = (size_t)q_off + (size_t)h * hd + j;
-            rotate(q[base], q[base + half], cs, sn, lo, hi);
-            q[base] = lo;
-            q[base + half] = hi;
-        } else {
-            const size_t base = (size_t)k_off + (size_t)h * hd + j;
-            rotate(k[base], k[base + half], cs, sn, lo, hi);
-            uint16_t *d = kc + ((size_t)h * cap + pos) * hd;
-            d[j] = f16_bits(lo);
-            d[j + half] = f16_bits(hi);
+    if (i >= (long long)t * per_pos) return;
+    const int pos = (int)(i / per_pos);
+    const int j0 = (int)(i % per_pos) * VEC;
+    float sn[VEC], cs[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; e++) pair_sincos(theta, j0 + e, hd, freq_div, first + pos, sn[e], cs[e]);
+    const int h0 = blockIdx.y * kRopeHeadChunk;
+    const int h1 = min(heads, h0 + kRopeHeadChunk);
+    float *row = x + (size_t)off + ((size_t)pos * heads + h0) * hd + j0;
+    // every load of the chunk is issued before its first store
+    float a[kRopeHeadChunk][VEC], b[kRopeHeadChunk][VEC];
+#pragma unroll
+    for (int h = 0; h < kRopeHeadChunk; h++) {
+        if (h0 + h < h1) {
+            if constexpr (VEC == 4) {
+                const float4 lo = *(const float4 *)(row + (size_t)h * hd);
+                const float4 hi = *(const float4 *)(row + (size_t)h * hd + half);
+                a[h][0] = lo.x; a[h][1] = lo.y; a[h][2] = lo.z; a[h][3] = lo.w;
+                b[h][0] = hi.x; b[h][1] = hi.y; b[h][2] = hi.z; b[h][3] = hi.w;
+            } else {
+                a[h][0] = row[(size_t)h * hd];
+                b[h][0] = row[(size_t)h * hd + half];
+            }
         }
-    } else if (i < nq + nk + nv) {
-        const int e = i - nq - nk;
-        const int h = e / hd;
-        const int j = e % hd;
-        vc[((size_t)h * hd + j) * cap + pos] = f16_bits(v[(size_t)v_off + e]);
+    }
+#pragma unroll
+    for (int h = 0; h < kRopeHeadChunk; h++) {
+        if (h0 + h < h1) {
+            float lo[VEC], hi[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; e++) rotate(a[h][e], b[h][e], cs[e], sn[e], lo[e], hi[e]);
+            if constexpr (VEC == 4) {
+                *(float4 *)(row + (size_t)h * hd) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                *(float4 *)(row + (size_t)h * hd + half) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            } else {
+                row[(size_t)h * hd] = lo[0];
+                row[(size_t)h * hd + half] = hi[0];
+            }
+        }
     }
 }
 
-// rope_cache_f16_kernel for a batch of sequences decoding together: sequence
-// blockIdx.y takes row blockIdx.y of q, k and v and its own caches, position
-// and capacity. The arithmetic per element is the single-sequence kernel's.
+// The decode step's RoPE and cache write for a batch of sequences (one is a
+// batch of one): sequence blockIdx.y rotates its q row in place, writes its
+// rotated k row into its f16 K cache and its v row into its transposed f16 V
+// cache, all at its own position. A thread owns pair j of one row of the
+// stacked [q heads | k heads]; the thread of a k row also moves the two
+// values that sit where its pair does, so no thread range is set aside for
+// v. q, k and v may be one allocation (offsets per sequence), so none of the
+// three is restrict.
 __global__ void rope_cache_batched_kernel(const __grid_constant__ RopeBatchParams p)
 {
     const RopeBatchSeq &sq = p.seq[blockIdx.y];
     const int half = p.hd >> 1;
-    const int nq = p.heads * half;
-    const int nk = p.kv_heads * half;
-    const int nv = p.kv_heads * p.hd;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    float *q = p.q + (size_t)blockIdx.y * p.heads * p.hd;
-    const float *k = p.k + (size_t)blockIdx.y * p.kv_heads * p.hd;
-    const float *v = p.v + (size_t)blockIdx.y * p.kv_heads * p.hd;
-    if (i < nq + nk) {
-        const bool is_q = i < nq;
-        const int e = is_q ? i : i - nq;
-        const int j = e % half;
-        const int h = e / half;
-        float sn, cs, lo, hi;
-        pair_sincos(p.theta, j, p.hd, p.freq_div, sq.pos, sn, cs);
-        if (is_q) {
-            const size_t base = (size_t)h * p.hd + j;
-            rotate(q[base], q[base + half], cs, sn, lo, hi);
-            q[base] = lo;
-            q[base + half] = hi;
-        } else {
-            const size_t base = (size_t)h * p.hd + j;
-            rotate(k[base], k[base + half], cs, sn, lo, hi);
-            uint16_t *d = sq.kc + ((size_t)h * sq.cap + sq.pos) * p.hd;
-            d[j] = f16_bits(lo);
-            d[j + half] = f16_bits(hi);
-        }
-    } else if (i < nq + nk + nv) {
-        const int e = i - nq - nk;
-        const int h = e / p.hd;
-        const int j = e % p.hd;
-        sq.vc[((size_t)h * p.hd + j) * sq.cap + sq.pos] = f16_bits(v[e]);
+    const int row = i / half;           // 0..heads-1: q heads, then the kv heads
+    const int j = i - row * half;
+    if (row >= p.heads + p.kv_heads) return;
+    float sn, cs, lo, hi;
+    pair_sincos(p.theta, j, p.hd, p.freq_div, sq.pos, sn, cs);
+    if (row < p.heads) {
+        float *x = p.q + sq.q_off + (size_t)row * p.hd + j;
+        rotate(x[0], x[half], cs, sn, lo, hi);
+        x[0] = lo;
+        x[half] = hi;
+        return;
     }
+    const int h = row - p.heads;
+    const float *x = p.k + sq.k_off + (size_t)h * p.hd + j;
+    rotate(x[0], x[half], cs, sn, lo, hi);
+    uint16_t *kd = sq.kc + ((size_t)h * sq.cap + sq.pos) * p.hd + j;
+    kd[0] = f16_bits(lo);
+    kd[half] = f16_bits(hi);
+    const float *y = p.v + sq.v_off + (size_t)h * p.hd + j;
+    uint16_t *vd = sq.vc + ((size_t)h * p.hd + j) * sq.cap + sq.pos;
+    vd[0] = f16_bits(y[0]);
+    vd[(size_t)half * sq.cap] = f16_bits(y[half]);
 }
 
-// src [n][kv_heads*hd] -> K layout [kv][cap][hd]. Consecutive threads take
-// consecutive source elements, which are consecutive destination elements
-// within a head row, so both sides coalesce.
-template <typename T>
+// src [n][kv_heads*hd] -> K layout [kv][cap][hd]: position ti of head h is a
+// run of hd elements on both sides, so a thread moves VEC neighbours of one
+// run (16 bytes in, 8 or 16 out when VEC = 4).
+template <typename T, int VEC>
 __global__ void cache_append_kernel(const float *__restrict__ src, long long src_off,
                                     T *__restrict__ dst, int n, int kv_heads, int hd, int cap,
                                     int past)
 {
+    const int per_run = hd / VEC;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int d = kv_heads * hd;
-    if (i >= (size_t)n * d) return;
-    const int ti = (int)(i / d);
-    const int h = (int)((i % d) / hd);
-    const int j = (int)(i % hd);
-    const float x = src[(size_t)src_off + i];
+    if (i >= (size_t)n * kv_heads * per_run) return;
+    const int j = (int)(i % per_run) * VEC;
+    const int h = (int)((i / per_run) % kv_heads);
+    const int ti = (int)(i / ((size_t)per_run * kv_heads));
+    const float *in = src + (size_t)src_off + ((size_t)ti * kv_heads + h) * hd + j;
     T *o = dst + ((size_t)h * cap + past + ti) * hd + j;
-    if constexpr (sizeof(T) == 2) {
-        *o = f16_bits(x);
+    if constexpr (VEC == 4) {
+        const float4 x = *(const float4 *)in;
+        if constexpr (sizeof(T) == 2) {
+            uint2 w;
+            w.x = (uint32_t)f16_bits(x.x) | ((uint32_t)f16_bits(x.y) << 16);
+            w.y = (uint32_t)f16_bits(x.z) | ((uint32_t)f16_bits(x.w) << 16);
+            *(uint2 *)o = w;
+        } else {
+            *(float4 *)o = x;
+        }
     } else {
-        *o = x;
+        if constexpr (sizeof(T) == 2) {
+            *o = f16_bits(*in);
+        } else {
+            *o = *in;
+        }
     }
 }
 
@@ -188,16 +193,19 @@ __global__ void cache_append_t_kernel(const float *__restrict__ src, long long s
     }
 }
 
-template <typename T>
-__global__ void cache_grow_kernel(const T *__restrict__ src, T *__restrict__ dst,
-                                  long long rows, long long len, long long src_stride,
-                                  long long dst_stride)
+// Re-strides `rows` runs of `len` elements from a cache of one capacity into
+// one of another. blockIdx.y is the run; the threads of a block walk it, 16
+// bytes at a time when both runs allow (U = uint4), else element by element.
+template <typename U>
+__global__ void cache_grow_kernel(const U *__restrict__ src, U *__restrict__ dst, long long len,
+                                  long long src_stride, long long dst_stride)
 {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= rows * len) return;
-    const long long r = i / len;
-    const long long j = i % len;
-    dst[r * dst_stride + j] = src[r * src_stride + j];
+    const U *in = src + (long long)blockIdx.y * src_stride;
+    U *out = dst + (long long)blockIdx.y * dst_stride;
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < len;
+         j += (long long)gridDim.x * blockDim.x) {
+        out[j] = in[j];
+    }
 }
 
 __global__ void round_f16_kernel(const float *__restrict__ src, uint16_t *__restrict__ dst,
@@ -369,25 +377,30 @@ inline unsigned flat_blocks(size_t n, int threads)
     return (unsigned)((n + threads - 1) / threads);
 }
 
+// names as the reference registers its kernels (device.rs:604-733)
+const KernelReg reg_rope("rope", (const void *)rope_kernel<4>);
+const KernelReg reg_rope_cache("rope_cache_f16", (const void *)rope_cache_batched_kernel);
+const KernelReg reg_append("cache_append_f16", (const void *)cache_append_kernel<uint16_t, 4>);
+const KernelReg reg_append_t("cache_append_t_f16", (const void *)cache_append_t_kernel<uint16_t>);
+const KernelReg reg_grow("cache_grow_f16", (const void *)cache_grow_kernel<uint4>);
+const KernelReg reg_rows_stage("rows_stage", (const void *)rows_stage_kernel);
+
 }  // namespace
 
 void launch_rope(cudaStream_t st, float *x, long long off, const float *freq_div, int t,
                  int heads, int hd, float theta, int first)
 {
-    const size_t n = (size_t)t * heads * (hd / 2);
-    if (n == 0) return;
-    rope_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(x, off, freq_div, t, heads, hd, theta,
-                                                    first);
-}
-
-void launch_rope_cache_f16(cudaStream_t st, float *q, long long q_off, const float *k,
-                           long long k_off, const float *v, long long v_off,
-                           const float *freq_div, int heads, int kv_heads, int hd,
-                           float theta, int pos, uint16_t *kc, uint16_t *vc, int cap)
-{
-    const size_t n = (size_t)heads * hd / 2 + (size_t)kv_heads * hd / 2 + (size_t)kv_heads * hd;
-    rope_cache_f16_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(
-        q, q_off, k, k_off, v, v_off, freq_div, heads, kv_heads, hd, theta, pos, kc, vc, cap);
+    const int half = hd / 2;
+    if ((size_t)t * heads * half == 0) return;
+    const unsigned chunks = (unsigned)((heads + kRopeHeadChunk - 1) / kRopeHeadChunk);
+    const bool vec4 = half % 4 == 0 && off % 4 == 0 && ((uintptr_t)x & 15u) == 0;
+    if (vec4) {
+        const dim3 grid(flat_blocks((size_t)t * (half / 4), 128), chunks);
+        rope_kernel<4><<<grid, 128, 0, st>>>(x, off, freq_div, t, heads, hd, theta, first);
+    } else {
+        const dim3 grid(flat_blocks((size_t)t * half, 128), chunks);
+        rope_kernel<1><<<grid, 128, 0, st>>>(x, off, freq_div, t, heads, hd, theta, first);
+    }
 }
 
 void launch_cache_append(cudaStream_t st, const float *src, long long src_off, void *dst,
@@ -397,11 +410,20 @@ void launch_cache_append(cudaStream_t st, const float *src, long long src_off, v
     const size_t total = (size_t)n * kv_heads * hd;
     if (total == 0) return;
     if (!transposed) {
-        if (f16) {
-            cache_append_kernel<uint16_t><<<flat_blocks(total, 256), 256, 0, st>>>(
+        const bool vec4 = hd % 4 == 0 && src_off % 4 == 0 && ((uintptr_t)src & 15u) == 0 &&
+                          ((uintptr_t)dst & 15u) == 0;
+        const unsigned blocks = flat_blocks(vec4 ? total / 4 : total, 256);
+        if (f16 && vec4) {
+            cache_append_kernel<uint16_t, 4><<<blocks, 256, 0, st>>>(
                 src, src_off, (uint16_t *)dst, n, kv_heads, hd, cap, past);
+        } else if (f16) {
+            cache_append_kernel<uint16_t, 1><<<blocks, 256, 0, st>>>(
+                src, src_off, (uint16_t *)dst, n, kv_heads, hd, cap, past);
+        } else if (vec4) {
+            cache_append_kernel<float, 4><<<blocks, 256, 0, st>>>(
+                src, src_off, (float *)dst, n, kv_heads, hd, cap, past);
         } else {
-            cache_append_kernel<float><<<flat_blocks(total, 256), 256, 0, st>>>(
+            cache_append_kernel<float, 1><<<blocks, 256, 0, st>>>(
                 src, src_off, (float *)dst, n, kv_heads, hd, cap, past);
         }
     } else {
@@ -420,14 +442,28 @@ void launch_cache_append(cudaStream_t st, const float *src, long long src_off, v
 void launch_cache_grow(cudaStream_t st, const void *src, void *dst, long long rows,
                        long long len, long long src_stride, long long dst_stride, int esize)
 {
-    const size_t total = (size_t)rows * len;
-    if (total == 0) return;
-    if (esize == 2) {
-        cache_grow_kernel<uint16_t><<<flat_blocks(total, 256), 256, 0, st>>>(
-            (const uint16_t *)src, (uint16_t *)dst, rows, len, src_stride, dst_stride);
-    } else {
-        cache_grow_kernel<float><<<flat_blocks(total, 256), 256, 0, st>>>(
-            (const float *)src, (float *)dst, rows, len, src_stride, dst_stride);
+    if (rows * len == 0) return;
+    // 16-byte moves when every run starts and ends on a 16-byte boundary
+    const long long per16 = 16 / esize;
+    const bool wide = len % per16 == 0 && src_stride % per16 == 0 && dst_stride % per16 == 0 &&
+                      ((uintptr_t)src & 15u) == 0 && ((uintptr_t)dst & 15u) == 0;
+    const long long n = wide ? len / per16 : len;
+    // rows ride blockIdx.y (at most 65535 a launch)
+    for (long long r0 = 0; r0 < rows; r0 += 65535) {
+        const long long nr = rows - r0 < 65535 ? rows - r0 : 65535;
+        const dim3 grid((unsigned)((n + 255) / 256 < 64 ? (n + 255) / 256 : 64), (unsigned)nr);
+        const char *s8 = (const char *)src + r0 * src_stride * esize;
+        char *d8 = (char *)dst + r0 * dst_stride * esize;
+        if (wide) {
+            cache_grow_kernel<uint4><<<grid, 256, 0, st>>>((const uint4 *)s8, (uint4 *)d8, n,
+                                                          src_stride / per16, dst_stride / per16);
+        } else if (esize == 2) {
+            cache_grow_kernel<uint16_t><<<grid, 256, 0, st>>>((const uint16_t *)s8, (uint16_t *)d8,
+                                                             n, src_stride, dst_stride);
+        } else {
+            cache_grow_kernel<float><<<grid, 256, 0, st>>>((const float *)s8, (float *)d8, n,
+                                                          src_stride, dst_stride);
+        }
     }
 }
 
@@ -457,7 +493,6 @@ void launch_varlen_rope_append(cudaStream_t st, const VarlenParams &p)
 
 void launch_rope_cache_batched(cudaStream_t st, const RopeBatchParams &p)
 {
-    const size_t n = (size_t)p.heads * p.hd / 2 + (size_t)p.kv_heads * p.hd / 2 +
-                     (size_t)p.kv_heads * p.hd;
-    rope_cache_batched_kernel<<<dim3(flat_blocks(n, 256), p.nseq), 256, 0, st>>>(p);
+    const size_t n = (size_t)(p.heads + p.kv_heads) * (p.hd / 2);
+    rope_cache_batched_kernel<<<dim3(flat_blocks(n, 128), p.nseq), 128, 0, st>>>(p);
 }

@@ -242,6 +242,12 @@ class Gpu:
     def synchronize(self) -> None:
         _check(self._lib.llmtie_synchronize(self._h))
 
+    def set_wait_limit_cycles(self, cycles: int) -> None:
+        """How long a device-side wait may spin before it gives up and the
+        next synchronize / download raises `DeviceTimeout`; 0 restores the
+        default of about a second."""
+        _check(self._lib.llmtie_set_wait_limit_cycles(self._h, int(cycles)))
+
     # ---- RoPE ----------------------------------------------------------------
 
     def rope(self, x, off, t, heads, head_dim, theta, first) -> None:
