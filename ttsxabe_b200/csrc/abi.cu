@@ -925,8 +925,15 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         // One block per SM, but never fewer than four units (512 keys) a block:
         // a short context cut any finer spends longer merging partials than
         // it saved streaming them.
+        // (LLMTIE_B200_DECODE_GRID caps the block count: a tuning switch)
+        static const int grid_cap = [] {
+            const char *e = getenv("LLMTIE_B200_DECODE_GRID");
+            const int v = e ? atoi(e) : 0;
+            return v > 0 ? v : LLMTIE_STREAM_MAX_BLOCKS;
+        }();
         const int grid = (int)std::min<long long>(
-            std::min(g->sm_count, LLMTIE_STREAM_MAX_BLOCKS), std::max<long long>(1, units / 4));
+            std::min(std::min(g->sm_count, grid_cap), LLMTIE_STREAM_MAX_BLOCKS),
+            std::max<long long>(1, units / 4));
         const size_t pairs = (size_t)p.nseq * inner;
         const llmtie_status s =
             scratch_reserve(g, scratch, pairs + 1, (size_t)grid * 2, (size_t)hd);
