@@ -922,6 +922,28 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         sp.sl2 = p.sl2;
         sp.twin_q = p.twin_q;
         sp.twin_s = p.twin_s;
+        sp.status = g->timeout_site;
+        sp.wait_cycles = g->wait_cycles;
+        // The tensor maps of the caches, kept with the scratch: they are made
+        // again only when a cache has moved or changed shape.
+        for (int b = 0; b < p.nseq; b++) {
+            DecodeMapKey &key = scratch->map_key[b];
+            if (key.k != p.seq[b].k || key.v != p.seq[b].v || key.cap != p.seq[b].cap ||
+                key.kv_heads != p.kv_heads || key.hd != hd) {
+                if (!decode_tensor_maps(&scratch->kmap[b], &scratch->vmap[b], p.seq[b].k,
+                                        p.seq[b].v, p.kv_heads, p.seq[b].cap, hd)) {
+                    key = DecodeMapKey();
+                    return llmtie_fail(LLMTIE_ERR_DRIVER, "making the tensor maps of a cache");
+                }
+                key.k = p.seq[b].k;
+                key.v = p.seq[b].v;
+                key.cap = p.seq[b].cap;
+                key.kv_heads = p.kv_heads;
+                key.hd = hd;
+            }
+            sp.kmap[b] = scratch->kmap[b];
+            sp.vmap[b] = scratch->vmap[b];
+        }
         // One block per SM, but never fewer than four units (512 keys) a block:
         // a short context cut any finer spends longer merging partials than
         // it saved streaming them.

@@ -47,11 +47,23 @@ struct llmtie_gpu {
     std::vector<llmtie_decode_scratch *> scratches;
 };
 
+// The caches a tensor map was made for: a map is made again only when one of
+// these changes (a cache is reallocated on growth, not on every token).
+struct DecodeMapKey {
+    const void *k = nullptr;
+    const void *v = nullptr;
+    int cap = 0, kv_heads = 0, hd = 0;
+};
+
 struct llmtie_decode_scratch {
     float *part = nullptr;     // [pairs][splits][8][hd + 2]
     unsigned *ctr = nullptr;   // [pairs], zero at rest
     size_t part_floats = 0;
     size_t ctr_words = 0;
+    // tensor maps of the caches this scratch was last used with, per sequence slot
+    DecodeMapKey map_key[32];
+    alignas(64) CUtensorMap kmap[32];
+    alignas(64) CUtensorMap vmap[32];
 };
 
 // Sets the thread's error message and returns `code`.
@@ -175,6 +187,10 @@ int decode_resident_blocks(int hd, int sm_count, int nb);
 // decode_stream.cu: the same operands cut over the grid by work (see there).
 #define LLMTIE_STREAM_MAX_BLOCKS 160
 struct DecodeStreamParams {
+    // Tensor maps of each sequence's caches (see decode_tensor_maps): keys as
+    // [hd/32][kv*cap][32 halves], values as [kv*hd][cap].
+    alignas(64) CUtensorMap kmap[LLMTIE_DECODE_MAX_SEQ];
+    alignas(64) CUtensorMap vmap[LLMTIE_DECODE_MAX_SEQ];
     DecodeSeq seq[LLMTIE_DECODE_MAX_SEQ];
     int ustart[LLMTIE_STREAM_MAX_BLOCKS + 1];     // block c takes units [ustart[c], ustart[c+1])
     long long unit0[LLMTIE_DECODE_MAX_SEQ + 1];   // first 128-key unit of each sequence
@@ -208,8 +224,19 @@ struct DecodeStreamParams {
     long long xch_wait_cycles;               // how long such a wait may spin
     signed char *twin_q;                     // int8 twin of the output (or null), as in DecodeParams
     float *twin_s;
+    int *status;                             // set when a wait on the ring's barriers gave up
+    long long wait_cycles;                   // how long such a wait may spin
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
+// The two tensor maps the ring kernel reads one sequence's caches through:
+// keys [kv][cap][hd] seen as 64-byte column chunks x rows (so that a 32-key
+// block lands in shared memory chunk by chunk, free of bank conflicts), values
+// [kv][hd][cap] seen as rows of `cap`. No swizzle; reads past the end return zero.
+bool decode_tensor_maps(CUtensorMap *kmap, CUtensorMap *vmap, const void *k, const void *v,
+                        int kv_heads, int cap, int hd);
+// cuTensorMapEncodeTiled for f16 data, through the runtime's driver entry point.
+bool llmtie_encode_tiled_f16(CUtensorMap *map, int rank, const void *base, const uint64_t *dims,
+                             const uint64_t *strides_bytes, const uint32_t *box, bool swizzle128);
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
                        const float *v, float *out, long long out_off, int heads, int kv_heads,
                        int hd, int tk, int cap, float q_scale, float s_scale);

@@ -1,16 +1,24 @@
 // The long-context decode kernel: the arithmetic of decode.cu (f32-exact
 // query and probabilities on mma.m16n8k16 by hi/lo splitting, permuted
 // contraction index, log-sum-exp merge by the last block to arrive), fed
-// through a per-warp ring of asynchronous copies and cut over the grid by
-// work rather than by head.
+// through a per-warp ring of TMA copies and cut over the grid by work rather
+// than by head.
 //
 // Why a ring. The kernel is bound by HBM, and a B200 needs tens of kilobytes
 // per SM in flight to cover DRAM latency. Loads that land in registers hold a
-// register for every byte in flight; cp.async lands in shared memory instead,
-// so each warp keeps two whole 32-key blocks (K 8 KB + V 8 KB each at
-// head_dim 128) in flight while it computes on a third. A warp owns its ring
-// outright: there is no block-wide barrier in the key loop, only
-// cp.async.wait_group and __syncwarp.
+// register for every byte in flight; bulk tensor copies land in shared memory
+// instead, so each warp keeps two whole 32-key blocks (K 8 KB + V 8 KB each
+// at head_dim 128) in flight while it computes on a third. A warp owns its
+// ring outright: there is no block-wide barrier in the key loop, only the
+// ring's own mbarriers and __syncwarp.
+//
+// Why TMA. With one warp to a scheduler the loop runs at the speed of that
+// warp's instruction stream, and half of that stream used to be the address
+// arithmetic of thirty-two 16-byte asynchronous copies a lane per block. One
+// lane now issues two tensor copies per block (the key rows as 64-byte
+// column chunks, which also keeps the fragment reads free of bank conflicts;
+// the value rows as they lie) and the warp spends its issue slots on the
+// products. No multicast: every block fetches its own tiles.
 //
 // Why by work. One block per SM is resident (the ring is 192 KB), and a grid
 // cut by (sequence, KV head) leaves SMs idle whenever their count does not
@@ -37,6 +45,63 @@ constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr int kRows = 8;
 constexpr int kStages = 3;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits until a ring stage has landed. Bounded: after `limit` SM cycles it
+// gives up and returns false (the copy engine never completed the stage).
+__device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, long long limit)
+{
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; it++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 63u) == 0 && clock64() - t0 > limit) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y, int z)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem, int src_bytes)
 {
@@ -325,13 +390,15 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
 {
     constexpr int KI = HD / 32;
     constexpr int NT = HD / 8;
-    constexpr int KROW = HD * 2;            // bytes of one key row
-    constexpr int KBYTES = 32 * KROW;       // one 32-key block of keys
+    constexpr int KBYTES = 32 * HD * 2;     // one 32-key block of keys
     constexpr int VBYTES = HD * 64;         // the same block of the transposed values
     constexpr int STAGE = KBYTES + VBYTES;
-    constexpr int KCH = KROW / 16;          // 16-byte chunks in a key row
+    constexpr int KCHUNK = 32 * 64;         // a 64-byte column chunk of the block's 32 key rows
 
-    extern __shared__ __align__(128) unsigned char ring_all[];
+    extern __shared__ unsigned char ring_raw[];
+    // tensor copies want their destination on a 128-byte boundary
+    unsigned char *ring_all = ring_raw + ((128u - (smem_u32(ring_raw) & 127u)) & 127u);
+    __shared__ __align__(8) uint64_t sm_bar[kWarps][kStages];
     __shared__ __align__(16) float sm_o[kWarps][kRows][HD + 8];   // +8: rows 0-3 and 4-7 tile the banks
     __shared__ float sm_m[kWarps][kRows];
     __shared__ float sm_l[kWarps][kRows];
@@ -350,6 +417,20 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     const int g = lane >> 2;
     const int c = lane & 3;
     unsigned char *ring = ring_all + (size_t)warp * kStages * STAGE;
+    const uint32_t ring_s = smem_u32(ring);
+    // The warp's ring barriers: one a stage, completed by the bytes of the
+    // stage's two copies. The stage and phase counters run on across the
+    // segments of the block's run.
+    const uint32_t bar0 = smem_u32(&sm_bar[warp][0]);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; s++) mbar_init(bar0 + 8u * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    uint32_t st_use = 0, ph_use = 0;   // the stage the next block is consumed from, its phase
+    uint32_t st_put = 0;               // the stage the next copy goes to
+    bool ring_ok = true;
 
     // When ranks exchange, the step number picks which of the two gather
     // buffers this launch fills; every block reads it before any block can
@@ -382,8 +463,6 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         const bool whole = (off == 0 && seg_end == n_units);
         const int pair_u0 = (int)p.unit0[b] + inner * n_units;
         const int pair = p.pair0[b] + inner;
-        const uint16_t *kbase = p.seq[b].k + (size_t)kh * cap * HD;
-        const uint16_t *vbase = p.seq[b].v + (size_t)kh * HD * cap;
         const int rows_here = min(kRows, p.rows - rc * kRows);
 
         float m = -CUDART_INF_F;
@@ -394,31 +473,24 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
         }
 
-        // Copies block `blk` (32 keys) into ring stage `st`. Keys past k_end are
-        // zero-filled (a copy of zero source bytes); a key row's two 64-byte
-        // halves are swapped on odd rows so that the fragment reads of two
-        // adjacent rows fall on different banks.
-        auto issue = [&](int blk, int st) {
-            unsigned char *ks = ring + st * STAGE;
-            unsigned char *vs = ks + KBYTES;
-#pragma unroll
-            for (int it = 0; it < KBYTES / 16 / 32; it++) {
-                const int chunk = lane + 32 * it;
-                const int row = chunk / KCH, ch = chunk % KCH;
-                const int key = blk + row;
-                const bool live = key < k_end;
-                const uint16_t *src = kbase + (size_t)(live ? key : k_begin) * HD + ch * 8;
-                cp_async16(ks + row * KROW + ((ch ^ ((row & 1) << 2)) << 4), src, live ? 16 : 0);
+        // Copies block `blk` (32 keys) into the ring's next stage: the key rows
+        // as HD/32 chunks of [32 keys][64 bytes] (two adjacent rows of a chunk
+        // fall on different halves of the banks), the value rows [HD][64
+        // bytes]. Whatever lies past k_end comes along (the next keys of the
+        // cache, its unused capacity, or zeros past its end) and is masked
+        // where it is used.
+        const CUtensorMap *kmap = &p.kmap[b];
+        const CUtensorMap *vmap = &p.vmap[b];
+        const int krow0 = kh * cap, vrow0 = kh * HD;
+        auto issue = [&](int blk) {
+            if (lane == 0) {
+                const uint32_t dst = ring_s + st_put * STAGE;
+                const uint32_t bar = bar0 + 8u * st_put;
+                mbar_expect_tx(bar, STAGE);
+                tma_load_3d(dst, kmap, bar, 0, krow0 + blk, 0);
+                tma_load_2d(dst + KBYTES, vmap, bar, blk, vrow0);
             }
-#pragma unroll
-            for (int it = 0; it < VBYTES / 16 / 32; it++) {
-                const int chunk = lane + 32 * it;
-                const int row = chunk >> 2, ch = chunk & 3;
-                const int k0 = blk + 8 * ch;
-                const bool live = k0 < k_end;
-                const uint16_t *src = vbase + (size_t)row * cap + (live ? k0 : k_begin);
-                cp_async16(vs + row * 64 + ch * 16, src, live ? 16 : 0);
-            }
+            st_put = (st_put + 1 == kStages) ? 0u : st_put + 1;
         };
 
         // The query row goes out first, ahead of the ring's first copies in the
@@ -446,8 +518,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         const int nblk = first < k_end ? (k_end - first + kWarps * 32 - 1) / (kWarps * 32) : 0;
 #pragma unroll
         for (int s = 0; s < kStages - 1; s++) {
-            if (s < nblk) issue(first + s * kWarps * 32, s);
-            cp_async_commit();
+            if (s < nblk) issue(first + s * kWarps * 32);
         }
 
         // ---- query fragments, permuted as the key loads are, split hi / lo ------
@@ -466,15 +537,22 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             // iteration finished with, then wait for this block's.
             {
                 const int nx = i + kStages - 1;
-                if (nx < nblk) issue(first + nx * kWarps * 32, nx % kStages);
-                cp_async_commit();
+                if (nx < nblk) issue(first + nx * kWarps * 32);
             }
-            cp_async_wait<kStages - 1>();
-            __syncwarp();
+            if (ring_ok && !ring_wait(bar0 + 8u * st_use, ph_use, p.wait_cycles)) {
+                // The stage never landed: say so, and finish the run on
+                // whatever the ring holds rather than wait again.
+                ring_ok = false;
+                if (lane == 0) report_timeout(p.status, 80 + warp);
+            }
 
             const int blk = first + i * kWarps * 32;
-            const unsigned char *ks = ring + (i % kStages) * STAGE;
+            const unsigned char *ks = ring + st_use * STAGE;
             const unsigned char *vs = ks + KBYTES;
+            if (++st_use == kStages) {
+                st_use = 0;
+                ph_use ^= 1u;
+            }
 
             // ---- scores: four 8-key tiles ----------------------------------------
             float t[2][2][2];
@@ -483,12 +561,12 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     const int row = 8 * (g >> 1) + 4 * mm + 2 * h + (g & 1);
-                    const unsigned char *krow = ks + row * KROW;
+                    const unsigned char *krow = ks + row * 64 + c * 16;
                     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                     for (int ii = 0; ii < KI; ii++) {
                         uint32_t r[4];
-                        lds128(r, krow + (((4 * ii + c) ^ ((g & 1) << 2)) << 4));
+                        lds128(r, krow + ii * KCHUNK);
                         mma16816(acc, qa[ii][0][0], qa[ii][0][1], qa[ii][0][2], qa[ii][0][3],
                                  r[0], r[1]);
                         mma16816(acc, qa[ii][1][0], qa[ii][1][1], qa[ii][1][2], qa[ii][1][3],
@@ -557,7 +635,6 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
             __syncwarp();   // every lane is done with this stage before it is refilled
         }
-        cp_async_wait<0>();
 
         // ---- the block's four warps merge through shared memory ----------------------
         l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -674,7 +751,10 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                 if (tid == 0) p.ctr[pair] = 0u;   // at rest again for the next call
             }
         }
-        __syncthreads();   // shared memory is reused by the next segment
+        // shared memory is reused by the next segment; what the merge wrote into
+        // the ring is ordered before the copy engine's next writes to it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
         u += seg_end - off;
     }
 
@@ -700,13 +780,29 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
 template <int HD>
 constexpr int ring_bytes()
 {
-    return kWarps * kStages * (32 * HD * 2 + HD * 64);
+    return kWarps * kStages * (32 * HD * 2 + HD * 64) + 128;   // + room to align the ring
 }
 
 const KernelReg reg_s128("attn_decode_h128_run", (const void *)decode_stream_kernel<128>);
 const KernelReg reg_s64("attn_decode_h64_run", (const void *)decode_stream_kernel<64>);
 
 }  // namespace
+
+bool decode_tensor_maps(CUtensorMap *kmap, CUtensorMap *vmap, const void *k, const void *v,
+                        int kv_heads, int cap, int hd)
+{
+    // keys: 32 halves of a row, then the rows of every kv head one after another
+    // (their stride is a whole row), then the row's hd/32 column chunks
+    const uint64_t kd[3] = {32, (uint64_t)kv_heads * (uint64_t)cap, (uint64_t)(hd / 32)};
+    const uint64_t ks[2] = {(uint64_t)hd * 2, 64};
+    const uint32_t kb[3] = {32, 32, (uint32_t)(hd / 32)};
+    if (!llmtie_encode_tiled_f16(kmap, 3, k, kd, ks, kb, false)) return false;
+    // values: a row of `cap` keys per (kv head, channel)
+    const uint64_t vd[2] = {(uint64_t)cap, (uint64_t)kv_heads * (uint64_t)hd};
+    const uint64_t vs[1] = {(uint64_t)cap * 2};
+    const uint32_t vb[2] = {32, (uint32_t)hd};
+    return llmtie_encode_tiled_f16(vmap, 2, v, vd, vs, vb, false);
+}
 
 // Cuts the launch's units into one contiguous run a block.
 //
@@ -942,6 +1038,13 @@ extern "C" llmtie_status llmtie_attn_decode_f16_noalloc(
     sp.sl2 = (scale_q ? 1.0f : scale) * 1.4426950408889634f;
     sp.part = ss.part;
     sp.ctr = ss.ctr;
+    sp.status = g->timeout_site;
+    sp.wait_cycles = g->wait_cycles;
+    // (making the tensor maps is arithmetic on the host: nothing is allocated)
+    if (!decode_tensor_maps(&sp.kmap[0], &sp.vmap[0], k, v, (int)kv_heads, (int)cap,
+                            (int)head_dim)) {
+        return llmtie_fail(LLMTIE_ERR_DRIVER, "making the tensor maps of the caches");
+    }
     long long grid = g->sm_count < kStaticMaxBlocks ? g->sm_count : kStaticMaxBlocks;
     if (units < grid) grid = units;
     // The counters must start at zero whatever an earlier call left behind.

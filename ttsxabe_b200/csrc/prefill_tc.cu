@@ -844,6 +844,25 @@ const KernelReg reg_tc64("flash_attn_64_tc", (const void *)prefill_tc_kernel<64>
 
 }  // namespace
 
+bool llmtie_encode_tiled_f16(CUtensorMap *map, int rank, const void *base, const uint64_t *dims,
+                             const uint64_t *strides_bytes, const uint32_t *box, bool swizzle128)
+{
+    EncodeFn fn = encode_fn();
+    if (!fn || rank < 1 || rank > 5) return false;
+    cuuint64_t d[5], s[4];
+    cuuint32_t b[5], e[5];
+    for (int i = 0; i < rank; i++) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        e[i] = 1;
+        if (i + 1 < rank) s[i] = strides_bytes[i];
+    }
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void *>(base), d, s,
+              b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool prefill_tc_eligible(const PrefillParams &p, int hd)
 {
     if ((hd != 128 && hd != 64) || p.kv_f32) return false;
