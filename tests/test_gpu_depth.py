@@ -163,3 +163,35 @@ def test_decode_batch8_context_131072(gpu):
         assert_parity(f"decode 8 x 131072, sequence {b}", want, got[b])
     del ks, vs
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("tq,past,heads,kv", [(2048, 0, 4, 1), (1500, 37, 2, 1), (8192, 0, 4, 1)])
+def test_cut_row_blocks_merge_to_the_same_answer(gpu, tq, past, heads, kv):
+    """A launch with too few blocks for the device - a short sequence of few
+    heads, or the one KV head a rank of eight holds of the 8192-position
+    prefill - has its long row blocks cut into pieces of their key range that
+    a second kernel merges. Checked against the oracle: every row where that
+    is cheap, the 16-row windows at 8192; `past` 37 puts rows in front of a
+    piece none of whose keys they may see."""
+    rng = np.random.default_rng(tq + past)
+    tk = past + tq
+    cap = (tk + 7) // 8 * 8
+    q = normal_f16(rng, tq * heads * HD)
+    kc = O.round_f16(rng.standard_normal(kv * cap * HD).astype(np.float32))
+    vc = O.round_f16(rng.standard_normal(kv * HD * cap).astype(np.float32))
+    out = gpu.flash_attn_f16(gpu.upload(q), gpu.upload_u16(kc), gpu.upload_u16(vc), tq, past,
+                             heads, kv, HD, cap, SCALE, True)
+    got = gpu.download(out).reshape(tq, heads * HD)
+    assert np.isfinite(got).all()
+    q2 = q.reshape(tq, heads * HD)
+    if tq <= 2048:
+        want = O.prefill(q, kc, vc, tq, past, heads, kv, HD, cap, SCALE, True, fast=True)
+        assert_parity(f"cut prefill {tq}+{past}", want, got.reshape(-1))
+        starts = [0, tq - 16]
+    else:
+        starts = windows(tq)
+    for r0 in starts:
+        want = O.prefill(np.ascontiguousarray(q2[r0:r0 + 16]), kc, vc, 16, past + r0, heads, kv,
+                         HD, cap, SCALE, True)
+        assert_parity(f"cut prefill {tq}+{past} rows {r0}..{r0 + 16}", want,
+                      got[r0:r0 + 16].reshape(-1))

@@ -221,7 +221,7 @@ extern "C" llmtie_status llmtie_set_wait_limit_cycles(llmtie_gpu *g, int64_t cyc
 static WaitCtl next_wait_ctl(llmtie_gpu *g)
 {
     g->epoch = g->epoch == 0x7fffffff ? 1 : g->epoch + 1;
-    return WaitCtl{g->timeout_site, g->abort_epoch, g->epoch, g->wait_cycles};
+    return WaitCtl{g->timeout_site, g->abort_epoch, g->epoch, g->wait_cycles, g->sm_count};
 }
 
 extern "C" llmtie_status llmtie_alloc(llmtie_gpu *g, size_t bytes, void **dptr)

@@ -281,7 +281,7 @@ cudaError_t launch_prefill_mma(cudaStream_t st, const PrefillParams &p, int hd);
 struct PrefillTcSeq {
     int row0, tq, past, tk;   // tk: keys the sequence holds (past + tq when causal)
 };
-#define LLMTIE_TC_MAX_ORDER 256
+#define LLMTIE_TC_MAX_ORDER 1024
 struct PrefillTcParams {
     alignas(64) CUtensorMap kmap[LLMTIE_TC_MAX_SEQ];
     alignas(64) CUtensorMap vmap[LLMTIE_TC_MAX_SEQ];
@@ -299,11 +299,23 @@ struct PrefillTcParams {
     int *abort_epoch;         // set to `epoch` then: later blocks of this launch leave at once
     int epoch;
     long long wait_cycles;    // how long a wait on a barrier may spin
-    // Ragged batches: the (sequence, row block) of grid row blockIdx.y, longest
-    // first over the whole batch and without the empty ones; n_order == 0 means
-    // blockIdx.z is the sequence and blockIdx.y the row block.
+    // The work of grid row blockIdx.y, longest first over the whole launch and
+    // without the empty ones: a (sequence, row-block slot) or, where long row
+    // blocks are cut so that a small launch still fills the device, one piece
+    // of its key tiles. n_order == 0 means blockIdx.z is the sequence and
+    // blockIdx.y the row block, whole.
     int n_order;
-    uint16_t order[LLMTIE_TC_MAX_ORDER];   // sequence << 8 | row-block slot
+    uint32_t order[LLMTIE_TC_MAX_ORDER];   // pieces << 20 | piece << 14 | sequence << 8 | slot
+    uint16_t pslot[LLMTIE_TC_MAX_ORDER];   // where a piece's partial result goes
+    // Partial results of the pieces, merged by prefill_merge_kernel:
+    // part_o [pslot][gridDim.x][2 tiles][128 rows][hd] f32, un-normalised,
+    // part_ml [..][128 rows] (reference maximum in log2 units, sum).
+    float *part_o;
+    float2 *part_ml;
+};
+// One row block whose key tiles were cut into pieces: where its rows go.
+struct PrefillMergeGroup {
+    int seq, slot, pslot0, pieces;
 };
 bool prefill_tc_eligible(const PrefillParams &p, int hd);
 // What a launch needs of the handle for its bounded waits.
@@ -312,6 +324,7 @@ struct WaitCtl {
     int *abort_epoch;
     int epoch;
     long long cycles;
+    int sm_count;             // SMs of the device (decides whether long row blocks are cut)
 };
 cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, const WaitCtl &w);
 

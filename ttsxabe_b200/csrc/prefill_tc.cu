@@ -40,7 +40,10 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <functional>
+#include <mutex>
 #include <vector>
+#include <stdio.h>
 #include <stdlib.h>
 
 namespace {
@@ -315,8 +318,11 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
 
     // ---- which two tiles this block carries ------------------------------------------
     // which sequence and which of its row-block slots (0 = the longest rows)
-    const int seq_i = p.n_order ? (int)(p.order[blockIdx.y] >> 8) : (int)blockIdx.z;
-    const int slot_y = p.n_order ? (int)(p.order[blockIdx.y] & 255u) : (int)blockIdx.y;
+    const uint32_t item = p.n_order ? p.order[blockIdx.y] : 0u;
+    const int seq_i = p.n_order ? (int)((item >> 8) & 63u) : (int)blockIdx.z;
+    const int slot_y = p.n_order ? (int)(item & 255u) : (int)blockIdx.y;
+    const int pieces = p.n_order ? (int)(item >> 20) : 1;      // 1: the row block is whole
+    const int piece = (int)((item >> 14) & 63u);
     const PrefillTcSeq sq = p.seq[seq_i];
     const int group = p.heads / p.kv_heads;
     const int row_blocks = (sq.tq + BM - 1) / BM;
@@ -343,7 +349,13 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
         const int last = p.causal ? min(sq.past + r0 + BM, all_keys) : all_keys;
         return (last + BN - 1) / BN;
     };
-    const int n_a = tiles_of(r0_a), n_b = tiles_of(r0_b);
+    // The key tiles this block takes: all of the row block's, or piece `piece`
+    // of `pieces` equal shares (both tiles see the same keys then: pieces are
+    // only cut where the two tiles are two heads at the same rows).
+    const int all_a = tiles_of(r0_a), all_b = tiles_of(r0_b);
+    const int jbeg = pieces > 1 ? (piece * all_a) / pieces : 0;
+    const int n_a = pieces > 1 ? ((piece + 1) * all_a) / pieces - jbeg : all_a;
+    const int n_b = pieces > 1 ? n_a : all_b;
     auto n_of = [n_a, n_b](int t) { return t == 0 ? n_a : n_b; };
     const int n_max = max(n_a, n_b);
     if (n_max == 0) return;
@@ -485,7 +497,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 bool pv_done = !kSplit || j == 0;
 
                 // -- mask the tiles that reach past what this row may see -----------------
-                const int key0 = j * BN;
+                const int key0 = (jbeg + j) * BN;
                 const int lim = (p.causal ? min(my_pos, all_keys - 1) : all_keys - 1) - key0;
                 if (key0 + BN - 1 > (p.causal ? sq.past + me.r0 : all_keys - 1)) {
 #pragma unroll
@@ -551,7 +563,10 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
 
                 // -- probabilities: l from the un-rounded values, P rounded to f16 -----------
                 const uint64_t sl2_2 = pack2(sl2, sl2);
-                const uint64_t neg_2 = pack2(-m_ref * sl2, -m_ref * sl2);
+                // (a row that has seen no key yet - possible in a piece that starts
+                // past the row's last key - keeps probabilities of zero)
+                const float neg = (m_ref == -CUDART_INF_F) ? 0.0f : -m_ref * sl2;
+                const uint64_t neg_2 = pack2(neg, neg);
                 uint64_t lc[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of partial sums
                 // All 64 pairs first, the four stores to tensor memory after them:
                 // a store fences the compiler's scheduling, and the more independent
@@ -593,7 +608,13 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
             }
             if (ok) {
                 tc_fence_after();
-                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                // A piece leaves its rows un-normalised, with the maximum they
+                // are relative to and their sum, for the merge.
+                const bool part = pieces > 1;
+                const float inv = part ? 1.0f : (l > 0.0f ? 1.0f / l : 0.0f);
+                const long long ptile =
+                    ((long long)p.pslot[blockIdx.y] * gridDim.x + blockIdx.x) * 2 + t;
+                if (part) p.part_ml[ptile * BM + row] = make_float2(m_ref * sl2, l);
                 // A thread holds a row, and rows lie heads*hd elements apart: stored
                 // straight from the registers every 16-byte store of a warp would
                 // open its own line. So each warp turns its 32 rows through shared
@@ -605,14 +626,18 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 constexpr int LPR = RB / 16;               // lanes to a row on the way out
                 constexpr int RPI = 32 / LPR;              // rows an instruction stores
                 const uint32_t scratch = q_smem(t) + (uint32_t)(warp & 3) * (32u * RB);
-                const int esize = p.out_f16 ? 2 : 4;
+                const bool out16 = p.out_f16 && !part;
+                const int esize = out16 ? 2 : 4;
                 const int passes = HD * esize / RB;        // 1 for f16, 2 for f32
-                unsigned char *obase = (unsigned char *)p.out +
-                                       ((long long)(sq.row0 + me.r0 + 32 * (warp & 3)) * p.out_stride +
-                                        me.head * HD) * esize;
+                const long long ostride = part ? HD : p.out_stride;
+                unsigned char *obase =
+                    part ? (unsigned char *)(p.part_o + (ptile * BM + 32 * (warp & 3)) * HD)
+                         : (unsigned char *)p.out +
+                               ((long long)(sq.row0 + me.r0 + 32 * (warp & 3)) * p.out_stride +
+                                me.head * HD) * esize;
                 for (int ps = 0; ps < passes; ps++) {
                     // ---- registers -> shared: this lane's row, RB bytes of it ------------
-                    if (p.out_f16) {
+                    if (out16) {
 #pragma unroll
                         for (int c = 0; c < HD / 32; c++) {
                             uint32_t o[32];
@@ -665,9 +690,8 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                                      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                                      : "r"(src));
-                        if (me.r0 + 32 * (warp & 3) + r < sq.tq) {
-                            *(uint4 *)(obase + (long long)r * p.out_stride * esize + ps * RB +
-                                       k * 16) = v;
+                        if (part || me.r0 + 32 * (warp & 3) + r < sq.tq) {
+                            *(uint4 *)(obase + (long long)r * ostride * esize + ps * RB + k * 16) = v;
                         }
                     }
                     __syncwarp();
@@ -687,12 +711,13 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 mbar_expect_tx(BAR(K_FULL + s), TILE_QK);
 #pragma unroll
                 for (int kt = 0; kt < KT; kt++) {
-                    tma_load_3d(k_smem(s) + kt * SUB, kmap, BAR(K_FULL + s), 64 * kt, j * BN, kh);
+                    tma_load_3d(k_smem(s) + kt * SUB, kmap, BAR(K_FULL + s), 64 * kt,
+                                (jbeg + j) * BN, kh);
                 }
                 if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1u, wt, 31)) break;
                 mbar_expect_tx(BAR(V_FULL + s), TILE_V);
-                tma_load_3d(v_smem(s), vmap, BAR(V_FULL + s), j * BN, 0, kh);
-                tma_load_3d(v_smem(s) + SUBV, vmap, BAR(V_FULL + s), j * BN + 64, 0, kh);
+                tma_load_3d(v_smem(s), vmap, BAR(V_FULL + s), (jbeg + j) * BN, 0, kh);
+                tma_load_3d(v_smem(s) + SUBV, vmap, BAR(V_FULL + s), (jbeg + j) * BN + 64, 0, kh);
             }
         }
     } else if (warp == 9) {
@@ -839,8 +864,98 @@ bool encode_map(CUtensorMap *map, const void *basep, uint64_t inner, uint64_t ro
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// ---- merge of the pieces of cut row blocks -------------------------------------------
+constexpr int kMergeGroups = 128;
+struct PrefillMergeParams {
+    PrefillMergeGroup group[kMergeGroups];
+    int n_groups;
+    const float *part_o;
+    const float2 *part_ml;
+    void *out;
+    long long out_stride;
+    int out_f16;
+    int heads_per_x;          // a grid column of the attention kernel is two heads
+    int grid_x;
+    int row0[64], tq[64];     // per sequence
+};
+
+// Row r of head h of a cut row block: out = sum_p O_p 2^(m_p - M) / sum_p l_p 2^(m_p - M)
+// over its pieces (crates/llmtie-cuda/src/kernels.rs:5836-5879 is the same
+// algebra for decode). A warp takes one row, a lane four channels of it (HD
+// 128) or two (HD 64); blockIdx = (row block, grid column x tile, 4-row slab).
+// The loads of up to eight pieces are all issued before the first is used:
+// the kernel is nothing but their latency.
+template <int HD>
+__global__ void __launch_bounds__(128) prefill_merge_kernel(const __grid_constant__ PrefillMergeParams p)
+{
+    constexpr int V = HD / 32;                 // channels a lane carries
+    constexpr int kBatch = 8;
+    const PrefillMergeGroup g = p.group[blockIdx.x];
+    const int x = blockIdx.y >> 1, t = blockIdx.y & 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = x * p.heads_per_x + t;
+    const int rbs = (p.tq[g.seq] + BM - 1) / BM;
+    const int r0 = (rbs - 1 - g.slot) * BM;
+    const int row = 4 * blockIdx.z + warp;
+    if (r0 + row >= p.tq[g.seq]) return;
+    const long long tile0 = ((long long)g.pslot0 * p.grid_x + x) * 2 + t;
+    const long long tile_step = (long long)p.grid_x * 2;    // from one piece to the next
+    float M = -CUDART_INF_F, L = 0.0f, acc[V];
+#pragma unroll
+    for (int e = 0; e < V; e++) acc[e] = 0.0f;
+    for (int k0 = 0; k0 < g.pieces; k0 += kBatch) {
+        float2 ml[kBatch];
+        float o[kBatch][V];
+#pragma unroll
+        for (int k = 0; k < kBatch; k++) {
+            const long long tile = tile0 + (long long)min(k0 + k, g.pieces - 1) * tile_step;
+            ml[k] = __ldg(&p.part_ml[tile * BM + row]);
+            const float *src = p.part_o + (tile * BM + row) * HD + V * lane;
+            if constexpr (V == 4) {
+                const float4 v = __ldg((const float4 *)src);
+                o[k][0] = v.x; o[k][1] = v.y; o[k][2] = v.z; o[k][3] = v.w;
+            } else {
+                const float2 v = __ldg((const float2 *)src);
+                o[k][0] = v.x; o[k][1] = v.y;
+            }
+        }
+        float bm = M;
+#pragma unroll
+        for (int k = 0; k < kBatch; k++) bm = fmaxf(bm, ml[k].x);   // repeats are harmless
+        const float keep = (M == -CUDART_INF_F) ? 0.0f : ex2(M - bm);
+        L *= keep;
+#pragma unroll
+        for (int e = 0; e < V; e++) acc[e] *= keep;
+#pragma unroll
+        for (int k = 0; k < kBatch; k++) {
+            if (k0 + k < g.pieces) {
+                const float f = (ml[k].x == -CUDART_INF_F) ? 0.0f : ex2(ml[k].x - bm);
+                L += f * ml[k].y;
+#pragma unroll
+                for (int e = 0; e < V; e++) acc[e] += f * o[k][e];
+            }
+        }
+        M = bm;
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    const long long at = (long long)(p.row0[g.seq] + r0 + row) * p.out_stride + head * HD + V * lane;
+    if (p.out_f16) {
+        uint32_t *dst = (uint32_t *)((uint16_t *)p.out + at);
+        dst[0] = pack_f16(acc[0] * inv, acc[1] * inv);
+        if constexpr (V == 4) dst[1] = pack_f16(acc[2] * inv, acc[3] * inv);
+    } else {
+        float *dst = (float *)p.out + at;
+        if constexpr (V == 4) {
+            *(float4 *)dst = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+        } else {
+            *(float2 *)dst = make_float2(acc[0] * inv, acc[1] * inv);
+        }
+    }
+}
+
 const KernelReg reg_tc("flash_attn_h_tc", (const void *)prefill_tc_kernel<128>);
 const KernelReg reg_tc64("flash_attn_64_tc", (const void *)prefill_tc_kernel<64>);
+const KernelReg reg_tcm("flash_attn_h_merge", (const void *)prefill_merge_kernel<128>);
 
 }  // namespace
 
@@ -938,37 +1053,181 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, c
     } else {
         grid = dim3(p.heads, (row_blocks + 1) / 2, p.nseq);
     }
-    if (p.nseq > 1) {
-        // A ragged batch: one grid row per (sequence, row-block slot) that has
-        // work, the slots with the most key tiles first over the whole batch,
-        // so that the SMs' last blocks are the short ones.
-        struct Item { int keys, seq, slot; };
+    // Key tiles row-block slot y of sequence b attends to (0: no rows).
+    auto tiles_of_slot = [&](int b, int y) {
+        const PrefillSeq &s = p.seq[b];
+        const int rbs = (s.tq + BM - 1) / BM;
+        const int slots = tp.pair_rows ? (rbs + 1) / 2 : rbs;
+        if (y >= slots) return 0;
+        const int top = tp.pair_rows ? std::min(rbs, 2 * (slots - 1 - y) + 2)
+                                     : rbs - y;          // row blocks up to and with it
+        const int keys = p.causal ? s.past + std::min(s.tq, top * BM) : s.tk;
+        return (keys + BN - 1) / BN;
+    };
+    // Whether to cut long row blocks into pieces of their key range. A causal
+    // launch is a set of blocks of very unequal length (1 to tq/128 key
+    // tiles); when there are too few of them for the SMs - a short sequence,
+    // or one KV head's share of a long one - the longest block is the launch.
+    // Pieces of at most `cut` tiles write partial results that a second
+    // kernel merges. A piece is a block with a block's fixed costs (its
+    // query tiles staged, first scores, epilogue: some five tile steps), so
+    // the cut is chosen by playing the launch through: blocks go to the SMs
+    // in grid order, longest first, each to the SM that is free first.
+    int cut = 0;
+    {
+        static const bool never = getenv("LLMTIE_B200_NO_SPLIT") != nullptr;
+        std::vector<int> lens;
+        long long work = 0;
+        int longest = 0;
+        for (int b = 0; b < p.nseq; b++) {
+            for (int y = 0;; y++) {
+                const int n = tiles_of_slot(b, y);
+                if (n == 0) break;
+                lens.push_back(n);
+                work += n;
+                longest = std::max(longest, n);
+            }
+        }
+        const int sms = std::max(1, w.sm_count);
+        const double share = (double)work * grid.x / sms;
+        if (!never && !tp.pair_rows && p.nseq <= 64 && longest >= 8 && longest > 1.25 * share) {
+            constexpr double kBlockCost = 5.5;   // a block's fixed costs, in tile steps
+            constexpr double kMergeCost = 5.0;   // the merge kernel, in tile steps
+            auto makespan = [&](int c) {
+                std::vector<int> items;
+                for (int n : lens) {
+                    const int pieces = (c > 0 && n > c) ? (n + c - 1) / c : 1;
+                    for (int k = 0; k < pieces; k++) {
+                        items.push_back(((k + 1) * n) / pieces - (k * n) / pieces);
+                    }
+                }
+                if (items.size() > LLMTIE_TC_MAX_ORDER) return 1e30;
+                std::sort(items.begin(), items.end(), std::greater<int>());
+                std::vector<double> free_at(sms, 0.0);   // a heap of the SMs' finishing times
+                auto later = std::greater<double>();
+                for (int len : items) {
+                    for (unsigned x = 0; x < grid.x; x++) {
+                        std::pop_heap(free_at.begin(), free_at.end(), later);
+                        free_at.back() += len + kBlockCost;
+                        std::push_heap(free_at.begin(), free_at.end(), later);
+                    }
+                }
+                return *std::max_element(free_at.begin(), free_at.end()) + (c > 0 ? kMergeCost : 0.0);
+            };
+            // The search costs a fraction of a millisecond of host time, and a
+            // caller repeats the same shapes: the last answers are kept.
+            struct Memo { long long work; int longest, gx, n, sms, cut; };
+            static std::mutex memo_lock;
+            static std::vector<Memo> memo;
+            bool known = false;
+            {
+                std::lock_guard<std::mutex> hold(memo_lock);
+                for (const Memo &m : memo) {
+                    if (m.work == work && m.longest == longest && m.gx == (int)grid.x &&
+                        m.n == (int)lens.size() && m.sms == sms) {
+                        cut = m.cut;
+                        known = true;
+                    }
+                }
+            }
+            if (!known) {
+                double best = makespan(0);
+                for (int c = (longest + 1) / 2; c >= 6; c -= (c > 24 ? 2 : 1)) {
+                    const double t = makespan(c);
+                    if (t < 0.95 * best && (cut == 0 || t < best)) {
+                        best = t;
+                        cut = c;
+                    }
+                }
+                std::lock_guard<std::mutex> hold(memo_lock);
+                if (memo.size() >= 64) memo.erase(memo.begin());
+                memo.push_back({work, longest, (int)grid.x, (int)lens.size(), sms, cut});
+            }
+        }
+    }
+    static const bool tell = getenv("LLMTIE_B200_TELL_CUT") != nullptr;
+    if (tell) fprintf(stderr, "prefill: row blocks cut at %d tiles\n", cut);
+    std::vector<PrefillMergeGroup> groups;
+    int n_pslots = 0;
+    if (p.nseq > 1 || cut > 0) {
+        // One grid row per (sequence, row-block slot, piece) that has work,
+        // those with the most key tiles first over the whole launch, so that
+        // the SMs' last blocks are the short ones.
+        struct Item { int tiles, seq, slot, piece, pieces, pslot; };
         std::vector<Item> items;
         for (int b = 0; b < p.nseq; b++) {
-            const PrefillSeq &s = p.seq[b];
-            const int rbs = (s.tq + BM - 1) / BM;
-            const int slots = tp.pair_rows ? (rbs + 1) / 2 : rbs;
-            for (int y = 0; y < slots; y++) {
-                const int top = tp.pair_rows ? std::min(rbs, 2 * (slots - 1 - y) + 2)
-                                             : rbs - y;          // row blocks up to and with it
-                const int keys = p.causal ? s.past + std::min(s.tq, top * BM) : s.tk;
-                items.push_back({keys, b, y});
+            for (int y = 0;; y++) {
+                const int n = tiles_of_slot(b, y);
+                if (n == 0) break;
+                const int pieces = (cut > 0 && n > cut) ? (n + cut - 1) / cut : 1;
+                if (pieces > 1) groups.push_back({b, y, n_pslots, pieces});
+                for (int k = 0; k < pieces; k++) {
+                    const int len = ((k + 1) * n) / pieces - (k * n) / pieces;
+                    items.push_back({len, b, y, k, pieces, pieces > 1 ? n_pslots + k : 0});
+                }
+                if (pieces > 1) n_pslots += pieces;
             }
         }
-        if (!items.empty() && items.size() <= LLMTIE_TC_MAX_ORDER) {
+        if (!items.empty() && items.size() <= LLMTIE_TC_MAX_ORDER && n_pslots <= 65535) {
             std::stable_sort(items.begin(), items.end(),
-                             [](const Item &a, const Item &b) { return a.keys > b.keys; });
+                             [](const Item &a, const Item &b) { return a.tiles > b.tiles; });
             tp.n_order = (int)items.size();
             for (size_t i = 0; i < items.size(); i++) {
-                tp.order[i] = (uint16_t)((items[i].seq << 8) | items[i].slot);
+                tp.order[i] = ((uint32_t)items[i].pieces << 20) | ((uint32_t)items[i].piece << 14) |
+                              ((uint32_t)items[i].seq << 8) | (uint32_t)items[i].slot;
+                tp.pslot[i] = (uint16_t)items[i].pslot;
             }
             grid = dim3(grid.x, (unsigned)items.size(), 1);
+        } else {
+            groups.clear();
+            n_pslots = 0;
         }
+    }
+    void *part = nullptr;
+    if (n_pslots > 0) {
+        const size_t tiles = (size_t)n_pslots * grid.x * 2;
+        const size_t o_bytes = tiles * BM * (size_t)hd * sizeof(float);
+        const size_t ml_bytes = tiles * BM * sizeof(float2);
+        const cudaError_t e = cudaMallocAsync(&part, o_bytes + ml_bytes, st);
+        if (e != cudaSuccess) return e;
+        tp.part_o = (float *)part;
+        tp.part_ml = (float2 *)((char *)part + o_bytes);
     }
     if (hd == 128) {
         prefill_tc_kernel<128><<<grid, kThreads, Geo<128>::SMEM, st>>>(tp);
     } else {
         prefill_tc_kernel<64><<<grid, kThreads, Geo<64>::SMEM, st>>>(tp);
     }
-    return cudaGetLastError();
+    cudaError_t err = cudaGetLastError();
+    if (part) {
+        if (err == cudaSuccess) {
+            // the row blocks that were cut: merge their pieces into the output
+            PrefillMergeParams mp;
+            memset(&mp, 0, sizeof(mp));
+            mp.part_o = tp.part_o;
+            mp.part_ml = tp.part_ml;
+            mp.out = p.out;
+            mp.out_stride = p.out_stride;
+            mp.out_f16 = p.out_f16;
+            mp.heads_per_x = 2;
+            mp.grid_x = (int)grid.x;
+            for (int b = 0; b < p.nseq; b++) {
+                mp.row0[b] = p.seq[b].row0;
+                mp.tq[b] = p.seq[b].tq;
+            }
+            for (size_t g0 = 0; g0 < groups.size() && err == cudaSuccess; g0 += kMergeGroups) {
+                mp.n_groups = (int)std::min<size_t>(kMergeGroups, groups.size() - g0);
+                for (int i = 0; i < mp.n_groups; i++) mp.group[i] = groups[g0 + i];
+                const dim3 mg((unsigned)mp.n_groups, grid.x * 2, BM / 4);
+                if (hd == 128) {
+                    prefill_merge_kernel<128><<<mg, 128, 0, st>>>(mp);
+                } else {
+                    prefill_merge_kernel<64><<<mg, 128, 0, st>>>(mp);
+                }
+                err = cudaGetLastError();
+            }
+        }
+        cudaFreeAsync(part, st);
+    }
+    return err;
 }
