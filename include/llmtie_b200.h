@@ -364,10 +364,14 @@ llmtie_status llmtie_cross_attn(llmtie_gpu *g, const float *q, size_t q_len,
 /* ChatModel::run's prefill of one layer (crates/llmtie-chat/src/model.rs:
  * 848-889, :967-980) for `batch` packed ragged sequences in one call: RoPE on
  * q and k, the new K/V written into each sequence's f16 cache at past[b], and
- * causal attention. q f32 [total][heads*hd] (rotated in place), k and v f32
- * [total][kv_heads*hd] (unrotated), cu_seqlens HOST int32 [batch+1],
- * past/cap/k_ptrs/v_ptrs HOST arrays; out f32 [total][heads*hd]. */
-llmtie_status llmtie_prefill_varlen(llmtie_gpu *g, float *q, size_t q_len, const float *k,
+ * causal attention. q f32 [total][heads*hd], k and v f32 [total][kv_heads*hd],
+ * all three unrotated and none of them written (the reference's chain rotates
+ * q in place; here q is rotated on its way into the attention kernel, in two
+ * launches where the caches are 16-byte aligned with capacities that are
+ * multiples of 8 and every sequence holds 128 keys or more, and a copy of it
+ * otherwise). cu_seqlens HOST int32 [batch+1], past/cap/k_ptrs/v_ptrs HOST
+ * arrays; out f32 [total][heads*hd]. */
+llmtie_status llmtie_prefill_varlen(llmtie_gpu *g, const float *q, size_t q_len, const float *k,
                                     size_t k_len, const float *v, size_t v_len,
                                     const int32_t *cu_seqlens, size_t batch,
                                     uint16_t *const *k_ptrs, uint16_t *const *v_ptrs,

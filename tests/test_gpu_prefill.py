@@ -118,6 +118,10 @@ def test_config1_single_layer_prefill(gpu):
     assert_parity("config 1 (varlen entry)", want, gpu.download(out2))
     assert np.array_equal(gpu.download_u16(kc2), gpu.download_u16(dkc))
     assert np.array_equal(gpu.download_u16(vc2), vc)
+    # q is rotated on its way into the kernel, with the chain's bits: the
+    # caller's q is left as it was, and the answers are the chain's exactly
+    assert np.array_equal(gpu.download(dq2), q)
+    assert np.array_equal(gpu.download(out2), got)
 
 
 def test_config2_ragged_batched_prefill(gpu):
@@ -183,9 +187,11 @@ def test_ragged_prefill_of_more_sequences_than_one_launch_maps(gpu):
     cap = 304
     kcs = [gpu.zeros_f16(kv * cap * hd) for _ in range(batch)]
     vcs = [gpu.zeros_f16(kv * cap * hd) for _ in range(batch)]
-    out = gpu.prefill_varlen(gpu.upload(q), gpu.upload(k), gpu.upload(v), cu, kcs, vcs,
+    dq = gpu.upload(q)
+    out = gpu.prefill_varlen(dq, gpu.upload(k), gpu.upload(v), cu, kcs, vcs,
                              [0] * batch, [cap] * batch, None, heads, kv, hd, 10000.0, scale)
     got = gpu.download(out).reshape(total, heads * hd)
+    assert np.array_equal(gpu.download(dq), q)      # rotated in a copy, not in place
     for b in range(batch):
         n, r0 = lens[b], int(cu[b])
         qr = O.rope(q.reshape(total, -1)[r0:r0 + n].reshape(-1), n, heads, hd, 10000.0, 0)

@@ -59,6 +59,24 @@ llmtie_status llmtie_fail(llmtie_status code, const char *fmt, ...)
 
 extern "C" const char *llmtie_last_error(void) { return g_err; }
 
+void *workspace_reserve(Workspace &w, size_t bytes, cudaStream_t st, cudaError_t *err)
+{
+    *err = cudaSuccess;
+    if (bytes <= w.bytes) return w.ptr;
+    if (w.ptr) cudaFreeAsync(w.ptr, st);
+    w.ptr = nullptr;
+    w.bytes = 0;
+    size_t want = 1 << 20;
+    while (want < bytes) want <<= 1;
+    *err = cudaMallocAsync(&w.ptr, want, st);
+    if (*err != cudaSuccess) {
+        w.ptr = nullptr;
+        return nullptr;
+    }
+    w.bytes = want;
+    return w.ptr;
+}
+
 LaunchScope::LaunchScope(llmtie_gpu *g_, const char *name_) : g(g_), name(name_)
 {
     if (g->kprof) cudaEventRecord(g->ev0, g->stream);
@@ -173,6 +191,9 @@ extern "C" void llmtie_close(llmtie_gpu *g)
     if (!g) return;
     cudaSetDevice(g->ordinal);
     if (g->stream) cudaStreamSynchronize(g->stream);
+    if (g->ws_rope.ptr) cudaFreeAsync(g->ws_rope.ptr, g->stream);
+    if (g->ws_part.ptr) cudaFreeAsync(g->ws_part.ptr, g->stream);
+    if (g->stream) cudaStreamSynchronize(g->stream);
     if (g->abort_epoch) cudaFree(g->abort_epoch);
     if (g->timeout_host) cudaFreeHost(g->timeout_host);
     if (g->ev0) cudaEventDestroy(g->ev0);
@@ -221,7 +242,8 @@ extern "C" llmtie_status llmtie_set_wait_limit_cycles(llmtie_gpu *g, int64_t cyc
 static WaitCtl next_wait_ctl(llmtie_gpu *g)
 {
     g->epoch = g->epoch == 0x7fffffff ? 1 : g->epoch + 1;
-    return WaitCtl{g->timeout_site, g->abort_epoch, g->epoch, g->wait_cycles, g->sm_count};
+    return WaitCtl{g->timeout_site, g->abort_epoch, g->epoch, g->wait_cycles, g->sm_count,
+                   &g->ws_part};
 }
 
 extern "C" llmtie_status llmtie_alloc(llmtie_gpu *g, size_t bytes, void **dptr)
@@ -1393,7 +1415,7 @@ extern "C" llmtie_status llmtie_cross_attn(llmtie_gpu *g, const float *q, size_t
 }
 
 extern "C" llmtie_status llmtie_prefill_varlen(
-    llmtie_gpu *g, float *q, size_t q_len, const float *k, size_t k_len, const float *v,
+    llmtie_gpu *g, const float *q, size_t q_len, const float *k, size_t k_len, const float *v,
     size_t v_len, const int32_t *cu_seqlens, size_t batch, uint16_t *const *k_ptrs,
     uint16_t *const *v_ptrs, const int32_t *past, const int32_t *cap, const float *freq_div,
     size_t heads, size_t kv_heads, size_t head_dim, float theta, float scale, float *out,
@@ -1416,6 +1438,7 @@ extern "C" llmtie_status llmtie_prefill_varlen(
                            total * kv_heads * head_dim, std::min(k_len, v_len));
     }
     if (((uintptr_t)q & 15u) != 0) return misaligned("the query", q, 16);
+    if (((uintptr_t)v & 15u) != 0) return misaligned("the value rows", v, 16);
     if (((uintptr_t)out & 7u) != 0) return misaligned("the output", out, 8);
     for (size_t b = 0; b < batch; b++) {
         const int n = cu_seqlens[b + 1] - cu_seqlens[b];
@@ -1452,7 +1475,8 @@ extern "C" llmtie_status llmtie_prefill_varlen(
             pp.seq[b].tk = past[b0 + b] + n;
         }
         vp.total = cu_seqlens[b0 + nb] - base;
-        vp.q = q + (size_t)base * heads * head_dim;
+        if (vp.total == 0) continue;
+        const float *q0 = q + (size_t)base * heads * head_dim;
         vp.k = k + (size_t)base * kv_heads * head_dim;
         vp.v = v + (size_t)base * kv_heads * head_dim;
         vp.freq_div = freq_div;
@@ -1460,14 +1484,7 @@ extern "C" llmtie_status llmtie_prefill_varlen(
         vp.kv_heads = (int)kv_heads;
         vp.hd = (int)head_dim;
         vp.theta = theta;
-        {
-            LaunchScope ls(g, "varlen_rope_append");
-            launch_varlen_rope_append(g->stream, vp);
-            g->launches++;   // two kernels in that launcher
-            const llmtie_status s = ls.done();
-            if (s != LLMTIE_OK) return s;
-        }
-        pp.q = vp.q;
+        pp.q = q0;
         pp.q_stride = (long long)(heads * head_dim);
         pp.out = out + (size_t)base * heads * head_dim;
         pp.out_stride = (long long)(heads * head_dim);
@@ -1478,19 +1495,54 @@ extern "C" llmtie_status llmtie_prefill_varlen(
         pp.sl2 = scale * kLog2e;
         // The tensor-core kernel carries a tensor map per sequence and so at
         // most LLMTIE_TC_MAX_SEQ of them a launch: a longer batch goes in groups.
+        bool all_tc = true;
         for (int s0 = 0; s0 < pp.nseq; s0 += LLMTIE_TC_MAX_SEQ) {
             PrefillParams part = pp;
             part.nseq = std::min(LLMTIE_TC_MAX_SEQ, pp.nseq - s0);
             for (int b = 0; b < part.nseq; b++) part.seq[b] = pp.seq[s0 + b];
-            const bool tc = use_tc(part, (int)head_dim);
+            all_tc = all_tc && use_tc(part, (int)head_dim);
+        }
+        if (getenv("LLMTIE_B200_NO_ROPE_FUSE")) all_tc = false;   // (an A/B switch)
+        // Where every group takes the tensor-memory kernel, q is rotated as
+        // that kernel stages it, from a table of the rows' cosines and sines
+        // that the one-launch pre-pass leaves (it rotates k into the caches
+        // and transposes v into them): two launches a group in all. Otherwise
+        // a copy of q is rotated by the stand-alone kernel, as the reference's
+        // chain does (crates/llmtie-chat/src/model.rs:848-889).
+        const size_t work_floats =
+            (size_t)vp.total * (all_tc ? head_dim : heads * head_dim);
+        cudaError_t werr;
+        void *work = workspace_reserve(g->ws_rope, work_floats * sizeof(float), g->stream, &werr);
+        if (!work) return driver_fail("allocating", werr);
+        llmtie_status st = LLMTIE_OK;
+        if (all_tc) {
+            vp.rope_tab = (float *)work;
+            pp.rope_tab = (const float *)work;
+        } else {
+            const cudaError_t e = cudaMemcpyAsync(work, q0, work_floats * sizeof(float),
+                                                  cudaMemcpyDeviceToDevice, g->stream);
+            if (e != cudaSuccess) return driver_fail("copying the query", e);
+            vp.q = (float *)work;
+            pp.q = (const float *)work;
+        }
+        {
+            LaunchScope ls(g, all_tc ? "varlen_kv" : "varlen_rope_append");
+            launch_varlen_rope_append(g->stream, vp);
+            if (!all_tc) g->launches++;   // two kernels in that launcher then
+            st = ls.done();
+        }
+        for (int s0 = 0; s0 < pp.nseq && st == LLMTIE_OK; s0 += LLMTIE_TC_MAX_SEQ) {
+            PrefillParams part = pp;
+            part.nseq = std::min(LLMTIE_TC_MAX_SEQ, pp.nseq - s0);
+            for (int b = 0; b < part.nseq; b++) part.seq[b] = pp.seq[s0 + b];
+            const bool tc = all_tc || use_tc(part, (int)head_dim);
             LaunchScope ls(g, tc ? "flash_attn_h_tc" : "flash_attn_h");
             const cudaError_t e =
                 tc ? launch_prefill_tc(g->stream, part, (int)head_dim, next_wait_ctl(g))
                    : launch_prefill_mma(g->stream, part, (int)head_dim);
-            if (e != cudaSuccess) return driver_fail("flash_attn_h", e);
-            const llmtie_status s = ls.done();
-            if (s != LLMTIE_OK) return s;
+            st = e != cudaSuccess ? driver_fail("flash_attn_h", e) : ls.done();
         }
+        if (st != LLMTIE_OK) return st;
     }
     return LLMTIE_OK;
 }

@@ -19,6 +19,16 @@ struct KprofEntry {
     double ms = 0.0;
 };
 
+// A device buffer the handle keeps between calls and only ever grows, so that
+// a call which needs scratch memory allocates nothing once it is warm. Work
+// on a handle is stream-ordered, so one call's use ends before the next's begins.
+struct Workspace {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+// Returns at least `bytes` of it (null and *err set if the allocation failed).
+void *workspace_reserve(Workspace &w, size_t bytes, cudaStream_t st, cudaError_t *err);
+
 struct llmtie_gpu {
     int ordinal = 0;
     cudaStream_t stream = nullptr;
@@ -45,6 +55,8 @@ struct llmtie_gpu {
     // are cleared when a timeout is reported, since a launch that gave up may
     // have left them mid-count.
     std::vector<llmtie_decode_scratch *> scratches;
+    Workspace ws_rope;   // the ragged prefill's table of cosines and sines (or its copy of q)
+    Workspace ws_part;   // partial results of a prefill whose long row blocks were cut
 };
 
 // The caches a tensor map was made for: a map is made again only when one of
@@ -153,6 +165,16 @@ __device__ __forceinline__ void report_timeout(int *site_word, int site)
 {
     *(volatile int *)site_word = site;
     __threadfence_system();
+}
+// The rotation of one RoPE pair, with the roundings spelled out so that every
+// kernel that rotates produces the same bits whatever the compiler would have
+// contracted: the fused decode-step and ragged-prefill paths are held to bit
+// equality with rope followed by an append.
+__device__ __forceinline__ void rope_rotate(float a, float b, float cs, float sn, float &lo,
+                                            float &hi)
+{
+    lo = __fmaf_rn(a, cs, -__fmul_rn(b, sn));
+    hi = __fmaf_rn(b, cs, __fmul_rn(a, sn));
 }
 // Acquire load at system scope: the consumer's half of a flag another GPU
 // raised after its own system-wide fence.
@@ -273,6 +295,7 @@ struct PrefillParams {
     int out_f16;
     float q_scale;         // scale when it goes on q before rounding, else 1
     float sl2;             // (scale on the scores, else 1) * log2(e)
+    const float *rope_tab; // tensor-memory kernel only: rotate q while staging it (see PrefillTcParams)
 };
 cudaError_t launch_prefill_mma(cudaStream_t st, const PrefillParams &p, int hd);
 
@@ -312,6 +335,9 @@ struct PrefillTcParams {
     // part_ml [..][128 rows] (reference maximum in log2 units, sum).
     float *part_o;
     float2 *part_ml;
+    // RoPE fused into the staging of q (or null: q arrives rotated): per packed
+    // row, hd/2 cosines then hd/2 sines of the row's position.
+    const float *rope_tab;
 };
 // One row block whose key tiles were cut into pieces: where its rows go.
 struct PrefillMergeGroup {
@@ -325,6 +351,7 @@ struct WaitCtl {
     int epoch;
     long long cycles;
     int sm_count;             // SMs of the device (decides whether long row blocks are cut)
+    Workspace *part;          // where the pieces of cut row blocks leave their partial results
 };
 cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, const WaitCtl &w);
 
@@ -339,12 +366,16 @@ struct VarlenParams {
     VarlenSeq seq[LLMTIE_PREFILL_MAX_SEQ];
     int nseq;
     int total;             // rows over all sequences
-    float *q;              // [total][heads*hd], rotated in place
+    float *q;              // [total][heads*hd], rotated in place (unless rope_tab)
     const float *k;        // [total][kv_heads*hd]
     const float *v;
     const float *freq_div;
     int heads, kv_heads, hd;
     float theta;
+    // When set, q is left alone and the rows' cosines and sines are written
+    // here instead ([total][hd]: hd/2 cosines, hd/2 sines), for the attention
+    // kernel to rotate q with as it stages it; one launch instead of two.
+    float *rope_tab;
 };
 void launch_varlen_rope_append(cudaStream_t st, const VarlenParams &p);
 

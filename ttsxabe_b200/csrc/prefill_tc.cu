@@ -438,6 +438,58 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 constexpr int RPI = 32 / LPR;      // rows a warp covers per load
                 const int sub_row = lane / LPR;
                 const int col4 = lane % LPR;
+                if (p.rope_tab) {
+                    // RoPE on the way in: a lane takes four pairs of a row - its
+                    // floats j..j+3 and their partners hd/2 further on - with the
+                    // row's cosines and sines from the pre-pass's table, rotates
+                    // them with the arithmetic of the stand-alone kernel (the same
+                    // bits), and stores both halves.
+                    constexpr int LPRr = HD / 8;        // lanes per row, each with both halves
+                    constexpr int RPIr = 32 / LPRr;
+                    const int sub = lane / LPRr, c = lane % LPRr;
+                    const float *tab = p.rope_tab + (long long)sq.row0 * HD;
+#pragma unroll
+                    for (int rr0 = 0; rr0 < 32; rr0 += 4 * RPIr) {
+                        float4 a[4], b[4], cs[4], sn[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int r = 32 * w + rr0 + u * RPIr + sub;
+                            a[u] = b[u] = cs[u] = sn[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (me.r0 + r < sq.tq) {
+                                const float *src = qh + (long long)(me.r0 + r) * p.q_stride + 4 * c;
+                                const float *tr = tab + (long long)(me.r0 + r) * HD + 4 * c;
+                                a[u] = __ldg((const float4 *)src);
+                                b[u] = __ldg((const float4 *)(src + HD / 2));
+                                cs[u] = __ldg((const float4 *)tr);
+                                sn[u] = __ldg((const float4 *)(tr + HD / 2));
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int r = 32 * w + rr0 + u * RPIr + sub;
+                            float lo[4], hi[4];
+                            rope_rotate(a[u].x, b[u].x, cs[u].x, sn[u].x, lo[0], hi[0]);
+                            rope_rotate(a[u].y, b[u].y, cs[u].y, sn[u].y, lo[1], hi[1]);
+                            rope_rotate(a[u].z, b[u].z, cs[u].z, sn[u].z, lo[2], hi[2]);
+                            rope_rotate(a[u].w, b[u].w, cs[u].w, sn[u].w, lo[3], hi[3]);
+#pragma unroll
+                            for (int hh = 0; hh < 2; hh++) {
+                                const float *y = hh ? hi : lo;
+                                const int cc = c + hh * LPRr;          // this half's float4 index
+                                const uint32_t w0 = pack_f16(y[0] * p.q_scale, y[1] * p.q_scale);
+                                const uint32_t w1 = pack_f16(y[2] * p.q_scale, y[3] * p.q_scale);
+                                const int chunk = (cc & 15) >> 1;
+                                const uint32_t dst = q_smem(t) + (uint32_t)(cc >> 4) * SUB +
+                                                     (uint32_t)r * 128 +
+                                                     (uint32_t)((chunk ^ (r & 7)) << 4) +
+                                                     (uint32_t)(cc & 1) * 8;
+                                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(dst), "r"(w0),
+                                             "r"(w1)
+                                             : "memory");
+                            }
+                        }
+                    }
+                } else {
                 // eight loads in flight at a time: one load per iteration
                 // would serialise that many global-memory latencies
 #pragma unroll
@@ -464,6 +516,7 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(dst), "r"(lo), "r"(hi)
                                      : "memory");
                     }
+                }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
@@ -1040,6 +1093,7 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, c
     tp.causal = p.causal;
     tp.q_scale = p.q_scale;
     tp.sl2 = p.sl2;
+    tp.rope_tab = p.rope_tab;
     tp.status = w.status;
     tp.abort_epoch = w.abort_epoch;
     tp.epoch = w.epoch;
@@ -1188,8 +1242,9 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, c
         const size_t tiles = (size_t)n_pslots * grid.x * 2;
         const size_t o_bytes = tiles * BM * (size_t)hd * sizeof(float);
         const size_t ml_bytes = tiles * BM * sizeof(float2);
-        const cudaError_t e = cudaMallocAsync(&part, o_bytes + ml_bytes, st);
-        if (e != cudaSuccess) return e;
+        cudaError_t e;
+        part = workspace_reserve(*w.part, o_bytes + ml_bytes, st, &e);
+        if (!part) return e;
         tp.part_o = (float *)part;
         tp.part_ml = (float2 *)((char *)part + o_bytes);
     }
@@ -1227,7 +1282,6 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, c
                 err = cudaGetLastError();
             }
         }
-        cudaFreeAsync(part, st);
     }
     return err;
 }

@@ -12,23 +12,41 @@ __device__ __forceinline__ uint16_t f16_bits(float x)
     return __half_as_ushort(__float2half_rn(x));
 }
 
-// The rotation of one pair, with the roundings spelled out so that every
-// kernel that rotates produces the same bits whatever the compiler would have
-// contracted: the fused decode-step and ragged-prefill kernels are held to
-// bit equality with rope followed by an append.
 __device__ __forceinline__ void rotate(float a, float b, float cs, float sn, float &lo, float &hi)
 {
-    lo = __fmaf_rn(a, cs, -__fmul_rn(b, sn));
-    hi = __fmaf_rn(b, cs, __fmul_rn(a, sn));
+    rope_rotate(a, b, cs, sn, lo, hi);
 }
 
-// The angle of pair j at position pos: f32 throughout, accurate powf.
-__device__ __forceinline__ void pair_sincos(float theta, int j, int hd, const float *freq_div,
-                                            int pos, float &sn, float &cs)
+// The inverse frequency of pair j: f32 throughout, accurate powf.
+__device__ __forceinline__ float inv_freq(float theta, int j, int hd, const float *freq_div)
 {
     float inv = powf(theta, __fdiv_rn(__fmul_rn(-2.0f, (float)j), (float)hd));
     if (freq_div) inv = __fdiv_rn(inv, freq_div[j]);
+    return inv;
+}
+// The angle of a pair at position pos, and its sine and cosine (accurate).
+__device__ __forceinline__ void angle_sincos(float inv, int pos, float &sn, float &cs)
+{
     sincosf(__fmul_rn((float)pos, inv), &sn, &cs);
+}
+// The accurate powf is some hundreds of instructions, far more than anything
+// else these kernels do, and depends on the pair alone: a block works the
+// inverse frequencies of its pairs out once, into shared memory (every thread
+// of the block must call). Pairs past kInvMax are worked out where they are
+// needed (no model is that wide).
+constexpr int kInvMax = 256;
+__device__ __forceinline__ void block_inv_freq(float *inv_s, float theta, int hd,
+                                               const float *freq_div)
+{
+    const int n = min(hd >> 1, kInvMax);
+    const int tid = threadIdx.y * blockDim.x + threadIdx.x;
+    for (int j = tid; j < n; j += blockDim.x * blockDim.y) inv_s[j] = inv_freq(theta, j, hd, freq_div);
+    __syncthreads();
+}
+__device__ __forceinline__ float inv_of(const float *inv_s, float theta, int j, int hd,
+                                        const float *freq_div)
+{
+    return j < kInvMax ? inv_s[j] : inv_freq(theta, j, hd, freq_div);
 }
 
 // RoPE in place over x [t][heads][hd]. The angle of a pair depends on the
@@ -44,6 +62,8 @@ __global__ void rope_kernel(float *__restrict__ x, long long off,
                             const float *__restrict__ freq_div, int t, int heads, int hd,
                             float theta, int first)
 {
+    __shared__ float inv_s[kInvMax];
+    block_inv_freq(inv_s, theta, hd, freq_div);
     const int half = hd >> 1;
     const int per_pos = half / VEC;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -52,7 +72,9 @@ __global__ void rope_kernel(float *__restrict__ x, long long off,
     const int j0 = (int)(i % per_pos) * VEC;
     float sn[VEC], cs[VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; e++) pair_sincos(theta, j0 + e, hd, freq_div, first + pos, sn[e], cs[e]);
+    for (int e = 0; e < VEC; e++) {
+        angle_sincos(inv_of(inv_s, theta, j0 + e, hd, freq_div), first + pos, sn[e], cs[e]);
+    }
     const int h0 = blockIdx.y * kRopeHeadChunk;
     const int h1 = min(heads, h0 + kRopeHeadChunk);
     float *row = x + (size_t)off + ((size_t)pos * heads + h0) * hd + j0;
@@ -99,6 +121,8 @@ __global__ void rope_kernel(float *__restrict__ x, long long off,
 // three is restrict.
 __global__ void rope_cache_batched_kernel(const __grid_constant__ RopeBatchParams p)
 {
+    __shared__ float inv_s[kInvMax];
+    block_inv_freq(inv_s, p.theta, p.hd, p.freq_div);
     const RopeBatchSeq &sq = p.seq[blockIdx.y];
     const int half = p.hd >> 1;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -106,7 +130,7 @@ __global__ void rope_cache_batched_kernel(const __grid_constant__ RopeBatchParam
     const int j = i - row * half;
     if (row >= p.heads + p.kv_heads) return;
     float sn, cs, lo, hi;
-    pair_sincos(p.theta, j, p.hd, p.freq_div, sq.pos, sn, cs);
+    angle_sincos(inv_of(inv_s, p.theta, j, p.hd, p.freq_div), sq.pos, sn, cs);
     if (row < p.heads) {
         float *x = p.q + sq.q_off + (size_t)row * p.hd + j;
         rotate(x[0], x[half], cs, sn, lo, hi);
@@ -293,6 +317,8 @@ __device__ __forceinline__ int varlen_seq_of(const VarlenParams &p, int row)
 // rounding, so the result equals the two-launch chain bit for bit.
 __global__ void varlen_rope_kernel(const __grid_constant__ VarlenParams p)
 {
+    __shared__ float inv_s[kInvMax];
+    block_inv_freq(inv_s, p.theta, p.hd, p.freq_div);
     const int half = p.hd >> 1;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)p.total * half) return;
@@ -302,7 +328,7 @@ __global__ void varlen_rope_kernel(const __grid_constant__ VarlenParams p)
     const VarlenSeq &sq = p.seq[b];
     const int ti = row - sq.row0;
     float sn, cs, lo, hi;
-    pair_sincos(p.theta, j, p.hd, p.freq_div, sq.past + ti, sn, cs);
+    angle_sincos(inv_of(inv_s, p.theta, j, p.hd, p.freq_div), sq.past + ti, sn, cs);
     // Eight heads at a time, every load of a batch issued before its first
     // store: a plain load-rotate-store loop over the heads keeps one access
     // in flight a thread and runs at a third of the memory system's speed.
@@ -368,6 +394,96 @@ __global__ void varlen_append_v_kernel(const __grid_constant__ VarlenParams p)
         const int c = c0 + r, ti = t0 + threadIdx.x;
         if (c < d && ti < sq.n) {
             sq.v[(size_t)c * sq.cap + sq.past + ti] = f16_bits(tile[threadIdx.x][r]);
+        }
+    }
+}
+
+// The ragged prefill's pre-pass in one launch, for the attention kernel that
+// rotates q itself: blocks [0, rope_blocks) take a (row, pair) each - the
+// pair's cosine and sine go to the table, the rotated keys of every kv head
+// into the f16 K cache; the blocks after them transpose v into the f16 V
+// caches through 64 x 64 tiles (tile = blockIdx - rope_blocks over
+// [sequence][position tile][channel tile]). Bits as varlen_rope_kernel's and
+// varlen_append_v_kernel's.
+__global__ void __launch_bounds__(256)
+varlen_kv_kernel(const __grid_constant__ VarlenParams p, int rope_blocks, int ctiles, int ttiles)
+{
+    const int half = p.hd >> 1;
+    if ((int)blockIdx.x < rope_blocks) {
+        __shared__ float inv_s[kInvMax];
+        block_inv_freq(inv_s, p.theta, p.hd, p.freq_div);
+        const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+        if (i >= (long long)p.total * half) return;
+        const int row = (int)(i / half);
+        const int j = (int)(i % half);
+        const VarlenSeq &sq = p.seq[varlen_seq_of(p, row)];
+        const int ti = row - sq.row0;
+        float sn, cs, lo, hi;
+        angle_sincos(inv_of(inv_s, p.theta, j, p.hd, p.freq_div), sq.past + ti, sn, cs);
+        p.rope_tab[(size_t)row * p.hd + j] = cs;
+        p.rope_tab[(size_t)row * p.hd + half + j] = sn;
+        const float *xk = p.k + (size_t)row * p.kv_heads * p.hd + j;
+        constexpr int kBatch = 8;
+        for (int h0 = 0; h0 < p.kv_heads; h0 += kBatch) {
+            float a[kBatch], b[kBatch];
+#pragma unroll
+            for (int e = 0; e < kBatch; e++) {
+                if (h0 + e < p.kv_heads) {
+                    a[e] = xk[(size_t)(h0 + e) * p.hd];
+                    b[e] = xk[(size_t)(h0 + e) * p.hd + half];
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < kBatch; e++) {
+                if (h0 + e < p.kv_heads) {
+                    rotate(a[e], b[e], cs, sn, lo, hi);
+                    uint16_t *d = sq.k + ((size_t)(h0 + e) * sq.cap + sq.past + ti) * p.hd;
+                    d[j] = f16_bits(lo);
+                    d[j + half] = f16_bits(hi);
+                }
+            }
+        }
+        return;
+    }
+    // values: a tile of 64 positions x 64 channels, float4 loads along the
+    // channels, then (where the cache rows allow 8-byte stores) four
+    // consecutive positions of a channel a store
+    __shared__ float tile[64][65];
+    const int tile_i = (int)blockIdx.x - rope_blocks;
+    const VarlenSeq &sq = p.seq[tile_i / (ctiles * ttiles)];
+    const int t0 = ((tile_i / ctiles) % ttiles) * 64;
+    const int c0 = (tile_i % ctiles) * 64;
+    if (t0 >= sq.n) return;
+    const int d = p.kv_heads * p.hd;            // a multiple of 4 (hd is even, checked: hd % 4)
+    const int tid = threadIdx.x;
+    const int c4 = tid & 15, f0 = tid >> 4;
+#pragma unroll
+    for (int pass = 0; pass < 4; pass++) {
+        const int f = pass * 16 + f0;
+        const int ti = t0 + f, c = c0 + 4 * c4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ti < sq.n && c < d) x = __ldg((const float4 *)(p.v + (size_t)(sq.row0 + ti) * d + c));
+        tile[f][4 * c4 + 0] = x.x;
+        tile[f][4 * c4 + 1] = x.y;
+        tile[f][4 * c4 + 2] = x.z;
+        tile[f][4 * c4 + 3] = x.w;
+    }
+    __syncthreads();
+    const bool wide = ((sq.cap | sq.past) & 3) == 0 && (((uintptr_t)sq.v) & 7u) == 0;
+    const int f4 = tid & 15, ch0 = tid >> 4;
+#pragma unroll
+    for (int pass = 0; pass < 4; pass++) {
+        const int ch = pass * 16 + ch0;
+        const int c = c0 + ch, ti = t0 + 4 * f4;
+        if (c >= d || ti >= sq.n) continue;
+        uint16_t *dst = sq.v + (size_t)c * sq.cap + sq.past + ti;
+        if (wide && ti + 4 <= sq.n) {
+            uint2 o;
+            o.x = (uint32_t)f16_bits(tile[4 * f4 + 0][ch]) | ((uint32_t)f16_bits(tile[4 * f4 + 1][ch]) << 16);
+            o.y = (uint32_t)f16_bits(tile[4 * f4 + 2][ch]) | ((uint32_t)f16_bits(tile[4 * f4 + 3][ch]) << 16);
+            *(uint2 *)dst = o;
+        } else {
+            for (int e = 0; e < 4 && ti + e < sq.n; e++) dst[e] = f16_bits(tile[4 * f4 + e][ch]);
         }
     }
 }
@@ -484,6 +600,15 @@ void launch_varlen_rope_append(cudaStream_t st, const VarlenParams &p)
 {
     if (p.total == 0) return;
     const size_t n = (size_t)p.total * (p.hd / 2);
+    if (p.rope_tab) {
+        int longest = 0;
+        for (int b = 0; b < p.nseq; b++) longest = p.seq[b].n > longest ? p.seq[b].n : longest;
+        const int rope_blocks = (int)flat_blocks(n, 256);
+        const int ctiles = (p.kv_heads * p.hd + 63) / 64, ttiles = (longest + 63) / 64;
+        varlen_kv_kernel<<<rope_blocks + ctiles * ttiles * p.nseq, 256, 0, st>>>(p, rope_blocks,
+                                                                               ctiles, ttiles);
+        return;
+    }
     varlen_rope_kernel<<<flat_blocks(n, 128), 128, 0, st>>>(p);
     int max_n = 0;
     for (int b = 0; b < p.nseq; b++) max_n = p.seq[b].n > max_n ? p.seq[b].n : max_n;
