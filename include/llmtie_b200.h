@@ -129,6 +129,35 @@ llmtie_status llmtie_cache_append(llmtie_gpu *g, const float *src, size_t src_le
                                   size_t kv_heads, size_t head_dim, size_t cap,
                                   size_t past, int32_t transposed);
 
+/* ---- Whisper cross-attention cache build ------------------------------------- */
+
+/* Gpu::split_heads_f16_at / split_heads_t_f16_at (device.rs:5636-5665, kernels
+ * kernels.rs:5089-5139): the block x[x_off .. x_off + t*heads*head_dim] of f32
+ * [t][heads*head_dim], plus the row bias[bias_off ..] when bias is not NULL
+ * (the f32 add a projection's epilogue would have made), rounded to f16 into
+ * keys [heads][cap][head_dim] or, transposed, values [heads][head_dim][cap].
+ * The reference allocates the result at cap == t; here the caller passes a
+ * zeroed buffer (llmtie_zeros) and may ask for cap > t: positions past t are
+ * left as they are, so a cache of 1500 frames can be given a capacity of 1504
+ * and its value rows 16-byte alignment, which is what lets the cross-attention
+ * calls below stream it through the fast decode kernel. */
+llmtie_status llmtie_split_heads_f16_at(llmtie_gpu *g, const float *x, size_t x_len,
+                                        size_t x_off, const float *bias, size_t bias_len,
+                                        size_t bias_off, uint16_t *out, size_t out_len, size_t t,
+                                        size_t heads, size_t head_dim, size_t cap,
+                                        int32_t transposed);
+/* AsrModel::cache's loop over the decoder layers (crates/llmtie-asr/src/model.rs:
+ * 917-939) in two launches: k_all and v_all f32 [layers][t][heads*head_dim] are
+ * the batched projections of the encoder output, v_bias f32 [layers][heads*
+ * head_dim] the value biases (NULL: none). k_out f16 [layers][heads][cap]
+ * [head_dim] and v_out f16 [layers][heads][head_dim][cap], both zeroed by the
+ * caller; layer l's caches start l*heads*cap*head_dim elements in. */
+llmtie_status llmtie_cross_kv_build(llmtie_gpu *g, const float *k_all, size_t k_len,
+                                    const float *v_all, size_t v_len, const float *v_bias,
+                                    size_t v_bias_len, uint16_t *k_out, size_t k_out_len,
+                                    uint16_t *v_out, size_t v_out_len, size_t layers, size_t t,
+                                    size_t heads, size_t head_dim, size_t cap);
+
 /* ---- RoPE ----------------------------------------------------------------- */
 
 /* Gpu::rope / rope_scaled (device.rs:5410-5471): NeoX/halves RoPE in place on

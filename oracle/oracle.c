@@ -623,3 +623,23 @@ int orc_decode_fast(const float *q, const uint16_t *k, const uint16_t *v,
     free(pl);
     return threads;
 }
+
+/* ---- Whisper cross-attention cache build -------------------------------------- */
+
+/* crates/llmtie-cuda/src/kernels.rs:5089-5139 (split_heads_f16 and
+ * split_heads_t_f16): x f32 [t][heads*hd] plus an optional bias row, rounded
+ * to f16 into [heads][cap][hd] or, transposed, [heads][hd][cap]. The
+ * reference's buffers have cap == t; positions past t are not written. */
+void orc_split_heads_f16(const float *x, const float *bias, uint16_t *out,
+                         size_t t, size_t heads, size_t hd, size_t cap,
+                         int transposed)
+{
+    const size_t d = heads * hd;
+    for (size_t i = 0; i < t * d; i++) {
+        const size_t ti = i / d, h = (i % d) / hd, j = i % hd;
+        const float v = x[i] + (bias ? bias[i % d] : 0.0f);
+        const size_t at = transposed ? (h * hd + j) * cap + ti
+                                     : (h * cap + ti) * hd + j;
+        out[at] = orc_f32_to_f16(v);
+    }
+}

@@ -141,6 +141,13 @@ int orc_decode_fast(const float *q, const uint16_t *k, const uint16_t *v,
 
 int orc_max_threads(void);
 
+/* crates/llmtie-cuda/src/kernels.rs:5089-5139: x f32 [t][heads*hd] (+ bias
+ * row or NULL) rounded to f16 into [heads][cap][hd] or, transposed,
+ * [heads][hd][cap]; positions past t are not written. */
+void orc_split_heads_f16(const float *x, const float *bias, uint16_t *out,
+                         size_t t, size_t heads, size_t hd, size_t cap,
+                         int transposed);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,6 +60,7 @@ def lib() -> C.CDLL:
         L.orc_decode_fast.restype = i32
         L.orc_decode_fast.argtypes = [vp, vp, vp, sz, sz, sz, sz, sz, f32, i32, vp, i32]
         L.orc_max_threads.restype = i32
+        L.orc_split_heads_f16.argtypes = [vp, vp, vp, sz, sz, sz, sz, i32]
         _lib = L
     return _lib
 
@@ -200,6 +201,18 @@ def decode_fast(q, k, v, heads, kv_heads, hd, tk, cap, scale, scale_q, threads=0
     used = lib().orc_decode_fast(_p(q), _p(k), _p(v), heads, kv_heads, hd, tk, cap, scale,
                                  int(scale_q), _p(out), threads)
     return out, used
+
+
+def split_heads_f16(x, bias, t, heads, hd, cap=None, transposed=False) -> np.ndarray:
+    """f16 bits of the cache [heads][cap][hd] (or transposed [heads][hd][cap])
+    holding x [t][heads*hd] + bias; zero past t."""
+    cap = t if cap is None else cap
+    x = _f32(x).reshape(-1)
+    b = None if bias is None else _f32(bias).reshape(-1)
+    out = np.zeros(heads * cap * hd, dtype=np.uint16)
+    lib().orc_split_heads_f16(_p(x), None if b is None else _p(b), _p(out), t, heads, hd, cap,
+                              int(transposed))
+    return out
 
 
 def max_threads() -> int:

@@ -222,3 +222,20 @@ def test_quantize_q8_known_answers_and_numpy_twin():
     assert np.array_equal(c1, c2) and np.array_equal(s1, s2)
     back = c1.reshape(-1, 32).astype(np.float32) * s1[:, None]
     assert np.abs(back.reshape(-1) - y).max() <= 0.5 * s1.max() * 1.0001
+
+
+def test_split_heads_is_a_reshape_with_rounding():
+    """The cross-attention cache builders (crates/llmtie-cuda/src/kernels.rs:
+    5089-5139) against numpy: [t][heads*hd] (+ bias) -> [heads][cap][hd] and
+    [heads][hd][cap], f16, zero past t."""
+    t, heads, hd, cap = 11, 3, 8, 16
+    x = O.seq(t * heads * hd, 5)
+    bias = O.seq(heads * hd, 6)
+    y = (x.reshape(t, heads * hd) + bias[None, :]).astype(np.float16).reshape(t, heads, hd)
+    k = np.zeros((heads, cap, hd), np.float16)
+    k[:, :t, :] = y.transpose(1, 0, 2)
+    v = np.zeros((heads, hd, cap), np.float16)
+    v[:, :, :t] = y.transpose(1, 2, 0)
+    assert np.array_equal(O.split_heads_f16(x, bias, t, heads, hd, cap=cap), k.view(np.uint16).reshape(-1))
+    assert np.array_equal(O.split_heads_f16(x, bias, t, heads, hd, cap=cap, transposed=True),
+                          v.view(np.uint16).reshape(-1))

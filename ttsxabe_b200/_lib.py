@@ -40,6 +40,8 @@ PROTOTYPES = {
     "llmtie_cache_grow": (i32, [vp, vp, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
     "llmtie_cache_append_f16": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
     "llmtie_cache_append": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
+    "llmtie_split_heads_f16_at": (i32, [vp, vp, sz, sz, vp, sz, sz, vp, sz, sz, sz, sz, sz, i32]),
+    "llmtie_cross_kv_build": (i32, [vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz]),
     "llmtie_rope_scaled": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, f32, sz]),
     "llmtie_rope_cache_f16": (
         i32,

@@ -435,6 +435,73 @@ extern "C" llmtie_status llmtie_cache_append(llmtie_gpu *g, const float *src, si
                        transposed != 0, false);
 }
 
+// ---- Whisper cross-attention cache build ----------------------------------------
+
+static llmtie_status split_impl(llmtie_gpu *g, const float *x, size_t x_len, size_t x_off,
+                                size_t x_layer, const float *bias, size_t bias_len,
+                                size_t bias_off, size_t bias_layer, uint16_t *out, size_t out_len,
+                                size_t layers, size_t t, size_t heads, size_t hd, size_t cap,
+                                bool transposed)
+{
+    NEED_HANDLE(g);
+    const size_t d = heads * hd, n = t * d;
+    if (layers == 0 || n == 0) return LLMTIE_OK;
+    if (cap < t) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", t, cap);
+    }
+    if (x_off + (layers - 1) * x_layer + n > x_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           x_off + (layers - 1) * x_layer + n, x_len);
+    }
+    if (bias && bias_off + (layers - 1) * bias_layer + d > bias_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           bias_off + (layers - 1) * bias_layer + d, bias_len);
+    }
+    if (layers * heads * cap * hd > out_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           layers * heads * cap * hd, out_len);
+    }
+    if (!fits_i32(t) || !fits_i32(d) || !fits_i32(cap) || !fits_i32(layers)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "cache geometry does not fit 32 bits");
+    }
+    LaunchScope ls(g, transposed ? "split_heads_t_f16" : "split_heads_f16");
+    launch_split_heads(g->stream, x + x_off, (long long)x_layer, bias ? bias + bias_off : nullptr,
+                       (long long)bias_layer, out, (long long)(heads * cap * hd), (int)layers,
+                       (int)t, (int)heads, (int)hd, (int)cap, transposed);
+    return ls.done();
+}
+
+extern "C" llmtie_status llmtie_split_heads_f16_at(llmtie_gpu *g, const float *x, size_t x_len,
+                                                   size_t x_off, const float *bias,
+                                                   size_t bias_len, size_t bias_off,
+                                                   uint16_t *out, size_t out_len, size_t t,
+                                                   size_t heads, size_t head_dim, size_t cap,
+                                                   int32_t transposed)
+{
+    return split_impl(g, x, x_len, x_off, 0, bias, bias_len, bias_off, 0, out, out_len, 1, t, heads,
+                      head_dim, cap, transposed != 0);
+}
+
+extern "C" llmtie_status llmtie_cross_kv_build(llmtie_gpu *g, const float *k_all, size_t k_len,
+                                               const float *v_all, size_t v_len,
+                                               const float *v_bias, size_t v_bias_len,
+                                               uint16_t *k_out, size_t k_out_len, uint16_t *v_out,
+                                               size_t v_out_len, size_t layers, size_t t,
+                                               size_t heads, size_t head_dim, size_t cap)
+{
+    if (cap % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_CACHE_CAPACITY,
+                           "an f16 cache with an odd capacity of %zu", cap);
+    }
+    const size_t d = heads * head_dim;
+    llmtie_status s = split_impl(g, k_all, k_len, 0, t * d, nullptr, 0, 0, 0, k_out, k_out_len,
+                                 layers, t, heads, head_dim, cap, false);
+    if (s != LLMTIE_OK) return s;
+    return split_impl(g, v_all, v_len, 0, t * d, v_bias, v_bias_len, 0, d, v_out, v_out_len, layers,
+                      t, heads, head_dim, cap, true);
+}
+
 // ---- RoPE ---------------------------------------------------------------------
 
 extern "C" llmtie_status llmtie_rope_scaled(llmtie_gpu *g, float *x, size_t x_len, size_t off,

@@ -119,6 +119,13 @@ void launch_cache_append(cudaStream_t st, const float *src, long long src_off, v
 void launch_cache_grow(cudaStream_t st, const void *src, void *dst, long long rows,
                        long long len, long long src_stride, long long dst_stride, int esize);
 void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n);
+// `layers` blocks of x f32 [t][heads*hd], x_layer elements apart (+ bias rows
+// bias_layer apart, or null), into f16 caches out_layer apart: keys
+// [heads][cap][hd] or, transposed, values [heads][hd][cap]. Positions past t
+// are not written.
+void launch_split_heads(cudaStream_t st, const float *x, long long x_layer, const float *bias,
+                        long long bias_layer, uint16_t *out, long long out_layer, int layers, int t,
+                        int heads, int hd, int cap, bool transposed);
 // Whisper encoder staging: qkv f32 [t][3*heads*64] -> K f16 [heads][tp][64],
 // V f16 [heads][64][tp] (tp = padded t), zero padded; `batch` utterances one
 // after another in qkv, each with its K then V in the staging buffer.

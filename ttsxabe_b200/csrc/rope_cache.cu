@@ -302,6 +302,102 @@ rows_stage_kernel(const float *__restrict__ qkv, uint16_t *__restrict__ k,
 }
 
 
+// The Whisper cross-attention caches from the decoder layers' projections of
+// the encoder output (crates/llmtie-asr/src/model.rs:891-939): x f32
+// [layers][t][d] (+ a bias row [layers][d] or none) -> f16 caches of `cap`
+// positions a head, zero past t: keys [layers][heads][cap][hd], or transposed
+// values [layers][heads][hd][cap]. blockIdx = (64-channel chunk, 64-frame
+// chunk, layer); float4 loads along the channels, 8-byte stores (of four
+// channels for keys, of four frames - through a shared tile - for values).
+// Needs d % 4 == 0, hd % 4 == 0 and, transposed, cap % 4 == 0.
+template <bool T>
+__global__ void __launch_bounds__(256)
+split_heads_kernel(const float *__restrict__ x, long long x_layer, const float *__restrict__ bias,
+                   long long bias_layer, uint16_t *__restrict__ out, long long out_layer, int t,
+                   int d, int hd, int cap)
+{
+    __shared__ float tile[64][65];
+    x += (size_t)blockIdx.z * x_layer;
+    out += (size_t)blockIdx.z * out_layer;
+    if (bias) bias += (size_t)blockIdx.z * bias_layer;
+    const int c0 = blockIdx.x * 64, t0 = blockIdx.y * 64;
+    const int tid = threadIdx.x;
+    const int c4 = tid & 15, f0 = tid >> 4;
+    const int c = c0 + 4 * c4;
+    float4 bz = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias && c < d) bz = __ldg((const float4 *)(bias + c));
+#pragma unroll
+    for (int pass = 0; pass < 4; pass++) {
+        const int f = pass * 16 + f0;
+        const int ti = t0 + f;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ti < t && c < d) {
+            v = __ldg((const float4 *)(x + (size_t)ti * d + c));
+            // the same f32 add the projection's epilogue would have made
+            v.x = __fadd_rn(v.x, bz.x);
+            v.y = __fadd_rn(v.y, bz.y);
+            v.z = __fadd_rn(v.z, bz.z);
+            v.w = __fadd_rn(v.w, bz.w);
+        }
+        if constexpr (!T) {
+            if (ti < t && c < d) {
+                const int h = c / hd, j = c % hd;
+                uint2 o;
+                o.x = (uint32_t)f16_bits(v.x) | ((uint32_t)f16_bits(v.y) << 16);
+                o.y = (uint32_t)f16_bits(v.z) | ((uint32_t)f16_bits(v.w) << 16);
+                *(uint2 *)(out + ((size_t)h * cap + ti) * hd + j) = o;
+            }
+        } else {
+            tile[f][4 * c4 + 0] = v.x;
+            tile[f][4 * c4 + 1] = v.y;
+            tile[f][4 * c4 + 2] = v.z;
+            tile[f][4 * c4 + 3] = v.w;
+        }
+    }
+    if constexpr (T) {
+        __syncthreads();
+        const int f4 = tid & 15, ch0 = tid >> 4;
+#pragma unroll
+        for (int pass = 0; pass < 4; pass++) {
+            const int ch = pass * 16 + ch0;
+            const int cc = c0 + ch, ti = t0 + 4 * f4;
+            if (cc >= d || ti >= t) continue;
+            uint16_t *dst = out + (size_t)cc * cap + ti;     // cc = h*hd + j
+            if (ti + 4 <= t) {
+                uint2 o;
+                o.x = (uint32_t)f16_bits(tile[4 * f4 + 0][ch]) |
+                      ((uint32_t)f16_bits(tile[4 * f4 + 1][ch]) << 16);
+                o.y = (uint32_t)f16_bits(tile[4 * f4 + 2][ch]) |
+                      ((uint32_t)f16_bits(tile[4 * f4 + 3][ch]) << 16);
+                *(uint2 *)dst = o;
+            } else {
+                for (int e = 0; e < 4 && ti + e < t; e++) dst[e] = f16_bits(tile[4 * f4 + e][ch]);
+            }
+        }
+    }
+}
+
+// The same for shapes the wide kernel does not take: one element a thread.
+template <bool T>
+__global__ void split_heads_any_kernel(const float *__restrict__ x, long long x_layer,
+                                       const float *__restrict__ bias, long long bias_layer,
+                                       uint16_t *__restrict__ out, long long out_layer, int t, int d,
+                                       int hd, int cap)
+{
+    x += (size_t)blockIdx.y * x_layer;
+    out += (size_t)blockIdx.y * out_layer;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)t * d) return;
+    const int ti = (int)(i / d), c = (int)(i % d);
+    float v = x[i];
+    if (bias) v = __fadd_rn(v, bias[(size_t)blockIdx.y * bias_layer + c]);
+    if constexpr (T) {
+        out[(size_t)c * cap + ti] = f16_bits(v);
+    } else {
+        out[((size_t)(c / hd) * cap + ti) * hd + c % hd] = f16_bits(v);
+    }
+}
+
 // Packed ragged sequences: which sequence a packed row belongs to.
 __device__ __forceinline__ int varlen_seq_of(const VarlenParams &p, int row)
 {
@@ -500,6 +596,8 @@ const KernelReg reg_append("cache_append_f16", (const void *)cache_append_kernel
 const KernelReg reg_append_t("cache_append_t_f16", (const void *)cache_append_t_kernel<uint16_t>);
 const KernelReg reg_grow("cache_grow_f16", (const void *)cache_grow_kernel<uint4>);
 const KernelReg reg_rows_stage("rows_stage", (const void *)rows_stage_kernel);
+const KernelReg reg_split("split_heads_f16", (const void *)split_heads_kernel<false>);
+const KernelReg reg_split_t("split_heads_t_f16", (const void *)split_heads_kernel<true>);
 
 }  // namespace
 
@@ -579,6 +677,43 @@ void launch_cache_grow(cudaStream_t st, const void *src, void *dst, long long ro
         } else {
             cache_grow_kernel<float><<<grid, 256, 0, st>>>((const float *)s8, (float *)d8, n,
                                                           src_stride, dst_stride);
+        }
+    }
+}
+
+void launch_split_heads(cudaStream_t st, const float *x, long long x_layer, const float *bias,
+                        long long bias_layer, uint16_t *out, long long out_layer, int layers, int t,
+                        int heads, int hd, int cap, bool transposed)
+{
+    const int d = heads * hd;
+    if ((size_t)layers * t * d == 0) return;
+    const bool wide = d % 4 == 0 && hd % 4 == 0 && x_layer % 4 == 0 && out_layer % 4 == 0 &&
+                      ((uintptr_t)x & 15u) == 0 && ((uintptr_t)out & 7u) == 0 &&
+                      (!bias || (((uintptr_t)bias & 15u) == 0 && bias_layer % 4 == 0)) &&
+                      (!transposed || cap % 4 == 0) && layers <= 65535;
+    if (wide) {
+        const dim3 grid((d + 63) / 64, (t + 63) / 64, layers);
+        if (transposed) {
+            split_heads_kernel<true><<<grid, 256, 0, st>>>(x, x_layer, bias, bias_layer, out,
+                                                          out_layer, t, d, hd, cap);
+        } else {
+            split_heads_kernel<false><<<grid, 256, 0, st>>>(x, x_layer, bias, bias_layer, out,
+                                                           out_layer, t, d, hd, cap);
+        }
+        return;
+    }
+    for (int l0 = 0; l0 < layers; l0 += 65535) {
+        const int nl = layers - l0 < 65535 ? layers - l0 : 65535;
+        const dim3 grid(flat_blocks((size_t)t * d, 256), nl);
+        const float *xs = x + (size_t)l0 * x_layer;
+        const float *bs = bias ? bias + (size_t)l0 * bias_layer : nullptr;
+        uint16_t *os = out + (size_t)l0 * out_layer;
+        if (transposed) {
+            split_heads_any_kernel<true><<<grid, 256, 0, st>>>(xs, x_layer, bs, bias_layer, os,
+                                                              out_layer, t, d, hd, cap);
+        } else {
+            split_heads_any_kernel<false><<<grid, 256, 0, st>>>(xs, x_layer, bs, bias_layer, os,
+                                                               out_layer, t, d, hd, cap);
         }
     }
 }

@@ -306,6 +306,36 @@ class Gpu:
             self._h, src.data_ptr(), src.numel(), dst.data_ptr(), dst.numel(), kv_heads,
             head_dim, old_cap, new_cap, live, int(bool(transposed))))
 
+    # ---- Whisper cross-attention cache ----------------------------------------------
+
+    def split_heads_f16_at(self, x, x_off, bias, t, heads, head_dim, cap=None,
+                           transposed=False) -> torch.Tensor:
+        """`split_heads_f16_at` / `split_heads_t_f16_at` (device.rs:5636-5665):
+        `bias` is None or (buffer, offset). Returns a zeroed f16 cache of
+        capacity `cap` (t when not given) with the block in it."""
+        cap = t if cap is None else cap
+        out = self.zeros_f16(heads * cap * head_dim)
+        b, boff = (None, 0) if bias is None else bias
+        _check(self._lib.llmtie_split_heads_f16_at(
+            self._h, x.data_ptr(), x.numel(), x_off, _ptr(b), 0 if b is None else b.numel(), boff,
+            out.data_ptr(), out.numel(), t, heads, head_dim, cap, int(bool(transposed))))
+        return out
+
+    def split_heads_t_f16_at(self, x, x_off, bias, t, heads, head_dim, cap=None) -> torch.Tensor:
+        return self.split_heads_f16_at(x, x_off, bias, t, heads, head_dim, cap, transposed=True)
+
+    def cross_kv_build(self, k_all, v_all, v_bias, layers, t, heads, head_dim, cap):
+        """Every decoder layer's cross-attention caches in two launches (see
+        include/llmtie_b200.h). Returns (k, v): f16 [layers][heads][cap][hd]
+        and [layers][heads][hd][cap]."""
+        n = layers * heads * cap * head_dim
+        k, v = self.zeros_f16(n), self.zeros_f16(n)
+        _check(self._lib.llmtie_cross_kv_build(
+            self._h, k_all.data_ptr(), k_all.numel(), v_all.data_ptr(), v_all.numel(),
+            _ptr(v_bias), 0 if v_bias is None else v_bias.numel(), k.data_ptr(), k.numel(),
+            v.data_ptr(), v.numel(), layers, t, heads, head_dim, cap))
+        return k, v
+
     # ---- prefill / encoder --------------------------------------------------------
 
     def supports_flash(self, head_dim, heads, kv_heads) -> bool:
