@@ -104,6 +104,15 @@ llmtie_status llmtie_round_f16(llmtie_gpu *g, const float *src, uint16_t *dst, s
  * want = min(max(next_pow2(past + n + (n > 1 ? 256 : 0)), 256),
  *            max(max_positions, past + n)). */
 size_t llmtie_kv_want_capacity(size_t cap, size_t past, size_t n, size_t max_positions);
+/* Prefix::shared_with and the cut complete_in makes with it
+ * (crates/llmtie-chat/src/generate.rs:264-272, :139-141): how many leading
+ * tokens of `ids` a cache that holds the tokens `held` can keep, never all of
+ * `ids` (the last token is always run, for its logits). The cache is then
+ * truncated to that length - Cache::truncate, chat/model.rs:259-261, only
+ * lowers the live length, nothing is zeroed - and the prompt prefilled from
+ * there with past = the returned value. Host only. */
+size_t llmtie_kv_shared_prefix(const uint32_t *held, size_t held_len, const uint32_t *ids,
+                               size_t ids_len);
 /* zeros_f16(want * kv_dim) twice (chat/model.rs:722-731): zeroed K
  * [kv_heads][cap][hd] and V [kv_heads][hd][cap]. cap must be even. */
 llmtie_status llmtie_kv_alloc_f16(llmtie_gpu *g, size_t kv_heads, size_t head_dim,
@@ -158,7 +167,26 @@ llmtie_status llmtie_cross_kv_build(llmtie_gpu *g, const float *k_all, size_t k_
                                     uint16_t *v_out, size_t v_out_len, size_t layers, size_t t,
                                     size_t heads, size_t head_dim, size_t cap);
 
+/* Gpu::split_heads / split_heads_t (device.rs:5573-5598, kernels.rs:5002-5075:
+ * the f32 twins of the above), as crates/llmtie-cosy/src/flow.rs:
+ * 560-566 lays out the keys and values of its non-causal attention for
+ * llmtie_flash_attn: x f32 [t][heads*head_dim] at x_off -> f32 [heads][cap]
+ * [head_dim] or, transposed, [heads][head_dim][cap]; out zeroed by the caller. */
+llmtie_status llmtie_split_heads(llmtie_gpu *g, const float *x, size_t x_len, size_t x_off,
+                                 float *out, size_t out_len, size_t t, size_t heads,
+                                 size_t head_dim, size_t cap, int32_t transposed);
+
 /* ---- RoPE ----------------------------------------------------------------- */
+
+/* Gpu::rope_gptj (device.rs:4853-4873, kernels.rs:5583-5613; the kernel
+ * itself :5598): GPT-J style
+ * partial rotary embedding in place on x f32 [positions][dim]. Only the first
+ * rot_dim of each row turns, element 2j pairs with 2j+1, angle = position *
+ * inv_freq[j] with the frequencies from a buffer of rot_dim/2, fast sine and
+ * cosine as the reference's kernel. The CosyVoice flow model's q and k rows
+ * go through it before llmtie_flash_attn (crates/llmtie-cosy/src/flow.rs:545-553). */
+llmtie_status llmtie_rope_gptj(llmtie_gpu *g, float *x, size_t x_len, const float *inv_freq,
+                               size_t inv_len, size_t positions, size_t dim, size_t rot_dim);
 
 /* Gpu::rope / rope_scaled (device.rs:5410-5471): NeoX/halves RoPE in place on
  * x[off .. off + t*heads*head_dim]; freq_div is NULL or head_dim/2 floats. */

@@ -643,3 +643,22 @@ void orc_split_heads_f16(const float *x, const float *bias, uint16_t *out,
         out[at] = orc_f32_to_f16(v);
     }
 }
+
+/* crates/llmtie-cuda/src/kernels.rs:5598-5613 (rope_gptj): partial,
+ * interleaved rotary embedding in place; the reference's kernel takes the
+ * fast sine and cosine, this takes libm's. */
+void orc_rope_gptj(float *x, const float *inv_freq, size_t positions,
+                   size_t dim, size_t rot_dim)
+{
+    const size_t pairs = rot_dim / 2;
+    for (size_t pos = 0; pos < positions; pos++) {
+        for (size_t j = 0; j < pairs; j++) {
+            const float ang = (float)pos * inv_freq[j];
+            const float c = cosf(ang), s = sinf(ang);
+            float *at = x + pos * dim + 2 * j;
+            const float a = at[0], b = at[1];
+            at[0] = a * c - b * s;
+            at[1] = b * c + a * s;
+        }
+    }
+}

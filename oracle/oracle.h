@@ -141,6 +141,11 @@ int orc_decode_fast(const float *q, const uint16_t *k, const uint16_t *v,
 
 int orc_max_threads(void);
 
+/* crates/llmtie-cuda/src/kernels.rs:5598-5613: GPT-J style rotary embedding
+ * over the interleaved pairs of the first rot_dim of each dim-wide row. */
+void orc_rope_gptj(float *x, const float *inv_freq, size_t positions,
+                   size_t dim, size_t rot_dim);
+
 /* crates/llmtie-cuda/src/kernels.rs:5089-5139: x f32 [t][heads*hd] (+ bias
  * row or NULL) rounded to f16 into [heads][cap][hd] or, transposed,
  * [heads][hd][cap]; positions past t are not written. */

@@ -60,6 +60,7 @@ def lib() -> C.CDLL:
         L.orc_decode_fast.restype = i32
         L.orc_decode_fast.argtypes = [vp, vp, vp, sz, sz, sz, sz, sz, f32, i32, vp, i32]
         L.orc_max_threads.restype = i32
+        L.orc_rope_gptj.argtypes = [vp, vp, sz, sz, sz]
         L.orc_split_heads_f16.argtypes = [vp, vp, vp, sz, sz, sz, sz, i32]
         _lib = L
     return _lib
@@ -212,6 +213,13 @@ def split_heads_f16(x, bias, t, heads, hd, cap=None, transposed=False) -> np.nda
     out = np.zeros(heads * cap * hd, dtype=np.uint16)
     lib().orc_split_heads_f16(_p(x), None if b is None else _p(b), _p(out), t, heads, hd, cap,
                               int(transposed))
+    return out
+
+
+def rope_gptj(x, inv_freq, positions, dim, rot_dim) -> np.ndarray:
+    out = _f32(x).reshape(-1).copy()
+    f = _f32(inv_freq).reshape(-1)
+    lib().orc_rope_gptj(_p(out), _p(f), positions, dim, rot_dim)
     return out
 
 

@@ -24,4 +24,4 @@ from .gpu import (  # noqa: F401
     UnsupportedAttention,
     decode_cut,
 )
-from .cache import KvCache, want_capacity  # noqa: F401
+from .cache import KvCache, Prefix, shared_prefix, want_capacity  # noqa: F401

@@ -35,6 +35,7 @@ PROTOTYPES = {
     "llmtie_download": (i32, [vp, vp, vp, sz]),
     "llmtie_round_f16": (i32, [vp, vp, vp, sz]),
     "llmtie_kv_want_capacity": (sz, [sz, sz, sz, sz]),
+    "llmtie_kv_shared_prefix": (sz, [C.POINTER(C.c_uint32), sz, C.POINTER(C.c_uint32), sz]),
     "llmtie_kv_alloc_f16": (i32, [vp, sz, sz, sz, pvp, pvp]),
     "llmtie_cache_grow_f16": (i32, [vp, vp, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
     "llmtie_cache_grow": (i32, [vp, vp, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
@@ -42,6 +43,8 @@ PROTOTYPES = {
     "llmtie_cache_append": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
     "llmtie_split_heads_f16_at": (i32, [vp, vp, sz, sz, vp, sz, sz, vp, sz, sz, sz, sz, sz, i32]),
     "llmtie_cross_kv_build": (i32, [vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz]),
+    "llmtie_split_heads": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, sz, sz, i32]),
+    "llmtie_rope_gptj": (i32, [vp, vp, sz, vp, sz, sz, sz, sz]),
     "llmtie_rope_scaled": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, f32, sz]),
     "llmtie_rope_cache_f16": (
         i32,

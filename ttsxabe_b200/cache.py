@@ -57,7 +57,62 @@ class KvCache:
         self.len += n
 
     def truncate(self, length: int) -> None:
+        """Forgets every position from `length` on. Nothing is zeroed: attention
+        reads only the live positions, and the next prefill writes its own keys
+        and values from `length` before any attention reads them."""
         self.len = min(self.len, length)
 
     def clear(self) -> None:
         self.len = 0
+
+
+def shared_prefix(held, ids) -> int:
+    """Leading tokens of `ids` that a cache holding `held` can keep (never all
+    of `ids`: the last token is always run)."""
+    import ctypes as C
+
+    h = (C.c_uint32 * len(held))(*held)
+    i = (C.c_uint32 * len(ids))(*ids)
+    return int(_lib.load().llmtie_kv_shared_prefix(h, len(held), i, len(ids)))
+
+
+class Prefix:
+    """`Prefix` (crates/llmtie-chat/src/generate.rs:258-283): the caches of one
+    conversation kept from one completion to the next, with exactly the tokens
+    they hold. A turn's prompt shares its opening with the last one, so only
+    the tokens from the first that differs are prefilled."""
+
+    def __init__(self, caches) -> None:
+        self.caches = list(caches)          # one KvCache a layer
+        self.held: list[int] = []
+
+    def __len__(self) -> int:
+        return len(self.held)
+
+    def shared_with(self, ids) -> int:
+        n = 0
+        for a, b in zip(self.held, ids):
+            if a != b:
+                break
+            n += 1
+        return n
+
+    def keep(self, ids) -> int:
+        """Cuts the caches back to what they share with the prompt `ids`
+        (generate.rs:139-141) and returns that length: the prompt is prefilled
+        from there, with `past` = the returned value."""
+        reused = shared_prefix(self.held, ids)
+        for c in self.caches:
+            c.truncate(reused)
+        del self.held[reused:]
+        return reused
+
+    def extend(self, ids) -> None:
+        """Records tokens the caches now hold (after a prefill or a decoded step)."""
+        self.held.extend(int(x) for x in ids)
+
+    def reset(self) -> None:
+        """What complete_after does when a completion failed half way."""
+        for c in self.caches:
+            c.clear()
+        self.held.clear()

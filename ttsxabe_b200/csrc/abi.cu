@@ -313,6 +313,15 @@ extern "C" size_t llmtie_kv_want_capacity(size_t cap, size_t past, size_t n,
     return want;
 }
 
+extern "C" size_t llmtie_kv_shared_prefix(const uint32_t *held, size_t held_len,
+                                          const uint32_t *ids, size_t ids_len)
+{
+    if (!held || !ids || ids_len == 0) return 0;
+    size_t n = 0;
+    while (n < held_len && n < ids_len && held[n] == ids[n]) n++;
+    return std::min(n, ids_len - 1);
+}
+
 extern "C" llmtie_status llmtie_kv_alloc_f16(llmtie_gpu *g, size_t kv_heads, size_t head_dim,
                                              size_t cap, uint16_t **k, uint16_t **v)
 {
@@ -502,7 +511,61 @@ extern "C" llmtie_status llmtie_cross_kv_build(llmtie_gpu *g, const float *k_all
                       t, heads, head_dim, cap, true);
 }
 
+extern "C" llmtie_status llmtie_split_heads(llmtie_gpu *g, const float *x, size_t x_len,
+                                            size_t x_off, float *out, size_t out_len, size_t t,
+                                            size_t heads, size_t head_dim, size_t cap,
+                                            int32_t transposed)
+{
+    NEED_HANDLE(g);
+    const size_t n = t * heads * head_dim;
+    if (n == 0) return LLMTIE_OK;
+    if (cap < t) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", t, cap);
+    }
+    if (x_off + n > x_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           x_off + n, x_len);
+    }
+    if (heads * cap * head_dim > out_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           heads * cap * head_dim, out_len);
+    }
+    if (!fits_i32(t) || !fits_i32(heads * head_dim) || !fits_i32(cap)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "cache geometry does not fit 32 bits");
+    }
+    LaunchScope ls(g, transposed ? "split_heads_t" : "split_heads");
+    launch_split_heads_f32(g->stream, x + x_off, out, (int)t, (int)heads, (int)head_dim, (int)cap,
+                           transposed != 0);
+    return ls.done();
+}
+
 // ---- RoPE ---------------------------------------------------------------------
+
+extern "C" llmtie_status llmtie_rope_gptj(llmtie_gpu *g, float *x, size_t x_len,
+                                          const float *inv_freq, size_t inv_len,
+                                          size_t positions, size_t dim, size_t rot_dim)
+{
+    NEED_HANDLE(g);
+    if (rot_dim % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_ODD_HEAD_DIM, "a rotary head of odd width %zu", rot_dim);
+    }
+    if (rot_dim > dim || positions * dim > x_len) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           rot_dim > dim ? rot_dim : positions * dim, rot_dim > dim ? dim : x_len);
+    }
+    if (inv_len < rot_dim / 2) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           rot_dim / 2, inv_len);
+    }
+    if (!fits_i32(positions) || !fits_i32(dim)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "rope geometry does not fit 32 bits");
+    }
+    if (positions * rot_dim == 0) return LLMTIE_OK;
+    LaunchScope ls(g, "rope_gptj");
+    launch_rope_gptj(g->stream, x, inv_freq, (int)positions, (int)dim, (int)rot_dim);
+    return ls.done();
+}
 
 extern "C" llmtie_status llmtie_rope_scaled(llmtie_gpu *g, float *x, size_t x_len, size_t off,
                                             const float *freq_div, size_t t, size_t heads,

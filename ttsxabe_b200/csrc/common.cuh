@@ -119,6 +119,10 @@ void launch_cache_append(cudaStream_t st, const float *src, long long src_off, v
 void launch_cache_grow(cudaStream_t st, const void *src, void *dst, long long rows,
                        long long len, long long src_stride, long long dst_stride, int esize);
 void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n);
+void launch_rope_gptj(cudaStream_t st, float *x, const float *inv_freq, int positions, int dim,
+                      int rot_dim);
+void launch_split_heads_f32(cudaStream_t st, const float *x, float *out, int t, int heads, int hd,
+                            int cap, bool transposed);
 // `layers` blocks of x f32 [t][heads*hd], x_layer elements apart (+ bias rows
 // bias_layer apart, or null), into f16 caches out_layer apart: keys
 // [heads][cap][hd] or, transposed, values [heads][hd][cap]. Positions past t

@@ -111,6 +111,39 @@ __global__ void rope_kernel(float *__restrict__ x, long long off,
     }
 }
 
+// GPT-J style partial rotary embedding (crates/llmtie-cuda/src/kernels.rs:
+// 5598-5613): only the first rot_dim of each dim-wide row turns, element 2j
+// pairs with 2j + 1, the frequencies come from a buffer and the sine and
+// cosine are the fast intrinsics, as the reference's are. A thread takes one
+// pair as one 8-byte access (or two 4-byte ones where the row is not aligned).
+__global__ void rope_gptj_kernel(float *__restrict__ x, const float *__restrict__ inv_freq,
+                                 int positions, int dim, int rot_dim, int wide)
+{
+    const int pairs = rot_dim >> 1;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)positions * pairs) return;
+    const int pos = (int)(i / pairs), j = (int)(i % pairs);
+    const float ang = (float)pos * inv_freq[j];
+    const float c = __cosf(ang), s = __sinf(ang);
+    float *at = x + (size_t)pos * dim + 2 * j;
+    float a, b;
+    if (wide) {
+        const float2 v = *(const float2 *)at;
+        a = v.x;
+        b = v.y;
+    } else {
+        a = at[0];
+        b = at[1];
+    }
+    const float lo = a * c - b * s, hi = b * c + a * s;
+    if (wide) {
+        *(float2 *)at = make_float2(lo, hi);
+    } else {
+        at[0] = lo;
+        at[1] = hi;
+    }
+}
+
 // The decode step's RoPE and cache write for a batch of sequences (one is a
 // batch of one): sequence blockIdx.y rotates its q row in place, writes its
 // rotated k row into its f16 K cache and its v row into its transposed f16 V
@@ -378,10 +411,10 @@ split_heads_kernel(const float *__restrict__ x, long long x_layer, const float *
 }
 
 // The same for shapes the wide kernel does not take: one element a thread.
-template <bool T>
+template <bool T, typename O = uint16_t>
 __global__ void split_heads_any_kernel(const float *__restrict__ x, long long x_layer,
                                        const float *__restrict__ bias, long long bias_layer,
-                                       uint16_t *__restrict__ out, long long out_layer, int t, int d,
+                                       O *__restrict__ out, long long out_layer, int t, int d,
                                        int hd, int cap)
 {
     x += (size_t)blockIdx.y * x_layer;
@@ -391,10 +424,16 @@ __global__ void split_heads_any_kernel(const float *__restrict__ x, long long x_
     const int ti = (int)(i / d), c = (int)(i % d);
     float v = x[i];
     if (bias) v = __fadd_rn(v, bias[(size_t)blockIdx.y * bias_layer + c]);
-    if constexpr (T) {
-        out[(size_t)c * cap + ti] = f16_bits(v);
+    O w;
+    if constexpr (sizeof(O) == 2) {
+        w = f16_bits(v);
     } else {
-        out[((size_t)(c / hd) * cap + ti) * hd + c % hd] = f16_bits(v);
+        w = v;
+    }
+    if constexpr (T) {
+        out[(size_t)c * cap + ti] = w;
+    } else {
+        out[((size_t)(c / hd) * cap + ti) * hd + c % hd] = w;
     }
 }
 
@@ -591,6 +630,7 @@ inline unsigned flat_blocks(size_t n, int threads)
 
 // names as the reference registers its kernels (device.rs:604-733)
 const KernelReg reg_rope("rope", (const void *)rope_kernel<4>);
+const KernelReg reg_rope_gptj("rope_gptj", (const void *)rope_gptj_kernel);
 const KernelReg reg_rope_cache("rope_cache_f16", (const void *)rope_cache_batched_kernel);
 const KernelReg reg_append("cache_append_f16", (const void *)cache_append_kernel<uint16_t, 4>);
 const KernelReg reg_append_t("cache_append_t_f16", (const void *)cache_append_t_kernel<uint16_t>);
@@ -716,6 +756,31 @@ void launch_split_heads(cudaStream_t st, const float *x, long long x_layer, cons
                                                                out_layer, t, d, hd, cap);
         }
     }
+}
+
+void launch_split_heads_f32(cudaStream_t st, const float *x, float *out, int t, int heads, int hd,
+                            int cap, bool transposed)
+{
+    const int d = heads * hd;
+    if ((size_t)t * d == 0) return;
+    const dim3 grid(flat_blocks((size_t)t * d, 256), 1);
+    if (transposed) {
+        split_heads_any_kernel<true, float><<<grid, 256, 0, st>>>(x, 0, nullptr, 0, out, 0, t, d, hd,
+                                                                 cap);
+    } else {
+        split_heads_any_kernel<false, float><<<grid, 256, 0, st>>>(x, 0, nullptr, 0, out, 0, t, d,
+                                                                  hd, cap);
+    }
+}
+
+void launch_rope_gptj(cudaStream_t st, float *x, const float *inv_freq, int positions, int dim,
+                      int rot_dim)
+{
+    const size_t n = (size_t)positions * (rot_dim / 2);
+    if (n == 0) return;
+    const int wide = dim % 2 == 0 && ((uintptr_t)x & 7u) == 0;
+    rope_gptj_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(x, inv_freq, positions, dim, rot_dim,
+                                                         wide);
 }
 
 void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n)

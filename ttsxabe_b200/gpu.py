@@ -257,6 +257,24 @@ class Gpu:
         _check(self._lib.llmtie_rope_scaled(self._h, x.data_ptr(), x.numel(), off,
                                             _ptr(freq_div), t, heads, head_dim, theta, first))
 
+    def rope_gptj(self, x, inv_freq, positions, dim, rot_dim) -> None:
+        """`rope_gptj` (device.rs:4853-4873): partial, interleaved, in place."""
+        _check(self._lib.llmtie_rope_gptj(self._h, x.data_ptr(), x.numel(), inv_freq.data_ptr(),
+                                          inv_freq.numel(), positions, dim, rot_dim))
+
+    def split_heads(self, x, t, heads, head_dim, x_off=0, cap=None, transposed=False):
+        """`split_heads` / `split_heads_t`: f32 [t][heads*hd] -> [heads][cap][hd]
+        (or transposed [heads][hd][cap]), cap = t unless given."""
+        cap = t if cap is None else cap
+        out = self.zeros(heads * cap * head_dim)
+        _check(self._lib.llmtie_split_heads(self._h, x.data_ptr(), x.numel(), x_off,
+                                            out.data_ptr(), out.numel(), t, heads, head_dim, cap,
+                                            int(bool(transposed))))
+        return out
+
+    def split_heads_t(self, x, t, heads, head_dim, x_off=0, cap=None):
+        return self.split_heads(x, t, heads, head_dim, x_off, cap, transposed=True)
+
     def rope_cache_f16(self, proj: Sequence[torch.Tensor], q, k, v, freq_div, heads, kv_heads,
                        head_dim, theta, pos, kc, vc, cap) -> None:
         """q, k, v are (buffer index, element offset) into `proj`."""
