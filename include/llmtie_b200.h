@@ -138,6 +138,23 @@ llmtie_status llmtie_cache_append(llmtie_gpu *g, const float *src, size_t src_le
                                   size_t kv_heads, size_t head_dim, size_t cap,
                                   size_t past, int32_t transposed);
 
+/* ---- the projection in front of the Whisper decoder's self-attention ---------- */
+
+/* Gpu::gemv_qkv_f16 (device.rs:4393-4479, kernels.rs:6876-6913): the three
+ * attention projections of one row a f32 [k] in one launch, each placed where
+ * the attention reads it: w is the three [d][k] f16 weights stacked into
+ * [3d][k]; q = Wq a (+ q_bias) into q f32 [d]; the keys into kc f32 [d/
+ * head_dim][cap][head_dim] at `pos`; the values into the transposed vc f32
+ * [d][cap] at `pos` - the caches llmtie_attn_decode reads. Each bias is f32
+ * [d] or NULL (the keys have none in any Whisper checkpoint). k must be even.
+ * Products accumulate in f32 in a fixed order, so a call is reproducible. */
+llmtie_status llmtie_gemv_qkv_f16(llmtie_gpu *g, const float *a, size_t a_len,
+                                  const uint16_t *w, size_t w_len, const float *q_bias,
+                                  const float *k_bias, const float *v_bias, size_t bias_len,
+                                  size_t k, size_t d, size_t head_dim, size_t cap, size_t pos,
+                                  float *q, size_t q_len, float *kc, size_t kc_len, float *vc,
+                                  size_t vc_len);
+
 /* ---- Whisper cross-attention cache build ------------------------------------- */
 
 /* Gpu::split_heads_f16_at / split_heads_t_f16_at (device.rs:5636-5665, kernels

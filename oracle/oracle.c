@@ -662,3 +662,30 @@ void orc_rope_gptj(float *x, const float *inv_freq, size_t positions,
         }
     }
 }
+
+/* ---- the stacked attention projection ------------------------------------------ */
+
+/* crates/llmtie-cuda/src/kernels.rs:6876-6913 (gemv_qkv_f16): column c of the
+ * stacked [3d][k] f16 weight times the row a, plus its third's bias; q into a
+ * row, k into [d/hd][cap][hd] at pos, v into [d][cap] at pos. The reference
+ * sums per lane in f32; this sums in f64 and rounds once. */
+void orc_gemv_qkv_f16(const float *a, const uint16_t *w, const float *qb,
+                      const float *kb, const float *vb, size_t k, size_t d,
+                      size_t hd, size_t cap, size_t pos, float *q, float *kc,
+                      float *vc)
+{
+    for (size_t col = 0; col < 3 * d; col++) {
+        double acc = 0.0;
+        for (size_t i = 0; i < k; i++) {
+            acc += (double)a[i] * (double)orc_f16_to_f32(w[col * k + i]);
+        }
+        const size_t part = col / d, c = col % d;
+        if (part == 0) {
+            q[c] = (float)acc + (qb ? qb[c] : 0.0f);
+        } else if (part == 1) {
+            kc[((c / hd) * cap + pos) * hd + c % hd] = (float)acc + (kb ? kb[c] : 0.0f);
+        } else {
+            vc[c * cap + pos] = (float)acc + (vb ? vb[c] : 0.0f);
+        }
+    }
+}

@@ -141,6 +141,13 @@ int orc_decode_fast(const float *q, const uint16_t *k, const uint16_t *v,
 
 int orc_max_threads(void);
 
+/* crates/llmtie-cuda/src/kernels.rs:6876-6913: the stacked q/k/v projection of
+ * one row, placed into a row and the two f32 caches at pos (f64 sums). */
+void orc_gemv_qkv_f16(const float *a, const uint16_t *w, const float *qb,
+                      const float *kb, const float *vb, size_t k, size_t d,
+                      size_t hd, size_t cap, size_t pos, float *q, float *kc,
+                      float *vc);
+
 /* crates/llmtie-cuda/src/kernels.rs:5598-5613: GPT-J style rotary embedding
  * over the interleaved pairs of the first rot_dim of each dim-wide row. */
 void orc_rope_gptj(float *x, const float *inv_freq, size_t positions,

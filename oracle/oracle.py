@@ -60,6 +60,7 @@ def lib() -> C.CDLL:
         L.orc_decode_fast.restype = i32
         L.orc_decode_fast.argtypes = [vp, vp, vp, sz, sz, sz, sz, sz, f32, i32, vp, i32]
         L.orc_max_threads.restype = i32
+        L.orc_gemv_qkv_f16.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, vp, vp, vp]
         L.orc_rope_gptj.argtypes = [vp, vp, sz, sz, sz]
         L.orc_split_heads_f16.argtypes = [vp, vp, vp, sz, sz, sz, sz, i32]
         _lib = L
@@ -214,6 +215,16 @@ def split_heads_f16(x, bias, t, heads, hd, cap=None, transposed=False) -> np.nda
     lib().orc_split_heads_f16(_p(x), None if b is None else _p(b), _p(out), t, heads, hd, cap,
                               int(transposed))
     return out
+
+
+def gemv_qkv_f16(a, w, bias, k, d, hd, cap, pos, q, kc, vc) -> None:
+    """Writes q [d], and position pos of kc [d/hd][cap][hd] and vc [d][cap], in place."""
+    a, w = _f32(a).reshape(-1), _u16(w).reshape(-1)
+    bs = [None if b is None else _f32(b).reshape(-1) for b in bias]
+    for x in (q, kc, vc):
+        assert x.dtype == np.float32 and x.flags.c_contiguous
+    lib().orc_gemv_qkv_f16(_p(a), _p(w), *[None if b is None else _p(b) for b in bs], k, d, hd,
+                           cap, pos, _p(q), _p(kc), _p(vc))
 
 
 def rope_gptj(x, inv_freq, positions, dim, rot_dim) -> np.ndarray:

@@ -41,6 +41,8 @@ PROTOTYPES = {
     "llmtie_cache_grow": (i32, [vp, vp, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
     "llmtie_cache_append_f16": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
     "llmtie_cache_append": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, sz, sz, sz, i32]),
+    "llmtie_gemv_qkv_f16": (
+        i32, [vp, vp, sz, vp, sz, vp, vp, vp, sz, sz, sz, sz, sz, sz, vp, sz, vp, sz, vp, sz]),
     "llmtie_split_heads_f16_at": (i32, [vp, vp, sz, sz, vp, sz, sz, vp, sz, sz, sz, sz, sz, i32]),
     "llmtie_cross_kv_build": (i32, [vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz]),
     "llmtie_split_heads": (i32, [vp, vp, sz, sz, vp, sz, sz, sz, sz, sz, i32]),

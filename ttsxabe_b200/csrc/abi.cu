@@ -444,6 +444,64 @@ extern "C" llmtie_status llmtie_cache_append(llmtie_gpu *g, const float *src, si
                        transposed != 0, false);
 }
 
+static llmtie_status misaligned(const char *what, const void *p, size_t align)
+{
+    return llmtie_fail(LLMTIE_ERR_MISALIGNED, "%s starts at %zu, which is not a multiple of %zu",
+                       what, (size_t)(uintptr_t)p, align);
+}
+
+// ---- the projection in front of the Whisper decoder's self-attention -------------
+
+extern "C" llmtie_status llmtie_gemv_qkv_f16(llmtie_gpu *g, const float *a, size_t a_len,
+                                             const uint16_t *w, size_t w_len, const float *q_bias,
+                                             const float *k_bias, const float *v_bias,
+                                             size_t bias_len, size_t k, size_t d, size_t head_dim,
+                                             size_t cap, size_t pos, float *q, size_t q_len,
+                                             float *kc, size_t kc_len, float *vc, size_t vc_len)
+{
+    NEED_HANDLE(g);
+    if (k % 2 != 0) {
+        return llmtie_fail(LLMTIE_ERR_RAGGED_BLOCK,
+                           "a contraction of %zu does not divide into pairs", k);
+    }
+    if (head_dim == 0 || d % head_dim != 0) {
+        return llmtie_fail(LLMTIE_ERR_RAGGED_BLOCK, "a row of %zu does not divide into blocks of %zu",
+                           d, head_dim);
+    }
+    if (pos >= cap) {
+        return llmtie_fail(LLMTIE_ERR_CACHE_OVERRUN,
+                           "appending at %zu to a cache with room for %zu", pos + 1, cap);
+    }
+    if (a_len < k) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", k, a_len);
+    }
+    if (w_len < 3 * d * k) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           3 * d * k, w_len);
+    }
+    if (q_len < d) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", d, q_len);
+    }
+    if (kc_len < d * cap || vc_len < d * cap) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", d * cap,
+                           std::min(kc_len, vc_len));
+    }
+    if ((q_bias || k_bias || v_bias) && bias_len < d) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu", d,
+                           bias_len);
+    }
+    if (((uintptr_t)w & 3u) != 0) return misaligned("the stacked weight", w, 4);
+    if (!fits_i32(k) || !fits_i32(3 * d) || !fits_i32(cap) || k * sizeof(float) > 200 * 1024) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "projection geometry out of range");
+    }
+    if (d == 0) return LLMTIE_OK;
+    LaunchScope ls(g, "gemv_qkv_f16");
+    const cudaError_t e = launch_gemv_qkv_f16(g->stream, a, w, q_bias, k_bias, v_bias, (int)k, (int)d,
+                                              (int)head_dim, (int)cap, (int)pos, q, kc, vc);
+    if (e != cudaSuccess) return driver_fail("gemv_qkv_f16", e);
+    return ls.done();
+}
+
 // ---- Whisper cross-attention cache build ----------------------------------------
 
 static llmtie_status split_impl(llmtie_gpu *g, const float *x, size_t x_len, size_t x_off,
@@ -716,11 +774,6 @@ static llmtie_status unsupported(size_t hd, size_t heads, size_t kv)
                        hd, heads, kv);
 }
 
-static llmtie_status misaligned(const char *what, const void *p, size_t align)
-{
-    return llmtie_fail(LLMTIE_ERR_MISALIGNED, "%s starts at %zu, which is not a multiple of %zu",
-                       what, (size_t)(uintptr_t)p, align);
-}
 
 // Whether a prefill takes the tensor-memory kernel (aligned f16 caches at
 // head_dim 128) or the general one. LLMTIE_B200_NO_TC forces the general one.

@@ -281,6 +281,11 @@ void launch_lse_merge_wait(cudaStream_t st, const float *gather, const unsigned 
                            const unsigned *step, int world, int rows, int hd, float *out,
                            int *status, long long wait_cycles);
 
+// gemv_qkv.cu: the stacked attention projection of one row into q and the f32 caches.
+cudaError_t launch_gemv_qkv_f16(cudaStream_t st, const float *a, const uint16_t *w, const float *qb,
+                                const float *kb, const float *vb, int k, int d, int hd, int cap,
+                                int pos, float *q, float *kc, float *vc);
+
 // prefill_mma.cu
 #define LLMTIE_PREFILL_MAX_SEQ 32
 struct PrefillSeq {

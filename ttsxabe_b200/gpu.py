@@ -324,6 +324,18 @@ class Gpu:
             self._h, src.data_ptr(), src.numel(), dst.data_ptr(), dst.numel(), kv_heads,
             head_dim, old_cap, new_cap, live, int(bool(transposed))))
 
+    # ---- the projection in front of decode attention ---------------------------------
+
+    def gemv_qkv_f16(self, a, w, bias, k, d, head_dim, cap, pos, q, kc, vc) -> None:
+        """`gemv_qkv_f16` (device.rs:4393-4479): `bias` is three f32 [d] tensors
+        or Nones, for q, k and v."""
+        bq, bk, bv = bias
+        blen = min([b.numel() for b in bias if b is not None], default=0)
+        _check(self._lib.llmtie_gemv_qkv_f16(
+            self._h, a.data_ptr(), a.numel(), w.data_ptr(), w.numel(), _ptr(bq), _ptr(bk), _ptr(bv),
+            blen, k, d, head_dim, cap, pos, q.data_ptr(), q.numel(), kc.data_ptr(), kc.numel(),
+            vc.data_ptr(), vc.numel()))
+
     # ---- Whisper cross-attention cache ----------------------------------------------
 
     def split_heads_f16_at(self, x, x_off, bias, t, heads, head_dim, cap=None,
