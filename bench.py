@@ -424,6 +424,9 @@ def decode128k(args, world, rank, local):
         "exchange": {"none": "none", "all-gather": "nccl all-gather",
                      "peer-push": "peer-memory push fused into the decode kernel, merge in a "
                                   "second waiting kernel",
+                     "peer-pairs": "peer-memory push with a flag per (sequence, KV head) pair, "
+                                   "merged by a kernel launched as the decode kernel's "
+                                   "programmatic dependent",
                      "peer-fused": "peer-memory push, wait and merge all fused into the decode "
                                    "kernel"}[sd.exchange],
         "exchange_max_abs_vs_allgather": exchange_err,
@@ -857,7 +860,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline legs")
     ap.add_argument("--no-prefill", action="store_true",
                     help="leave the prefill object out of the decode line")
-    ap.add_argument("--exchange", default="push", choices=["push", "fused", "nccl"],
+    ap.add_argument("--exchange", default="push", choices=["push", "pairs", "fused", "nccl"],
                     help="how the ranks exchange their triples: everything in the decode "
                          "kernel over peer memory (fused), the push in the kernel and the merge "
                          "in a second waiting kernel (push), or an NCCL all-gather (nccl)")

@@ -425,6 +425,33 @@ llmtie_status llmtie_decode_batched_fused(llmtie_gpu *g, const float *q, size_t 
                                           const llmtie_exchange *xch,
                                           uint32_t *const *pair_flags, float *out,
                                           size_t out_len);
+/* The sharded step in two kernels that overlap (no counterpart in the
+ * reference): llmtie_decode_batched_signal is llmtie_decode_batched_push with a
+ * flag per (sequence, KV head) pair instead of one per rank - the block that
+ * finishes a pair stores its triple into every rank's gather buffer and raises
+ * [pair][rank] of every rank's pair_flags (HOST array of `world` device
+ * pointers, each [batch*kv_heads][world] words, zero before the first step).
+ * llmtie_lse_merge_pairs, enqueued right after it on the same stream, is
+ * launched as a programmatic dependent: its blocks are resident while the
+ * decode kernel still streams, each waits (bounded, as above) for the `world`
+ * flags of its row's pair and merges the row at once, so the merge's launch
+ * and every pair's exchange but the last are off the step's critical path.
+ * pair_flags there is THIS rank's array; merge_step is a device uint32[2] of
+ * this rank's own, zero before the first step (the merge counts its own
+ * steps); rows = batch*heads, rows_per_pair = heads/kv_heads. gather and step
+ * as for the push entry; xch->flags is unused. */
+llmtie_status llmtie_decode_batched_signal(llmtie_gpu *g, const float *q, size_t q_len,
+                                           const uint16_t *const *k_ptrs,
+                                           const uint16_t *const *v_ptrs, const int32_t *tk,
+                                           const int32_t *cap, size_t batch, size_t heads,
+                                           size_t kv_heads, size_t head_dim, float scale,
+                                           int32_t scale_q, llmtie_decode_scratch *scratch,
+                                           const llmtie_exchange *xch,
+                                           uint32_t *const *pair_flags);
+llmtie_status llmtie_lse_merge_pairs(llmtie_gpu *g, const llmtie_exchange *xch,
+                                     const uint32_t *pair_flags, uint32_t *merge_step, size_t rows,
+                                     size_t rows_per_pair, size_t head_dim, float *out,
+                                     size_t out_len);
 /* AsrModel::attend (crates/llmtie-asr/src/model.rs:573-641) fused: n query
  * rows (q f32 [n][heads*hd], scale applied to q) over f16 cross caches
  * K [heads][cap][hd], V [heads][hd][cap] with tk live keys, non-causal;

@@ -199,13 +199,17 @@ def test_partial_triples_merge_to_the_whole(gpu):
     assert_close_to("merged partials", want, merged, 2e-5)
 
 
-def test_peer_push_exchange_on_one_device(gpu):
+@pytest.mark.parametrize("mode", ["push", "pairs"])
+def test_peer_push_exchange_on_one_device(gpu, mode):
     """The fused multi-GPU exchange, with both "ranks" on one device: each rank
     decodes its slice of the keys and pushes its triples into every rank's
     gather buffer (here: two buffers in the same memory), then each rank's
     waiting merge runs. The kernels are enqueued one after another on one
     stream, so every flag a merge waits for was raised by a kernel that has
-    already finished. Two steps, to use both gather buffers."""
+    already finished (or, for the merge launched as a programmatic dependent
+    in "pairs" mode, by a kernel all of whose blocks have at least started).
+    "push" raises one flag a rank, "pairs" one a (sequence, KV head) pair. Two
+    steps, to use both gather buffers."""
     import torch
 
     from ttsxabe_b200 import DecodeScratch, Exchange
@@ -223,8 +227,11 @@ def test_peer_push_exchange_on_one_device(gpu):
                    for _ in range(world)]
         flags = [torch.zeros(64, dtype=torch.int32, device=gpu.device) for _ in range(world)]
         steps = [torch.zeros(1, dtype=torch.int32, device=gpu.device) for _ in range(world)]
+        msteps = [torch.zeros(2, dtype=torch.int32, device=gpu.device) for _ in range(world)]
+        pflags = [torch.zeros(batch * kv * world, dtype=torch.int32, device=gpu.device)
+                  for _ in range(world)]
     xchs = [Exchange(world, r, [g_.data_ptr() for g_ in gathers], [f.data_ptr() for f in flags],
-                     steps[r].data_ptr()) for r in range(world)]
+                     steps[r].data_ptr(), [f.data_ptr() for f in pflags]) for r in range(world)]
     caches = []
     for r in range(world):
         t0 = sum(per[:r])
@@ -242,10 +249,15 @@ def test_peer_push_exchange_on_one_device(gpu):
         q = normal_f16(rng, batch * heads * hd)
         dq = gpu.upload(q)
         for r in range(world):
-            gpu.decode_batched_push(dq, caches[r][0], caches[r][1], [per[r]] * batch,
-                                    [caps[r]] * batch, heads, kv, hd, scale, False, scratch[r],
-                                    xchs[r])
-        outs = [gpu.download(gpu.lse_merge_wait(xchs[r], rows, hd)) for r in range(world)]
+            push = gpu.decode_batched_push if mode == "push" else gpu.decode_batched_signal
+            push(dq, caches[r][0], caches[r][1], [per[r]] * batch, [caps[r]] * batch, heads, kv, hd,
+                 scale, False, scratch[r], xchs[r])
+        if mode == "push":
+            outs = [gpu.download(gpu.lse_merge_wait(xchs[r], rows, hd)) for r in range(world)]
+        else:
+            outs = [gpu.download(gpu.lse_merge_pairs(xchs[r], msteps[r], rows, heads // kv, hd))
+                    for r in range(world)]
+            assert all(int(m[0].item()) == step + 1 and int(m[1].item()) == 0 for m in msteps)
         assert np.array_equal(outs[0], outs[1]), "both ranks must merge to the same context"
         for b in range(batch):
             kc = np.ascontiguousarray(kfull[b])

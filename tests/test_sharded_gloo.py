@@ -86,3 +86,43 @@ def test_two_rank_sharded_decode_equals_one_rank(tmp_path):
     a = np.load(tmp_path / "out0.npy")
     b = np.load(tmp_path / "out1.npy")
     assert np.array_equal(a, b), "both ranks must hold the same merged context"
+
+
+def _leaver(rank, world, port, tmp):
+    """Rank 1 takes part in the first step and then leaves between steps (its
+    process ends with nothing of its own in flight); rank 0 goes into the next
+    step's exchange alone and must get an error, not a hang."""
+    import datetime
+
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=4))
+    from ttsxabe_b200.sharded import ShardedDecode
+
+    heads, hd, batch = 2, 4, 1
+    part = torch.arange(batch * heads * (hd + 2), dtype=torch.float32)
+    sd = ShardedDecode(heads, hd, None, lambda q, partial: part.clone(),
+                       lambda g, parts, rows: g.reshape(parts, rows, hd + 2)[0, :, :hd].reshape(-1))
+    sd.decode(torch.zeros(batch * heads * hd))        # a step with both ranks: fine
+    if rank == 1:
+        return                                        # leaves between steps
+    try:
+        sd.decode(torch.zeros(batch * heads * hd))
+        verdict = "returned"
+    except Exception as e:                            # the collective's own timeout or a reset
+        verdict = "raised " + type(e).__name__
+    with open(os.path.join(tmp, "verdict.txt"), "w") as f:
+        f.write(verdict)
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_next_exchange_with_an_error(tmp_path):
+    """Failure on the host, no device involved: the surviving rank's next
+    all-gather ends with an error within the process group's timeout (four
+    seconds here) instead of waiting for ever."""
+    world = 2
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_leaver, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    verdict = (tmp_path / "verdict.txt").read_text()
+    assert verdict.startswith("raised"), verdict

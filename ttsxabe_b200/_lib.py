@@ -82,6 +82,9 @@ PROTOTYPES = {
     "llmtie_decode_batched_fused": (
         i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp, pvp, vp, sz]),
     "llmtie_lse_merge_wait": (i32, [vp, vp, sz, sz, vp, sz]),
+    "llmtie_decode_batched_signal": (
+        i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp, pvp]),
+    "llmtie_lse_merge_pairs": (i32, [vp, vp, vp, vp, sz, sz, sz, vp, sz]),
     "llmtie_cross_attn": (
         i32, [vp, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, sz, f32, vp, vp, sz]),
     "llmtie_prefill_varlen": (

@@ -1077,6 +1077,7 @@ static void decode_plan(llmtie_gpu *g, DecodeParams &p, int hd)
 struct FusedMerge {
     uint32_t *const *pair_flags;
     float *out;
+    int mode;   // 1: merge inside the decode kernel; 2: raise the pair flags only
 };
 
 static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams &p, int hd,
@@ -1179,7 +1180,7 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
             sp.xch_pairs = (int)pairs;
             sp.xch_rank_stride = (long long)p.nseq * p.out_seq;
             if (fused) {
-                sp.xch_fused = 1;
+                sp.xch_fused = fused->mode;
                 for (int r = 0; r < xch->world; r++) sp.xch_pflags[r] = fused->pair_flags[r];
                 sp.xch_out = fused->out;
                 sp.xch_status = g->timeout_site;
@@ -1400,7 +1401,7 @@ static llmtie_status decode_batched_impl(llmtie_gpu *g, const float *q, size_t q
         // (a world of one rank is a valid fused exchange: the rank merges its own triple)
         if (xch->world < (fused ? 1 : 2) || xch->world > LLMTIE_MAX_RANKS || xch->rank < 0 ||
             xch->rank >= xch->world || !xch->gather || !xch->step ||
-            (fused ? !fused->pair_flags || !fused->out : !xch->flags)) {
+            (fused ? !fused->pair_flags || (fused->mode == 1 && !fused->out) : !xch->flags)) {
             return llmtie_fail(LLMTIE_ERR_INVALID, "a malformed exchange descriptor");
         }
         if (batch > LLMTIE_DECODE_MAX_SEQ) {
@@ -1490,9 +1491,52 @@ extern "C" llmtie_status llmtie_decode_batched_fused(
         return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
                            batch * heads * head_dim, out_len);
     }
-    const FusedMerge fused = {pair_flags, out};
+    const FusedMerge fused = {pair_flags, out, 1};
     return decode_batched_impl(g, q, q_len, k_ptrs, v_ptrs, tk, cap, batch, heads, kv_heads,
                                head_dim, scale, scale_q, scratch, nullptr, 0, 1, xch, &fused);
+}
+
+extern "C" llmtie_status llmtie_decode_batched_signal(
+    llmtie_gpu *g, const float *q, size_t q_len, const uint16_t *const *k_ptrs,
+    const uint16_t *const *v_ptrs, const int32_t *tk, const int32_t *cap, size_t batch,
+    size_t heads, size_t kv_heads, size_t head_dim, float scale, int32_t scale_q,
+    llmtie_decode_scratch *scratch, const llmtie_exchange *xch, uint32_t *const *pair_flags)
+{
+    if (!xch) return llmtie_fail(LLMTIE_ERR_INVALID, "null exchange descriptor");
+    if (xch->world < 2) return llmtie_fail(LLMTIE_ERR_INVALID, "a malformed exchange descriptor");
+    const FusedMerge fused = {pair_flags, nullptr, 2};
+    return decode_batched_impl(g, q, q_len, k_ptrs, v_ptrs, tk, cap, batch, heads, kv_heads,
+                               head_dim, scale, scale_q, scratch, nullptr, 0, 1, xch, &fused);
+}
+
+extern "C" llmtie_status llmtie_lse_merge_pairs(llmtie_gpu *g, const llmtie_exchange *xch,
+                                                const uint32_t *pair_flags, uint32_t *merge_step,
+                                                size_t rows, size_t rows_per_pair,
+                                                size_t head_dim, float *out, size_t out_len)
+{
+    NEED_HANDLE(g);
+    if (!xch || xch->world < 2 || xch->world > LLMTIE_MAX_RANKS || xch->rank < 0 ||
+        xch->rank >= xch->world || !xch->gather || !pair_flags || !merge_step) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "a malformed exchange descriptor");
+    }
+    if (out_len < rows * head_dim) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %zu in a buffer of %zu",
+                           rows * head_dim, out_len);
+    }
+    if (head_dim == 0 || head_dim > 1024) return unsupported(head_dim, rows, rows);
+    if (rows_per_pair == 0 || rows % rows_per_pair != 0) {
+        return llmtie_fail(LLMTIE_ERR_RAGGED_BLOCK, "a row of %zu does not divide into blocks of %zu",
+                           rows, rows_per_pair);
+    }
+    if (rows == 0) return LLMTIE_OK;
+    // (LLMTIE_B200_NO_PDL launches it as an ordinary kernel: an A/B switch)
+    static const bool plain = getenv("LLMTIE_B200_NO_PDL") != nullptr;
+    LaunchScope ls(g, "lse_merge_pairs");
+    const cudaError_t e = launch_lse_merge_pairs(
+        g->stream, xch->gather[xch->rank], pair_flags, merge_step, xch->world, (int)rows,
+        (int)rows_per_pair, (int)head_dim, out, g->timeout_site, g->wait_cycles, !plain && !g->kprof);
+    if (e != cudaSuccess) return driver_fail("lse_merge_pairs", e);
+    return ls.done();
 }
 
 extern "C" llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_exchange *xch,

@@ -247,9 +247,10 @@ struct DecodeStreamParams {
     unsigned *xch_done;                      // pairs finished in this launch, zero at rest
     int xch_pairs;                           // pairs in this launch
     long long xch_rank_stride;               // floats one rank's triples take
-    // Fused merge (xch_fused): the block that finishes a pair on this rank
+    // Fused merge (xch_fused = 1): the block that finishes a pair on this rank
     // raises that pair's flag on every rank, and before it exits waits for the
     // other ranks' flags of the pair and merges it into xch_out, normalised.
+    // xch_fused = 2: the flags only; a dependent kernel merges.
     int xch_fused;
     unsigned *xch_pflags[LLMTIE_MAX_RANKS];  // every rank's pair flags [pairs][world]
     float *xch_out;                          // [rows][hd], this rank's merged result
@@ -285,6 +286,12 @@ void launch_lse_merge_wait(cudaStream_t st, const float *gather, const unsigned 
 cudaError_t launch_gemv_qkv_f16(cudaStream_t st, const float *a, const uint16_t *w, const float *qb,
                                 const float *kb, const float *vb, int k, int d, int hd, int cap,
                                 int pos, float *q, float *kc, float *vc);
+
+// The merge of a step signalled pair by pair (see lse_merge_pairs_kernel);
+// `early` launches it as a programmatic dependent of the kernel before it.
+cudaError_t launch_lse_merge_pairs(cudaStream_t st, const float *gather, const unsigned *pflags,
+                                   unsigned *mstep, int world, int rows, int rows_per_pair, int hd,
+                                   float *out, int *status, long long wait_cycles, bool early);
 
 // prefill_mma.cu
 #define LLMTIE_PREFILL_MAX_SEQ 32

@@ -33,6 +33,8 @@
 //          exactly the A fragment the value product wants.
 #include "common.cuh"
 
+#include <string.h>
+
 #include <math_constants.h>
 
 namespace {
@@ -557,6 +559,72 @@ __global__ void lse_merge_wait_kernel(const float *__restrict__ gather,
 
 const KernelReg reg_merge_wait("lse_merge_wait", (const void *)lse_merge_wait_kernel);
 
+// The merge of a step whose decode kernels raise a flag per (sequence, KV head)
+// pair and source rank. Launched as a programmatic dependent of this rank's
+// decode kernel, so its blocks are resident and polling while that kernel
+// still streams: a row is merged as soon as every rank's triple of its pair
+// has landed, and neither this kernel's launch nor the exchange of any pair
+// but the last lies on the step's critical path. It never waits for the
+// decode kernel as a whole, only for flags (bounded), and counts its own
+// steps: mstep[0] is the step it is about to merge, advanced by the last
+// block to finish (mstep[1] counts the blocks out). Layout: gather
+// [2][world][rows][hd + 2], pflags [rows / rows_per_pair][world].
+__global__ void lse_merge_pairs_kernel(const float *__restrict__ gather, const unsigned *pflags,
+                                       unsigned *mstep, int world, int rows, int rows_per_pair,
+                                       int hd, float *__restrict__ out, int *status,
+                                       long long wait_cycles)
+{
+    __shared__ int s_ok;
+    const unsigned step = *(volatile const unsigned *)mstep;
+    const int row = blockIdx.x;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if ((int)threadIdx.x < world) {
+        const unsigned *f = pflags + (size_t)(row / rows_per_pair) * world + threadIdx.x;
+        const long long t0 = clock64();
+        while ((int)(ld_acquire_sys(f) - (step + 1u)) < 0) {
+            if (clock64() - t0 > wait_cycles) {
+                s_ok = 0;
+                report_timeout(status, 90 + (int)threadIdx.x);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (s_ok) {
+        const int stride = hd + 2;
+        const float *buf = gather + (size_t)(step & 1u) * world * rows * stride;
+        float M = -CUDART_INF_F;
+        for (int i = 0; i < world; i++) {
+            M = fmaxf(M, __ldcg(buf + ((size_t)i * rows + row) * stride + hd));
+        }
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            float O = 0.0f, L = 0.0f;
+            for (int i = 0; i < world; i++) {
+                const float *pr = buf + ((size_t)i * rows + row) * stride;
+                const float mi = __ldcg(pr + hd);
+                const float f = (mi == -CUDART_INF_F) ? 0.0f : __expf(mi - M);
+                O += f * __ldcg(pr + d);
+                L += f * __ldcg(pr + hd + 1);
+            }
+            out[(size_t)row * hd + d] = L > 0.0f ? O / L : 0.0f;
+        }
+    }
+    // count the block out; the last one advances the step (every block has
+    // read it by then)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(mstep + 1, 1u);
+        if (prev == gridDim.x - 1) {
+            mstep[1] = 0u;
+            __threadfence();
+            *(volatile unsigned *)mstep = step + 1u;
+        }
+    }
+}
+
+const KernelReg reg_merge_pairs("lse_merge_pairs", (const void *)lse_merge_pairs_kernel);
+
 }  // namespace
 
 void launch_lse_merge_wait(cudaStream_t st, const float *gather, const unsigned *flags,
@@ -565,6 +633,24 @@ void launch_lse_merge_wait(cudaStream_t st, const float *gather, const unsigned 
 {
     lse_merge_wait_kernel<<<rows, hd, 0, st>>>(gather, flags, step, world, rows, hd, out, status,
                                                wait_cycles);
+}
+
+cudaError_t launch_lse_merge_pairs(cudaStream_t st, const float *gather, const unsigned *pflags,
+                                   unsigned *mstep, int world, int rows, int rows_per_pair, int hd,
+                                   float *out, int *status, long long wait_cycles, bool early)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(rows);
+    cfg.blockDim = dim3(hd < 32 ? 32 : (hd > 256 ? 256 : hd));
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = early ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, lse_merge_pairs_kernel, gather, pflags, mstep, world, rows,
+                              rows_per_pair, hd, out, status, wait_cycles);
 }
 
 cudaError_t launch_decode_f16(cudaStream_t st, const DecodeParams &p, int hd)

@@ -532,6 +532,26 @@ class Gpu:
             out.numel()))
         return out
 
+    def decode_batched_signal(self, q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale, scale_q,
+                              scratch: DecodeScratch, xch: Exchange) -> None:
+        """Decode, push, and a flag per (sequence, KV head) pair (see
+        include/llmtie_b200.h); `lse_merge_pairs` follows it."""
+        if xch.pair_flags is None:
+            raise ValueError("this exchange needs per-pair flags")
+        _check(self._lib.llmtie_decode_batched_signal(
+            self._h, q.data_ptr(), q.numel(), self._ptr_table(ks), self._ptr_table(vs),
+            self._i32_table(tk), self._i32_table(cap), len(ks), heads, kv_heads, head_dim, scale,
+            int(bool(scale_q)), scratch._bind(self), xch.ref(), xch.pair_flags))
+
+    def lse_merge_pairs(self, xch: Exchange, merge_step, rows, rows_per_pair, head_dim,
+                        out=None) -> torch.Tensor:
+        if out is None:
+            out = self.uninit(rows * head_dim)
+        _check(self._lib.llmtie_lse_merge_pairs(
+            self._h, xch.ref(), xch.pair_flags[xch.rank], merge_step.data_ptr(), rows,
+            rows_per_pair, head_dim, out.data_ptr(), out.numel()))
+        return out
+
     def lse_merge_wait(self, xch: Exchange, rows, head_dim, out=None) -> torch.Tensor:
         if out is None:
             out = self.uninit(rows * head_dim)

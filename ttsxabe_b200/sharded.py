@@ -94,7 +94,8 @@ class ShardedDecode:
             fused, why = None, ""
             try:
                 fused = cls._on_gpu_p2p(gpu, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
-                                        scale_q, group, scratch, one_kernel=(p2p == "fused"))
+                                        scale_q, group, scratch,
+                                        one_kernel=("pairs" if p2p == "pairs" else p2p == "fused"))
             except (ImportError, RuntimeError, AttributeError) as e:
                 why = str(e)
             ok = torch.tensor([1 if fused is not None else 0], dtype=torch.int32,
@@ -151,6 +152,7 @@ class ShardedDecode:
             flags.zero_()
             pflags.zero_()
             step = torch.zeros(1, dtype=torch.int32, device=gpu.device)
+            mstep = torch.zeros(2, dtype=torch.int32, device=gpu.device)
             out = torch.empty(rows * head_dim, dtype=torch.float32, device=gpu.device)
         gh = symm_mem.rendezvous(gather, pg)
         fh = symm_mem.rendezvous(flags, pg)
@@ -162,9 +164,14 @@ class ShardedDecode:
                        [int(p) for p in ph.buffer_ptrs])
 
         self = cls(heads, head_dim, group, None, None, gpu.stream)
-        self._keep = (gather, flags, pflags, step, gh, fh, ph, xch, scratch, out)
+        self._keep = (gather, flags, pflags, step, mstep, gh, fh, ph, xch, scratch, out)
 
-        if one_kernel:
+        if one_kernel == "pairs":
+            def fused(q):
+                gpu.decode_batched_signal(q, ks, vs, tk, cap, heads, kv_heads, head_dim, scale,
+                                          scale_q, scratch, xch)
+                return gpu.lse_merge_pairs(xch, mstep, rows, heads // kv_heads, head_dim, out=out)
+        elif one_kernel:
             def fused(q):
                 return gpu.decode_batched_fused(q, ks, vs, tk, cap, heads, kv_heads, head_dim,
                                                 scale, scale_q, scratch, xch, out=out)
@@ -186,7 +193,8 @@ class ShardedDecode:
                                       scale_q, scratch, out=local[partial], partial=partial)
 
         self.partial_fn = partial_fn
-        self.exchange = "peer-fused" if one_kernel else "peer-push"
+        self.exchange = ("peer-pairs" if one_kernel == "pairs"
+                         else "peer-fused" if one_kernel else "peer-push")
         return self
 
     def decode(self, q: torch.Tensor) -> torch.Tensor:
