@@ -35,9 +35,14 @@ def test_a_run_that_crosses_a_pair_boundary_carries_fewer_keys():
     sizes = np.diff(cut)
     crossing = np.array([(a // 128) != ((b - 1) // 128) for a, b in zip(cut, cut[1:])])
     assert crossing.any() and (~crossing).any()
-    # three virtual units at the head of a pair: the runs that swallow them are shorter
+    # five virtual units at the head of a long pair: the runs that swallow them are shorter
     assert sizes[crossing].max() < np.median(sizes[~crossing])
-    assert 2.0 <= sizes[~crossing].mean() - sizes[crossing].mean() <= 4.0
+    assert 4.0 <= sizes[~crossing].mean() - sizes[crossing].mean() <= 6.0
+    # short pairs (24 units each) carry three
+    cut = decode_cut([3072] * 16, kv, 128, 148)
+    sizes = np.diff(cut)
+    crossing = np.array([(a // 24) != ((b - 1) // 24) for a, b in zip(cut, cut[1:])])
+    assert 1.0 <= sizes[~crossing].mean() - sizes[crossing].mean() <= 4.0
     assert sizes.max() - sizes.min() <= 4
 
 

@@ -399,7 +399,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     extern __shared__ unsigned char ring_raw[];
     // tensor copies want their destination on a 128-byte boundary
     unsigned char *ring_all = ring_raw + ((128u - (smem_u32(ring_raw) & 127u)) & 127u);
-    __shared__ __align__(8) uint64_t sm_bar[kWarps][2 * kStages];
+    __shared__ __align__(8) uint64_t sm_bar[kWarps][kStages];
     __shared__ __align__(16) float sm_o[kWarps][kRows][HD + 8];   // +8: rows 0-3 and 4-7 tile the banks
     __shared__ float sm_m[kWarps][kRows];
     __shared__ float sm_l[kWarps][kRows];
@@ -417,26 +417,20 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     const int lane = tid & 31;
     const int g = lane >> 2;
     const int c = lane & 3;
-    // The warp's rings: kStages key blocks, then kStages value blocks. They
-    // are two rings because they run one block apart: while the values of
-    // block i go into the context, the keys of block i + 1 are already being
-    // scored (see the key loop).
     unsigned char *ring = ring_all + (size_t)warp * kStages * STAGE;
-    unsigned char *ring_v = ring + kStages * KBYTES;
-    const uint32_t ring_ks = smem_u32(ring), ring_vs = smem_u32(ring_v);
-    // One barrier a stage of either ring, completed by the bytes of the
-    // stage's copy. The stage and phase counters run on across the segments
-    // of the block's run.
-    const uint32_t kbar0 = smem_u32(&sm_bar[warp][0]);
-    const uint32_t vbar0 = kbar0 + 8u * kStages;
+    const uint32_t ring_s = smem_u32(ring);
+    // The warp's ring barriers: one a stage, completed by the bytes of the
+    // stage's two copies. The stage and phase counters run on across the
+    // segments of the block's run.
+    const uint32_t bar0 = smem_u32(&sm_bar[warp][0]);
     if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < 2 * kStages; s++) mbar_init(kbar0 + 8u * s, 1);
+        for (int s = 0; s < kStages; s++) mbar_init(bar0 + 8u * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    uint32_t k_use = 0, k_ph = 0, k_put = 0;   // keys: stage consumed next, its phase, stage filled next
-    uint32_t v_use = 0, v_ph = 0, v_put = 0;   // values: the same
+    uint32_t st_use = 0, ph_use = 0;   // the stage the next block is consumed from, its phase
+    uint32_t st_put = 0;               // the stage the next copy goes to
     bool ring_ok = true;
 
     // When ranks exchange, the step number picks which of the two gather
@@ -484,30 +478,24 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
         }
 
-        // Copies the keys (values) of block `blk` (32 keys) into the next stage
-        // of their ring: the key rows as HD/32 chunks of [32 keys][64 bytes]
-        // (two adjacent rows of a chunk fall on different halves of the
-        // banks), the value rows [HD][64 bytes]. Whatever lies past k_end
-        // comes along (the next keys of the cache, its unused capacity, or
-        // zeros past its end) and is masked where it is used.
+        // Copies block `blk` (32 keys) into the ring's next stage: the key rows
+        // as HD/32 chunks of [32 keys][64 bytes] (two adjacent rows of a chunk
+        // fall on different halves of the banks), the value rows [HD][64
+        // bytes]. Whatever lies past k_end comes along (the next keys of the
+        // cache, its unused capacity, or zeros past its end) and is masked
+        // where it is used.
         const CUtensorMap *kmap = &p.kmap[b];
         const CUtensorMap *vmap = &p.vmap[b];
         const int krow0 = kh * cap, vrow0 = kh * HD;
-        auto issue_k = [&](int blk) {
+        auto issue = [&](int blk) {
             if (lane == 0) {
-                const uint32_t bar = kbar0 + 8u * k_put;
-                mbar_expect_tx(bar, KBYTES);
-                tma_load_3d(ring_ks + k_put * KBYTES, kmap, bar, 0, krow0 + blk, 0);
+                const uint32_t dst = ring_s + st_put * STAGE;
+                const uint32_t bar = bar0 + 8u * st_put;
+                mbar_expect_tx(bar, STAGE);
+                tma_load_3d(dst, kmap, bar, 0, krow0 + blk, 0);
+                tma_load_2d(dst + KBYTES, vmap, bar, blk, vrow0);
             }
-            k_put = (k_put + 1 == kStages) ? 0u : k_put + 1;
-        };
-        auto issue_v = [&](int blk) {
-            if (lane == 0) {
-                const uint32_t bar = vbar0 + 8u * v_put;
-                mbar_expect_tx(bar, VBYTES);
-                tma_load_2d(ring_vs + v_put * VBYTES, vmap, bar, blk, vrow0);
-            }
-            v_put = (v_put + 1 == kStages) ? 0u : v_put + 1;
+            st_put = (st_put + 1 == kStages) ? 0u : st_put + 1;
         };
 
         // The query row goes out first, ahead of the ring's first copies in the
@@ -533,11 +521,9 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         // This warp's blocks: k_begin + (warp + kWarps * i) * 32.
         const int first = k_begin + warp * 32;
         const int nblk = first < k_end ? (k_end - first + kWarps * 32 - 1) / (kWarps * 32) : 0;
-        constexpr int BSTEP = kWarps * 32;   // keys from one of this warp's blocks to its next
-        if (nblk > 0) {
-            issue_k(first);
-            issue_v(first);
-            if (nblk > 1) issue_k(first + BSTEP);
+#pragma unroll
+        for (int s = 0; s < kStages - 1; s++) {
+            if (s < nblk) issue(first + s * kWarps * 32);
         }
 
         // ---- query fragments, permuted as the key loads are, split hi / lo ------
@@ -551,138 +537,108 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
         }
 
-        // The key loop, software-pipelined by one block: pass i puts the values of
-        // block i into the context while it scores the keys of block i + 1, the
-        // two streams of MMAs interleaved step for step. With one warp to a
-        // scheduler nothing else hides an MMA's latency; the two products are
-        // independent, so each fills the other's bubbles. Pass -1 only scores
-        // block 0. Every accumulator still takes its terms in the same order.
-        float t[2][2][2];
-        for (int i = nblk > 0 ? -1 : 0; i < nblk; i++) {
-            const bool has_pv = i >= 0, has_qk = i + 1 < nblk;
-            // keys three blocks ahead, values two: into the stages the last
-            // pass finished with
-            if (i + 3 < nblk) issue_k(first + (i + 3) * BSTEP);
-            if (i + 2 < nblk) issue_v(first + (i + 2) * BSTEP);
+        for (int i = 0; i < nblk; i++) {
+            // Start the copy two blocks ahead, into the stage the last
+            // iteration finished with, then wait for this block's.
+            {
+                const int nx = i + kStages - 1;
+                if (nx < nblk) issue(first + nx * kWarps * 32);
+            }
+            if (ring_ok && !ring_wait(bar0 + 8u * st_use, ph_use, p.wait_cycles)) {
+                // The stage never landed: say so, and finish the run on
+                // whatever the ring holds rather than wait again.
+                ring_ok = false;
+                if (lane == 0) report_timeout(p.status, 80 + warp);
+            }
 
-            // ---- online softmax over block i ---------------------------------------
+            const int blk = first + i * kWarps * 32;
+            const unsigned char *ks = ring + st_use * STAGE;
+            const unsigned char *vs = ks + KBYTES;
+            if (++st_use == kStages) {
+                st_use = 0;
+                ph_use ^= 1u;
+            }
+
+            // ---- scores: four 8-key tiles ----------------------------------------
+            float t[2][2][2];
+#pragma unroll
+            for (int mm = 0; mm < 2; mm++) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int row = 8 * (g >> 1) + 4 * mm + 2 * h + (g & 1);
+                    const unsigned char *krow = ks + row * 64 + c * 16;
+                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int ii = 0; ii < KI; ii++) {
+                        uint32_t r[4];
+                        lds128(r, krow + ii * KCHUNK);
+                        mma16816(acc, qa[ii][0][0], qa[ii][0][1], qa[ii][0][2], qa[ii][0][3],
+                                 r[0], r[1]);
+                        mma16816(acc, qa[ii][1][0], qa[ii][1][1], qa[ii][1][2], qa[ii][1][3],
+                                 r[2], r[3]);
+                    }
+                    const int k0 = blk + 8 * c + 4 * mm + 2 * h;
+                    t[mm][h][0] = (k0 < k_end) ? (acc[0] + acc[2]) * p.sl2 : -CUDART_INF_F;
+                    t[mm][h][1] = (k0 + 1 < k_end) ? (acc[1] + acc[3]) * p.sl2 : -CUDART_INF_F;
+                }
+            }
+
+            // ---- online softmax over the block -------------------------------------
+            float bm = -CUDART_INF_F;
+#pragma unroll
+            for (int mm = 0; mm < 2; mm++) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) bm = fmaxf(bm, fmaxf(t[mm][h][0], t[mm][h][1]));
+            }
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+            const float m_new = fmaxf(m, bm);
+            if (__any_sync(0xffffffffu, m_new > m)) {
+                const float alpha = ex2(m - m_new);   // 0 on the first block
+                l *= alpha;
+#pragma unroll
+                for (int j = 0; j < NT; j++) {
+                    o[j][0] *= alpha;
+                    o[j][1] *= alpha;
+                    o[j][2] *= alpha;
+                    o[j][3] *= alpha;
+                }
+            }
+            m = m_new;
             uint32_t pa[2][4];
-            if (has_pv) {
-                float bm = -CUDART_INF_F;
 #pragma unroll
-                for (int mm = 0; mm < 2; mm++) {
+            for (int mm = 0; mm < 2; mm++) {
 #pragma unroll
-                    for (int h = 0; h < 2; h++) bm = fmaxf(bm, fmaxf(t[mm][h][0], t[mm][h][1]));
-                }
-                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-                const float m_new = fmaxf(m, bm);
-                if (__any_sync(0xffffffffu, m_new > m)) {
-                    const float alpha = ex2(m - m_new);   // 0 on the first block
-                    l *= alpha;
-#pragma unroll
-                    for (int j = 0; j < NT; j++) {
-                        o[j][0] *= alpha;
-                        o[j][1] *= alpha;
-                        o[j][2] *= alpha;
-                        o[j][3] *= alpha;
-                    }
-                }
-                m = m_new;
-#pragma unroll
-                for (int mm = 0; mm < 2; mm++) {
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const float p0 = ex2(t[mm][h][0] - m);
-                        const float p1 = ex2(t[mm][h][1] - m);
-                        l += p0 + p1;
-                        split_pair(p0, p1, pa[mm][2 * h], pa[mm][2 * h + 1]);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; e++) pa[0][e] = pa[1][e] = 0u;
-            }
-
-            // ---- wait for the values of block i and the keys of block i + 1 ---------
-            const unsigned char *vs = ring_v + v_use * VBYTES;
-            const unsigned char *kn = ring + k_use * KBYTES;
-            if (has_pv) {
-                if (ring_ok && !ring_wait(vbar0 + 8u * v_use, v_ph, p.wait_cycles)) {
-                    // The stage never landed: say so, and finish the run on
-                    // whatever the ring holds rather than wait again.
-                    ring_ok = false;
-                    if (lane == 0) report_timeout(p.status, 80 + warp);
-                }
-                if (++v_use == kStages) {
-                    v_use = 0;
-                    v_ph ^= 1u;
-                }
-            }
-            if (has_qk) {
-                if (ring_ok && !ring_wait(kbar0 + 8u * k_use, k_ph, p.wait_cycles)) {
-                    ring_ok = false;
-                    if (lane == 0) report_timeout(p.status, 84 + warp);
-                }
-                if (++k_use == kStages) {
-                    k_use = 0;
-                    k_ph ^= 1u;
+                for (int h = 0; h < 2; h++) {
+                    const float p0 = ex2(t[mm][h][0] - m);
+                    const float p1 = ex2(t[mm][h][1] - m);
+                    l += p0 + p1;
+                    split_pair(p0, p1, pa[mm][2 * h], pa[mm][2 * h + 1]);
                 }
             }
 
-            // ---- context of block i and scores of block i + 1, step for step ---------
-            const int blk = first + i * BSTEP;
+            // ---- context ---------------------------------------------------------------
             const int nlive = k_end - (blk + 8 * c);   // keys of this thread's eight that exist
-            float acc[4][4];
 #pragma unroll
-            for (int tl = 0; tl < 4; tl++) acc[tl][0] = acc[tl][1] = acc[tl][2] = acc[tl][3] = 0.0f;
+            for (int j = 0; j < NT; j++) {
+                uint32_t r[4];
+                lds128(r, vs + (8 * j + g) * 64 + c * 16);
+                if (nlive < 8) {
+                    // Capacity past the live keys may hold anything, and
+                    // 0 * NaN is NaN: clear what lies beyond.
 #pragma unroll
-            for (int s = 0; s < NT; s++) {
-                if (has_pv) {
-                    uint32_t r[4];
-                    lds128(r, vs + (8 * s + g) * 64 + c * 16);
-                    if (nlive < 8) {
-                        // Capacity past the live keys may hold anything, and
-                        // 0 * NaN is NaN: clear what lies beyond.
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            if (nlive <= 2 * e) {
-                                r[e] = 0u;
-                            } else if (nlive == 2 * e + 1) {
-                                r[e] &= 0x0000ffffu;
-                            }
+                    for (int e = 0; e < 4; e++) {
+                        if (nlive <= 2 * e) {
+                            r[e] = 0u;
+                        } else if (nlive == 2 * e + 1) {
+                            r[e] &= 0x0000ffffu;
                         }
                     }
-                    mma16816(o[s], pa[0][0], pa[0][1], pa[0][2], pa[0][3], r[0], r[1]);
-                    mma16816(o[s], pa[1][0], pa[1][1], pa[1][2], pa[1][3], r[2], r[3]);
                 }
-                if (has_qk) {
-                    // score tile tl = (mm, h) takes its k-step ii; the four tiles
-                    // take turns, so a tile's dependent MMAs lie four steps apart
-                    const int tl = s & 3, ii = s >> 2;
-                    const int row = 8 * (g >> 1) + 4 * (tl >> 1) + 2 * (tl & 1) + (g & 1);
-                    uint32_t r[4];
-                    lds128(r, kn + row * 64 + c * 16 + ii * KCHUNK);
-                    mma16816(acc[tl], qa[ii][0][0], qa[ii][0][1], qa[ii][0][2], qa[ii][0][3], r[0],
-                             r[1]);
-                    mma16816(acc[tl], qa[ii][1][0], qa[ii][1][1], qa[ii][1][2], qa[ii][1][3], r[2],
-                             r[3]);
-                }
+                mma16816(o[j], pa[0][0], pa[0][1], pa[0][2], pa[0][3], r[0], r[1]);
+                mma16816(o[j], pa[1][0], pa[1][1], pa[1][2], pa[1][3], r[2], r[3]);
             }
-            if (has_qk) {
-#pragma unroll
-                for (int mm = 0; mm < 2; mm++) {
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int tl = 2 * mm + h;
-                        const int k0 = blk + BSTEP + 8 * c + 4 * mm + 2 * h;
-                        t[mm][h][0] = (k0 < k_end) ? (acc[tl][0] + acc[tl][2]) * p.sl2 : -CUDART_INF_F;
-                        t[mm][h][1] =
-                            (k0 + 1 < k_end) ? (acc[tl][1] + acc[tl][3]) * p.sl2 : -CUDART_INF_F;
-                    }
-                }
-            }
-            __syncwarp();   // every lane is done with these stages before they are refilled
+            __syncwarp();   // every lane is done with this stage before it is refilled
         }
 
         // ---- the block's four warps merge through shared memory ----------------------
@@ -870,8 +826,12 @@ static void stream_partition(DecodeStreamParams &p, int hd, int grid)
         const char *e = getenv("LLMTIE_B200_DECODE_OV");
         return e ? atoi(e) : -1;
     }();
-    const long long ov = ov_env >= 0 ? (hd == 128 ? ov_env : 2 * ov_env)
-                                     : (hd == 128 ? 3 : 6);   // the same time in units of either width
+    // Five units' worth measured best on long pairs (128 units each: 4-6 all
+    // within a percent, 3 and 8 some 3 % slower); short pairs, where a run is
+    // only a few units, do better with three.
+    const long long pairs_all = std::max<long long>(1, (long long)p.nseq * p.kv_heads * p.row_chunks);
+    const int credit = p.total_units / pairs_all >= 64 ? 5 : 3;
+    const long long ov = (ov_env >= 0 ? ov_env : credit) * (hd == 128 ? 1 : 2);   // the same time at either width
     const int inner = p.kv_heads * p.row_chunks;
     const long long W = p.total_units;
     const long long V = W + ov * (long long)p.nseq * inner;
