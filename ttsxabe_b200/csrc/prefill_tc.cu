@@ -409,6 +409,8 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     const bool dead = abort_flag_s != 0;
+    // a dependent kernel (the merge of cut row blocks) may be set up from here on
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // The register file is split by role: a warp scheduler holds one warp of
     // each warpgroup, and 208 + 208 + 88 registers are the 3 x 168 per lane the block was launched with (asking for more would wait forever).
@@ -943,6 +945,9 @@ __global__ void __launch_bounds__(128) prefill_merge_kernel(const __grid_constan
 {
     constexpr int V = HD / 32;                 // channels a lane carries
     constexpr int kBatch = 8;
+    // (launched as the attention kernel's programmatic dependent: nothing of
+    // that kernel's may be read before it has ended)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const PrefillMergeGroup g = p.group[blockIdx.x];
     const int x = blockIdx.y >> 1, t = blockIdx.y & 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1274,12 +1279,21 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, c
                 mp.n_groups = (int)std::min<size_t>(kMergeGroups, groups.size() - g0);
                 for (int i = 0; i < mp.n_groups; i++) mp.group[i] = groups[g0 + i];
                 const dim3 mg((unsigned)mp.n_groups, grid.x * 2, BM / 4);
-                if (hd == 128) {
-                    prefill_merge_kernel<128><<<mg, 128, 0, st>>>(mp);
-                } else {
-                    prefill_merge_kernel<64><<<mg, 128, 0, st>>>(mp);
-                }
-                err = cudaGetLastError();
+                // A programmatic dependent of the attention kernel: its blocks are
+                // set up while that kernel's last blocks still run, and wait for
+                // its end (griddepcontrol.wait) before they read anything.
+                cudaLaunchConfig_t cfg;
+                memset(&cfg, 0, sizeof(cfg));
+                cfg.gridDim = mg;
+                cfg.blockDim = dim3(128);
+                cfg.stream = st;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[0].val.programmaticStreamSerializationAllowed = 1;
+                cfg.attrs = attr;
+                cfg.numAttrs = (g0 == 0) ? 1 : 0;
+                err = hd == 128 ? cudaLaunchKernelEx(&cfg, prefill_merge_kernel<128>, mp)
+                                : cudaLaunchKernelEx(&cfg, prefill_merge_kernel<64>, mp);
             }
         }
     }
