@@ -221,7 +221,7 @@ int decode_resident_blocks(int hd, int sm_count, int nb);
 #define LLMTIE_STREAM_MAX_BLOCKS 160
 struct DecodeStreamParams {
     // Tensor maps of each sequence's caches (see decode_tensor_maps): keys as
-    // [hd/32][kv*cap][32 halves], values as [kv*hd][cap].
+    // [kv*cap][hd], values as [kv*hd][cap].
     alignas(64) CUtensorMap kmap[LLMTIE_DECODE_MAX_SEQ];
     alignas(64) CUtensorMap vmap[LLMTIE_DECODE_MAX_SEQ];
     DecodeSeq seq[LLMTIE_DECODE_MAX_SEQ];
@@ -263,14 +263,15 @@ struct DecodeStreamParams {
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
 // The two tensor maps the ring kernel reads one sequence's caches through:
-// keys [kv][cap][hd] seen as 64-byte column chunks x rows (so that a 32-key
-// block lands in shared memory chunk by chunk, free of bank conflicts), values
-// [kv][hd][cap] seen as rows of `cap`. No swizzle; reads past the end return zero.
+// keys [kv][cap][hd] seen as kv*cap rows (boxes of 32 rows x 128 bytes, 128-byte
+// swizzle), values [kv][hd][cap] seen as kv*hd rows of `cap` (boxes of hd rows
+// x 64 bytes, 64-byte swizzle): what ldmatrix reads without bank conflicts.
+// Reads past the end return zero.
 bool decode_tensor_maps(CUtensorMap *kmap, CUtensorMap *vmap, const void *k, const void *v,
                         int kv_heads, int cap, int hd);
 // cuTensorMapEncodeTiled for f16 data, through the runtime's driver entry point.
 bool llmtie_encode_tiled_f16(CUtensorMap *map, int rank, const void *base, const uint64_t *dims,
-                             const uint64_t *strides_bytes, const uint32_t *box, bool swizzle128);
+                             const uint64_t *strides_bytes, const uint32_t *box, int swizzle_bytes);
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
                        const float *v, float *out, long long out_off, int heads, int kv_heads,
                        int hd, int tk, int cap, float q_scale, float s_scale);

@@ -540,18 +540,28 @@ __global__ void lse_merge_wait_kernel(const float *__restrict__ gather,
     const int row = blockIdx.x;
     const int stride = hd + 2;
     const float *buf = gather + (size_t)((s_expected - 1u) & 1u) * world * rows * stride;
-    float M = -CUDART_INF_F;
-    for (int i = 0; i < world; i++) {
-        M = fmaxf(M, __ldcg(buf + ((size_t)i * rows + row) * stride + hd));
-    }
+    // every rank's (m, l) and this thread's channel of o in flight at once:
+    // the kernel is one trip to L2, not one per pass
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float mi[LLMTIE_MAX_RANKS], li[LLMTIE_MAX_RANKS], oi[LLMTIE_MAX_RANKS];
+#pragma unroll
+        for (int i = 0; i < LLMTIE_MAX_RANKS; i++) {
+            const float *pr = buf + ((size_t)min(i, world - 1) * rows + row) * stride;
+            mi[i] = __ldcg(pr + hd);
+            li[i] = __ldcg(pr + hd + 1);
+            oi[i] = __ldcg(pr + d);
+        }
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < LLMTIE_MAX_RANKS; i++) M = fmaxf(M, mi[i]);   // repeats are harmless
         float O = 0.0f, L = 0.0f;
-        for (int i = 0; i < world; i++) {
-            const float *pr = buf + ((size_t)i * rows + row) * stride;
-            const float mi = __ldcg(pr + hd);
-            const float f = (mi == -CUDART_INF_F) ? 0.0f : __expf(mi - M);
-            O += f * __ldcg(pr + d);
-            L += f * __ldcg(pr + hd + 1);
+#pragma unroll
+        for (int i = 0; i < LLMTIE_MAX_RANKS; i++) {
+            if (i < world) {
+                const float f = (mi[i] == -CUDART_INF_F) ? 0.0f : __expf(mi[i] - M);
+                O += f * oi[i];
+                L += f * li[i];
+            }
         }
         out[(size_t)row * hd + d] = L > 0.0f ? O / L : 0.0f;
     }

@@ -94,16 +94,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
-                                            int x, int y, int z)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
-        "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
-        : "memory");
-}
-
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem, int src_bytes)
 {
     const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
@@ -121,12 +111,13 @@ __device__ __forceinline__ void cp_async_wait()
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-__device__ __forceinline__ void lds128(uint32_t (&r)[4], const void *smem)
+// Four 8 x 8 matrices of halves, one 16-byte row a lane; lane (g, c) receives
+// row g, columns 2c and 2c + 1 of each.
+__device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], uint32_t addr)
 {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(a));
+                 : "r"(addr));
 }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -394,11 +385,12 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     constexpr int KBYTES = 32 * HD * 2;     // one 32-key block of keys
     constexpr int VBYTES = HD * 64;         // the same block of the transposed values
     constexpr int STAGE = KBYTES + VBYTES;
-    constexpr int KCHUNK = 32 * 64;         // a 64-byte column chunk of the block's 32 key rows
+    constexpr int KSUB = 32 * 128;          // a sub-tile of the key block: 32 rows x 64 channels
 
     extern __shared__ unsigned char ring_raw[];
-    // tensor copies want their destination on a 128-byte boundary
-    unsigned char *ring_all = ring_raw + ((128u - (smem_u32(ring_raw) & 127u)) & 127u);
+    // the 128-byte swizzle of the key tiles is a function of the address: the
+    // ring starts on a 1024-byte boundary
+    unsigned char *ring_all = ring_raw + ((1024u - (smem_u32(ring_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t sm_bar[kWarps][kStages];
     __shared__ __align__(16) float sm_o[kWarps][kRows][HD + 8];   // +8: rows 0-3 and 4-7 tile the banks
     __shared__ float sm_m[kWarps][kRows];
@@ -479,9 +471,9 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         }
 
         // Copies block `blk` (32 keys) into the ring's next stage: the key rows
-        // as HD/32 chunks of [32 keys][64 bytes] (two adjacent rows of a chunk
-        // fall on different halves of the banks), the value rows [HD][64
-        // bytes]. Whatever lies past k_end comes along (the next keys of the
+        // as HD/64 sub-tiles of [32 keys][128 bytes] (128-byte swizzle), the
+        // value rows [HD][64 bytes] (64-byte swizzle): whole lines from memory,
+        // and ldmatrix reads both without bank conflicts. Whatever lies past k_end comes along (the next keys of the
         // cache, its unused capacity, or zeros past its end) and is masked
         // where it is used.
         const CUtensorMap *kmap = &p.kmap[b];
@@ -492,7 +484,10 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                 const uint32_t dst = ring_s + st_put * STAGE;
                 const uint32_t bar = bar0 + 8u * st_put;
                 mbar_expect_tx(bar, STAGE);
-                tma_load_3d(dst, kmap, bar, 0, krow0 + blk, 0);
+#pragma unroll
+                for (int kt = 0; kt < HD / 64; kt++) {
+                    tma_load_2d(dst + kt * KSUB, kmap, bar, 64 * kt, krow0 + blk);
+                }
                 tma_load_2d(dst + KBYTES, vmap, bar, blk, vrow0);
             }
             st_put = (st_put + 1 == kStages) ? 0u : st_put + 1;
@@ -500,20 +495,20 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
 
         // The query row goes out first, ahead of the ring's first copies in the
         // load pipe, and is consumed after them: the two latencies overlap.
-        float qx[KI][2][4];
+        // (fragment layout of the m16n8k16 A operand: step s of sixteen channels,
+        // this lane's columns 2c, 2c + 1 and 2c + 8, 2c + 9 of it)
+        constexpr int KS = HD / 16;
+        float qx[KS][4];
         {
             const float *qrow = p.q + (long long)b * p.q_seq + (long long)kh * p.q_kv +
                                 (long long)(rc * kRows + g) * p.q_row;
             const bool live = g < rows_here;
 #pragma unroll
-            for (int i = 0; i < KI; i++) {
+            for (int ks_ = 0; ks_ < KS; ks_++) {
 #pragma unroll
-                for (int uu = 0; uu < 2; uu++) {
-                    const int at = 32 * i + 8 * c + 4 * uu;
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        qx[i][uu][e] = live ? __ldg(qrow + at + e) * p.q_scale : 0.0f;
-                    }
+                for (int e = 0; e < 4; e++) {
+                    const int at = 16 * ks_ + 2 * c + 8 * (e >> 1) + (e & 1);
+                    qx[ks_][e] = live ? __ldg(qrow + at) * p.q_scale : 0.0f;
                 }
             }
         }
@@ -526,16 +521,16 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             if (s < nblk) issue(first + s * kWarps * 32);
         }
 
-        // ---- query fragments, permuted as the key loads are, split hi / lo ------
-        uint32_t qa[KI][2][4];
+        // ---- query fragments, split hi / lo: a0 a2 carry the heads (rows 0-7 of
+        // the operand), a1 a3 the remainders (rows 8-15) ---------------------------
+        uint32_t qa[KS][4];
 #pragma unroll
-        for (int i = 0; i < KI; i++) {
-#pragma unroll
-            for (int uu = 0; uu < 2; uu++) {
-                split_pair(qx[i][uu][0], qx[i][uu][1], qa[i][uu][0], qa[i][uu][1]);
-                split_pair(qx[i][uu][2], qx[i][uu][3], qa[i][uu][2], qa[i][uu][3]);
-            }
+        for (int ks_ = 0; ks_ < KS; ks_++) {
+            split_pair(qx[ks_][0], qx[ks_][1], qa[ks_][0], qa[ks_][1]);
+            split_pair(qx[ks_][2], qx[ks_][3], qa[ks_][2], qa[ks_][3]);
         }
+        // ldmatrix row addresses of this lane: matrix lane >> 3, row lane & 7
+        const int lm = lane >> 3, li = lane & 7;
 
         for (int i = 0; i < nblk; i++) {
             // Start the copy two blocks ahead, into the stage the last
@@ -560,36 +555,33 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
 
             // ---- scores: four 8-key tiles ----------------------------------------
-            float t[2][2][2];
+            // Tile T is keys 8T..8T+7 of the block; one ldmatrix brings 32
+            // channels of them (four 8 x 8 matrices) for two MMAs.
+            const uint32_t ks_s = smem_u32(ks), vs_s = smem_u32(vs);
+            float t[4][2];
 #pragma unroll
-            for (int mm = 0; mm < 2; mm++) {
+            for (int T = 0; T < 4; T++) {
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const uint32_t krow = ks_s + (uint32_t)(8 * T + li) * 128u;
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int row = 8 * (g >> 1) + 4 * mm + 2 * h + (g & 1);
-                    const unsigned char *krow = ks + row * 64 + c * 16;
-                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                    for (int ii = 0; ii < KI; ii++) {
-                        uint32_t r[4];
-                        lds128(r, krow + ii * KCHUNK);
-                        mma16816(acc, qa[ii][0][0], qa[ii][0][1], qa[ii][0][2], qa[ii][0][3],
-                                 r[0], r[1]);
-                        mma16816(acc, qa[ii][1][0], qa[ii][1][1], qa[ii][1][2], qa[ii][1][3],
-                                 r[2], r[3]);
-                    }
-                    const int k0 = blk + 8 * c + 4 * mm + 2 * h;
-                    t[mm][h][0] = (k0 < k_end) ? (acc[0] + acc[2]) * p.sl2 : -CUDART_INF_F;
-                    t[mm][h][1] = (k0 + 1 < k_end) ? (acc[1] + acc[3]) * p.sl2 : -CUDART_INF_F;
+                for (int ii = 0; ii < KI; ii++) {
+                    uint32_t r[4];
+                    ldmatrix4(r, krow + (uint32_t)(ii >> 1) * KSUB +
+                                     (uint32_t)(((4 * (ii & 1) + lm) ^ li) << 4));
+                    mma16816(acc, qa[2 * ii][0], qa[2 * ii][1], qa[2 * ii][2], qa[2 * ii][3], r[0],
+                             r[1]);
+                    mma16816(acc, qa[2 * ii + 1][0], qa[2 * ii + 1][1], qa[2 * ii + 1][2],
+                             qa[2 * ii + 1][3], r[2], r[3]);
                 }
+                const int k0 = blk + 8 * T + 2 * c;
+                t[T][0] = (k0 < k_end) ? (acc[0] + acc[2]) * p.sl2 : -CUDART_INF_F;
+                t[T][1] = (k0 + 1 < k_end) ? (acc[1] + acc[3]) * p.sl2 : -CUDART_INF_F;
             }
 
             // ---- online softmax over the block -------------------------------------
             float bm = -CUDART_INF_F;
 #pragma unroll
-            for (int mm = 0; mm < 2; mm++) {
-#pragma unroll
-                for (int h = 0; h < 2; h++) bm = fmaxf(bm, fmaxf(t[mm][h][0], t[mm][h][1]));
-            }
+            for (int T = 0; T < 4; T++) bm = fmaxf(bm, fmaxf(t[T][0], t[T][1]));
             bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
             bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
             const float m_new = fmaxf(m, bm);
@@ -605,33 +597,36 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                 }
             }
             m = m_new;
+            // the probabilities of tiles 2u and 2u + 1 are the A operand of the
+            // value product over keys 16u..16u+15
             uint32_t pa[2][4];
 #pragma unroll
-            for (int mm = 0; mm < 2; mm++) {
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const float p0 = ex2(t[mm][h][0] - m);
-                    const float p1 = ex2(t[mm][h][1] - m);
-                    l += p0 + p1;
-                    split_pair(p0, p1, pa[mm][2 * h], pa[mm][2 * h + 1]);
-                }
+            for (int T = 0; T < 4; T++) {
+                const float p0 = ex2(t[T][0] - m);
+                const float p1 = ex2(t[T][1] - m);
+                l += p0 + p1;
+                split_pair(p0, p1, pa[T >> 1][2 * (T & 1)], pa[T >> 1][2 * (T & 1) + 1]);
             }
 
             // ---- context ---------------------------------------------------------------
-            const int nlive = k_end - (blk + 8 * c);   // keys of this thread's eight that exist
+            // Channel tile j is channels 8j..8j+7; one ldmatrix brings the block's
+            // 32 keys of them: register x holds keys 8x + 2c and 8x + 2c + 1.
+            const bool ragged = blk + 32 > k_end;
 #pragma unroll
             for (int j = 0; j < NT; j++) {
                 uint32_t r[4];
-                lds128(r, vs + (8 * j + g) * 64 + c * 16);
-                if (nlive < 8) {
+                const int d = 8 * j + li;
+                ldmatrix4(r, vs_s + (uint32_t)d * 64u + (uint32_t)((lm ^ ((d >> 1) & 3)) << 4));
+                if (ragged) {
                     // Capacity past the live keys may hold anything, and
                     // 0 * NaN is NaN: clear what lies beyond.
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        if (nlive <= 2 * e) {
-                            r[e] = 0u;
-                        } else if (nlive == 2 * e + 1) {
-                            r[e] &= 0x0000ffffu;
+                    for (int x = 0; x < 4; x++) {
+                        const int k0 = blk + 8 * x + 2 * c;
+                        if (k0 >= k_end) {
+                            r[x] = 0u;
+                        } else if (k0 + 1 >= k_end) {
+                            r[x] &= 0x0000ffffu;
                         }
                     }
                 }
@@ -695,9 +690,11 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                 }
                 return;
             }
-            __threadfence_system();
+            // One fence, by the thread that counts the pair, after the barrier:
+            // it orders every store the barrier ordered before it.
             __syncthreads();
             if (tid == 0) {
+                __threadfence_system();
                 const unsigned prev = atomicAdd(p.xch_done, 1u);
                 if (prev == (unsigned)(p.xch_pairs - 1)) {
                     *p.xch_done = 0u;
@@ -786,7 +783,7 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
 template <int HD>
 constexpr int ring_bytes()
 {
-    return kWarps * kStages * (32 * HD * 2 + HD * 64) + 128;   // + room to align the ring
+    return kWarps * kStages * (32 * HD * 2 + HD * 64) + 1024;   // + room to align the ring
 }
 
 const KernelReg reg_s128("attn_decode_h128_run", (const void *)decode_stream_kernel<128>);
@@ -797,17 +794,17 @@ const KernelReg reg_s64("attn_decode_h64_run", (const void *)decode_stream_kerne
 bool decode_tensor_maps(CUtensorMap *kmap, CUtensorMap *vmap, const void *k, const void *v,
                         int kv_heads, int cap, int hd)
 {
-    // keys: 32 halves of a row, then the rows of every kv head one after another
-    // (their stride is a whole row), then the row's hd/32 column chunks
-    const uint64_t kd[3] = {32, (uint64_t)kv_heads * (uint64_t)cap, (uint64_t)(hd / 32)};
-    const uint64_t ks[2] = {(uint64_t)hd * 2, 64};
-    const uint32_t kb[3] = {32, 32, (uint32_t)(hd / 32)};
-    if (!llmtie_encode_tiled_f16(kmap, 3, k, kd, ks, kb, false)) return false;
-    // values: a row of `cap` keys per (kv head, channel)
+    // keys: the rows of every kv head one after another; a box is 32 rows by 64
+    // channels (whole 128-byte lines), swizzled by the row
+    const uint64_t kd[2] = {(uint64_t)hd, (uint64_t)kv_heads * (uint64_t)cap};
+    const uint64_t ks[1] = {(uint64_t)hd * 2};
+    const uint32_t kb[2] = {64, 32};
+    if (!llmtie_encode_tiled_f16(kmap, 2, k, kd, ks, kb, 128)) return false;
+    // values: a row of `cap` keys per (kv head, channel); a box is hd rows by 32 keys
     const uint64_t vd[2] = {(uint64_t)cap, (uint64_t)kv_heads * (uint64_t)hd};
     const uint64_t vs[1] = {(uint64_t)cap * 2};
     const uint32_t vb[2] = {32, (uint32_t)hd};
-    return llmtie_encode_tiled_f16(vmap, 2, v, vd, vs, vb, false);
+    return llmtie_encode_tiled_f16(vmap, 2, v, vd, vs, vb, 64);
 }
 
 // Cuts the launch's units into one contiguous run a block.

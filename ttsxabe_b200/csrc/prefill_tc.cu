@@ -1018,7 +1018,7 @@ const KernelReg reg_tcm("flash_attn_h_merge", (const void *)prefill_merge_kernel
 }  // namespace
 
 bool llmtie_encode_tiled_f16(CUtensorMap *map, int rank, const void *base, const uint64_t *dims,
-                             const uint64_t *strides_bytes, const uint32_t *box, bool swizzle128)
+                             const uint64_t *strides_bytes, const uint32_t *box, int swizzle_bytes)
 {
     EncodeFn fn = encode_fn();
     if (!fn || rank < 1 || rank > 5) return false;
@@ -1032,7 +1032,9 @@ bool llmtie_encode_tiled_f16(CUtensorMap *map, int rank, const void *base, const
     }
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void *>(base), d, s,
               b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+              swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+              : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                    : CU_TENSOR_MAP_SWIZZLE_NONE,
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
