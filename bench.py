@@ -54,12 +54,12 @@ PREFILL_DRAM_BYTES_8K = 192.388e6 + 94.125e6
 
 # DRAM traffic of the dominant kernel from the ncu captures summarised under
 # profiles/. The decode entry is dram__bytes_read.sum + dram__bytes_write.sum
-# per algorithmic byte, captured on a batch 8 x 16384-key launch (537.30 MB read
-# + 4.54 MB written for 536.87 MB of KV) and scaled to the launch at hand, since
+# per algorithmic byte, captured on a batch 8 x 16384-key launch (537.31 MB read
+# + 4.40 MB written for 536.87 MB of KV) and scaled to the launch at hand, since
 # traffic grows in proportion to the keys streamed; a full-size launch is too
 # large to capture.
 NCU_TRAFFIC = {
-    "decode128k": (537.303e6 + 4.539e6) / 536.870912e6,
+    "decode128k": (537.309e6 + 4.404e6) / 536.870912e6,
     # bytes per launch of the 8192-position prefill on one GPU (32 / 8 heads),
     # captured at that size; a rank holding fewer KV heads moves that share
     "prefill8k": PREFILL_DRAM_BYTES_8K,
