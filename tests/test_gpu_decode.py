@@ -370,3 +370,43 @@ def test_the_twin_row_variant_fills_one_row_and_refuses_short_buffers(gpu):
     with pytest.raises(SliceOverrun):
         gpu.attn_decode_f16_q_row(dq, n, dk, dv, heads, kv, hd, tk, cap, scale, False, scratch, out,
                                   short, 1)
+
+
+@pytest.mark.parametrize("shape", [
+    # heads, kv, hd, batch, keys, capacity: 64 or 72 pairs of equal length
+    (32, 8, 128, 8, 3000, 3072), (64, 64, 64, 1, 2500, 2560), (36, 9, 128, 8, 2049, 2056),
+])
+def test_pairs_cut_over_clusters(gpu, shape):
+    """When the (sequence, KV head) pairs of a launch are all the same length
+    and two blocks a pair nearly fill the device, each pair goes to one
+    thread-block cluster whose two blocks merge through distributed shared
+    memory. Same answers as ever: the f64 oracle at the reference's bar, the
+    same bits on a second call, and poison in the unused capacity ignored."""
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, kv, hd, batch, tk, cap = shape
+    rng = np.random.default_rng(heads + tk)
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, batch * heads * hd)
+    kbits = [poison_f16_bits(O.round_f16(normal_f16(rng, kv * cap * hd)), kv, tk, hd, cap, False)
+             for _ in range(batch)]
+    vbits = [poison_f16_bits(O.round_f16(normal_f16(rng, kv * cap * hd)), kv, tk, hd, cap, True)
+             for _ in range(batch)]
+    ks, vs = [gpu.upload_u16(x) for x in kbits], [gpu.upload_u16(x) for x in vbits]
+    scratch = DecodeScratch()
+    dq = gpu.upload(q)
+    a = gpu.download(gpu.decode_batched(dq, ks, vs, [tk] * batch, [cap] * batch, heads, kv, hd,
+                                        scale, False, scratch)).reshape(batch, -1)
+    b = gpu.download(gpu.decode_batched(dq, ks, vs, [tk] * batch, [cap] * batch, heads, kv, hd,
+                                        scale, False, scratch)).reshape(batch, -1)
+    assert np.array_equal(a, b) and np.isfinite(a).all()
+    for s in range(batch):
+        want = O.decode_f64(q.reshape(batch, -1)[s], kbits[s], vbits[s], heads, kv, hd, 0, tk, cap,
+                            scale, False)
+        assert_close_to(f"pairs by cluster {shape} sequence {s}", want, a[s], 2e-5)
+    # the un-normalised triples of the same launch (what a sharded step exchanges)
+    tri = gpu.download(gpu.decode_batched(dq, ks, vs, [tk] * batch, [cap] * batch, heads, kv, hd,
+                                          scale, False, scratch, partial=True))
+    tri = tri.reshape(batch, heads, hd + 2)
+    got = tri[:, :, :hd] / tri[:, :, hd + 1:hd + 2]
+    assert np.abs(got.reshape(batch, -1) - a).max() <= 1e-6 * np.abs(a).max()

@@ -260,6 +260,11 @@ struct DecodeStreamParams {
     float *twin_s;
     int *status;                             // set when a wait on the ring's barriers gave up
     long long wait_cycles;                   // how long such a wait may spin
+    // Pairs by cluster (set by the launcher): every (sequence, KV head) pair is
+    // cut over the two blocks of one thread-block cluster, which merge through
+    // distributed shared memory; no run crosses a pair, no partial goes
+    // through global memory.
+    int by_cluster;
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
 // The two tensor maps the ring kernel reads one sequence's caches through:

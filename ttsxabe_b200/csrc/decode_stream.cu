@@ -396,6 +396,9 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     __shared__ float sm_m[kWarps][kRows];
     __shared__ float sm_l[kWarps][kRows];
     __shared__ int sm_last;
+    // pairs by cluster: both blocks' merged triples, the peer's through
+    // distributed shared memory
+    __shared__ __align__(16) float sm_pair[2][kRows][HD + 2];
     __shared__ int sm_dead;                // a cross-rank wait of this block ran out
     constexpr int kMineMax = 16;
     __shared__ int sm_mine[kMineMax][3];   // pairs this block finished: pair, first row, rows
@@ -722,6 +725,22 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
             if (whole) {
                 emit(row, d, O, M, L);
+            } else if (p.by_cluster) {
+                // into the leading block's shared memory, slot = this block's rank
+                uint32_t crank;
+                asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+                const uint32_t mine = smem_u32(&sm_pair[crank][row][0]);
+                uint32_t there;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(there) : "r"(mine));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(there + 4u * d), "f"(O)
+                             : "memory");
+                if (d == 0) {
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(there + 4u * HD), "f"(M)
+                                 : "memory");
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(there + 4u * (HD + 1)),
+                                 "f"(L)
+                                 : "memory");
+                }
             } else {
                 float *pr = part + row * (HD + 2);
                 pr[d] = O;
@@ -733,7 +752,25 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         }
 
         if (whole) pair_done();
-        if (!whole) {
+        if (!whole && p.by_cluster) {
+            // ---- the cluster's two blocks meet; the leading one merges -------------------
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            uint32_t crank;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+            if (crank == 0) {
+                for (int idx = tid; idx < rows_here * HD; idx += kThreads) {
+                    const int row = idx / HD, d = idx % HD;
+                    const float m0 = sm_pair[0][row][HD], m1 = sm_pair[1][row][HD];
+                    const float M = fmaxf(m0, m1);
+                    const float f0 = (m0 == -CUDART_INF_F) ? 0.0f : ex2(m0 - M);
+                    const float f1 = (m1 == -CUDART_INF_F) ? 0.0f : ex2(m1 - M);
+                    emit(row, d, f0 * sm_pair[0][row][d] + f1 * sm_pair[1][row][d], M,
+                         f0 * sm_pair[0][row][HD + 1] + f1 * sm_pair[1][row][HD + 1]);
+                }
+                pair_done();
+            }
+        } else if (!whole) {
             // ---- the last block of this pair to arrive merges every partial -------------
             const int c_first = block_of(sm_ustart, pair_u0, G);
             const int c_last = block_of(sm_ustart, pair_u0 + n_units - 1, G);
@@ -890,6 +927,30 @@ extern "C" llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size
     return LLMTIE_OK;
 }
 
+// Whether the launch goes pair by cluster: every sequence the same length,
+// two blocks a pair filling at least four fifths of the SMs, and runs short
+// enough (at most 256 units a block) for the launch's fixed costs to matter -
+// a long launch is bound by HBM either way and does better on every SM.
+static bool cluster_cut(DecodeStreamParams &p, int sm_count, int *grid)
+{
+    static const bool never = getenv("LLMTIE_B200_DECODE_NO_CLUSTER") != nullptr;
+    const long long pairs = (long long)p.nseq * p.kv_heads * p.row_chunks;
+    if (never || pairs * 2 > sm_count || pairs * 2 * 5 < (long long)sm_count * 4) return false;
+    const int n = (p.seq[0].tk + 127) / 128;
+    for (int b = 1; b < p.nseq; b++) {
+        if ((p.seq[b].tk + 127) / 128 != n) return false;
+    }
+    if (n < 16 || n > 512 || pairs * 2 > LLMTIE_STREAM_MAX_BLOCKS) return false;
+    for (long long q = 0; q < pairs; q++) {
+        p.ustart[2 * q] = (int)(q * n);
+        p.ustart[2 * q + 1] = (int)(q * n + (n + 1) / 2);
+    }
+    p.ustart[2 * pairs] = (int)(pairs * n);
+    p.by_cluster = 1;
+    *grid = (int)(2 * pairs);
+    return true;
+}
+
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in, int hd, int grid)
 {
     if (grid < 1 || grid > LLMTIE_STREAM_MAX_BLOCKS || p_in.total_units > 0x7fffffffLL ||
@@ -897,11 +958,13 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in
         return cudaErrorInvalidValue;
     }
     DecodeStreamParams p = p_in;
-    stream_partition(p, hd, grid);
+    p.by_cluster = 0;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (!cluster_cut(p, sms, &grid)) stream_partition(p, hd, grid);
 
     static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaFuncSetAttribute(decode_stream_kernel<128>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes<128>());
@@ -909,12 +972,21 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in
                              cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes<64>());
         configured[dev] = true;
     }
-    if (hd == 128) {
-        decode_stream_kernel<128><<<grid, kThreads, ring_bytes<128>(), st>>>(p);
-    } else {
-        decode_stream_kernel<64><<<grid, kThreads, ring_bytes<64>(), st>>>(p);
-    }
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = hd == 128 ? ring_bytes<128>() : ring_bytes<64>();
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.by_cluster ? 1 : 0;
+    return hd == 128 ? cudaLaunchKernelEx(&cfg, decode_stream_kernel<128>, p)
+                     : cudaLaunchKernelEx(&cfg, decode_stream_kernel<64>, p);
 }
 
 // ---- a decode entry point that allocates nothing -----------------------------------
