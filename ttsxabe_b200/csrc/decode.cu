@@ -592,12 +592,15 @@ __global__ void lse_merge_pairs_kernel(const float *__restrict__ gather, const u
     if ((int)threadIdx.x < world) {
         const unsigned *f = pflags + (size_t)(row / rows_per_pair) * world + threadIdx.x;
         const long long t0 = clock64();
+        // (polled at leisure: these blocks sit beside a kernel that is still
+        // streaming, and a flag only matters once it is up)
         while ((int)(ld_acquire_sys(f) - (step + 1u)) < 0) {
             if (clock64() - t0 > wait_cycles) {
                 s_ok = 0;
                 report_timeout(status, 90 + (int)threadIdx.x);
                 break;
             }
+            __nanosleep(200);
         }
     }
     __syncthreads();
