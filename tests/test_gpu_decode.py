@@ -199,7 +199,7 @@ def test_partial_triples_merge_to_the_whole(gpu):
     assert_close_to("merged partials", want, merged, 2e-5)
 
 
-@pytest.mark.parametrize("mode", ["push", "pairs"])
+@pytest.mark.parametrize("mode", ["push", "pairs", "push-clusters"])
 def test_peer_push_exchange_on_one_device(gpu, mode):
     """The fused multi-GPU exchange, with both "ranks" on one device: each rank
     decodes its slice of the keys and pushes its triples into every rank's
@@ -215,11 +215,14 @@ def test_peer_push_exchange_on_one_device(gpu, mode):
     from ttsxabe_b200 import DecodeScratch, Exchange
 
     heads, kv, hd, batch, world = 32, 8, 128, 3, 2
+    per = [1000, 1536]                     # keys held by rank 0 and rank 1
+    caps = [1024, 1536]
+    if mode == "push-clusters":
+        # 64 pairs of equal length a rank: the launch that goes pair by cluster
+        batch, per, caps, mode = 8, [2048, 2304], [2048, 2304], "push"
     rows = batch * heads
     rng = np.random.default_rng(91)
     scale = float(np.float32(hd) ** np.float32(-0.5))
-    per = [1000, 1536]                     # keys held by rank 0 and rank 1
-    caps = [1024, 1536]
     kfull = [normal_f16(rng, kv * sum(per) * hd).reshape(kv, sum(per), hd) for _ in range(batch)]
     vfull = [normal_f16(rng, kv * sum(per) * hd).reshape(kv, sum(per), hd) for _ in range(batch)]
     with torch.cuda.stream(gpu.stream):

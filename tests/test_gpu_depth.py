@@ -195,3 +195,29 @@ def test_cut_row_blocks_merge_to_the_same_answer(gpu, tq, past, heads, kv):
                          HD, cap, SCALE, True)
         assert_parity(f"cut prefill {tq}+{past} rows {r0}..{r0 + 16}", want,
                       got[r0:r0 + 16].reshape(-1))
+
+
+def test_cut_row_blocks_in_a_ragged_batch(gpu):
+    """The same cut through the ragged entry: two sequences of two query heads
+    over one KV head (so few blocks that their row blocks are cut), RoPE and
+    the cache write included, every row against the oracle."""
+    heads, kv = 2, 1
+    lens = [1500, 900]
+    rng = np.random.default_rng(5)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    total = int(cu[-1])
+    q = normal_f16(rng, total * heads * HD)
+    k = normal_f16(rng, total * kv * HD)
+    v = normal_f16(rng, total * kv * HD)
+    cap = 1504
+    kcs = [gpu.zeros_f16(kv * cap * HD) for _ in lens]
+    vcs = [gpu.zeros_f16(kv * cap * HD) for _ in lens]
+    out = gpu.prefill_varlen(gpu.upload(q), gpu.upload(k), gpu.upload(v), cu, kcs, vcs, [0, 0],
+                             [cap, cap], None, heads, kv, HD, 10000.0, SCALE)
+    got = gpu.download(out).reshape(total, heads * HD)
+    for b, n in enumerate(lens):
+        r0 = int(cu[b])
+        qr = O.rope(q.reshape(total, -1)[r0:r0 + n].reshape(-1), n, heads, HD, 10000.0, 0)
+        want = O.prefill(qr, gpu.download_u16(kcs[b]), gpu.download_u16(vcs[b]), n, 0, heads, kv, HD,
+                         cap, SCALE, True, fast=True)
+        assert_parity(f"ragged cut prefill, sequence {b}", want, got[r0:r0 + n].reshape(-1))
