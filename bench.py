@@ -353,7 +353,7 @@ def decode128k(args, world, rank, local):
         out = e2e_enqueue()
         lib.llmtie_download(h, hout.data_ptr(), out.data_ptr(), batch * nq * esz)
 
-    e2e_graph = bool(world > 1 and not args.no_graph)
+    e2e_graph = not args.no_graph
     if e2e_graph:
         # The same calls - the copy in from pinned host memory, RoPE and the
         # cache write, attention, exchange and merge, the copy out - recorded
