@@ -113,6 +113,24 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+// The waiting form: the thread is suspended by the hardware until the phase
+// completes or a time limit of the hardware's own runs out (then: false), so a
+// waiting warp takes no issue slots from the warp that shares its scheduler.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait: a plain poll of the barrier's phase with no sleep of its own
 // (nanosleep's granularity is far coarser than the few hundred nanoseconds a
 // pipeline step lasts). The bound is a deadline in
@@ -131,8 +149,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     if (mbar_try(bar, parity)) return true;
     const long long start = clock64();
     for (uint32_t it = 1;; it++) {
-        if (mbar_try(bar, parity)) return true;
-        if ((it & 255u) == 0) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 15u) == 0) {
             if (*w.abort_flag) return false;
             if (clock64() - start > w.cycles) break;
         }
