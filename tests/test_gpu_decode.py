@@ -378,11 +378,16 @@ def test_the_twin_row_variant_fills_one_row_and_refuses_short_buffers(gpu):
 @pytest.mark.parametrize("shape", [
     # heads, kv, hd, batch, keys, capacity: 64 or 72 pairs of equal length
     (32, 8, 128, 8, 3000, 3072), (64, 64, 64, 1, 2500, 2560), (36, 9, 128, 8, 2049, 2056),
+    # a few short pairs: eight blocks a pair (8 pairs of 24 units), four (16 of 13, 32 of 20,
+    # 10 of 12 at head_dim 64), a pair count that leaves eight too few units a block
+    (32, 8, 128, 1, 3000, 3072), (32, 8, 128, 2, 1600, 1600), (32, 8, 128, 4, 2500, 2560),
+    (20, 10, 64, 1, 1500, 1504), (32, 8, 128, 1, 2049, 2056),
 ])
 def test_pairs_cut_over_clusters(gpu, shape):
     """When the (sequence, KV head) pairs of a launch are all the same length
-    and two blocks a pair nearly fill the device, each pair goes to one
-    thread-block cluster whose two blocks merge through distributed shared
+    and two blocks a pair nearly fill the device - or the pairs are few and
+    short, and four or eight blocks a pair fit - each pair goes to one
+    thread-block cluster whose blocks merge through distributed shared
     memory. Same answers as ever: the f64 oracle at the reference's bar, the
     same bits on a second call, and poison in the unused capacity ignored."""
     from ttsxabe_b200 import DecodeScratch

@@ -260,10 +260,10 @@ struct DecodeStreamParams {
     float *twin_s;
     int *status;                             // set when a wait on the ring's barriers gave up
     long long wait_cycles;                   // how long such a wait may spin
-    // Pairs by cluster (set by the launcher): every (sequence, KV head) pair is
-    // cut over the two blocks of one thread-block cluster, which merge through
-    // distributed shared memory; no run crosses a pair, no partial goes
-    // through global memory.
+    // Pairs by cluster (set by the launcher; 0 or the cluster's size: 2, 4 or
+    // 8): every (sequence, KV head) pair is cut over the blocks of one
+    // thread-block cluster, which merge through distributed shared memory; no
+    // run crosses a pair, no partial goes through global memory.
     int by_cluster;
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);

@@ -37,6 +37,7 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <mutex>
 #include <stdlib.h>
 #include <string.h>
 
@@ -376,6 +377,8 @@ __device__ __noinline__ void cross_merge(const DecodeStreamParams &p, int pair, 
     }
 }
 
+constexpr int kClusterMax = 8;   // blocks a pair at most (the portable cluster size)
+
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
@@ -396,8 +399,10 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     __shared__ float sm_m[kWarps][kRows];
     __shared__ float sm_l[kWarps][kRows];
     __shared__ int sm_last;
-    // pairs by cluster: both blocks' merged triples, the peer's through
-    // distributed shared memory
+    // Pairs by cluster. Two blocks a pair: both blocks' merged triples in the
+    // leading block's slots, the peer's pushed there through distributed shared
+    // memory. More blocks a pair: every block keeps its triple in its own
+    // slot 0 and the leading block fetches them.
     __shared__ __align__(16) float sm_pair[2][kRows][HD + 2];
     __shared__ int sm_dead;                // a cross-rank wait of this block ran out
     constexpr int kMineMax = 16;
@@ -725,6 +730,12 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
             }
             if (whole) {
                 emit(row, d, O, M, L);
+            } else if (p.by_cluster > 2) {
+                sm_pair[0][row][d] = O;
+                if (d == 0) {
+                    sm_pair[0][row][HD] = M;
+                    sm_pair[0][row][HD + 1] = L;
+                }
             } else if (p.by_cluster) {
                 // into the leading block's shared memory, slot = this block's rank
                 uint32_t crank;
@@ -752,7 +763,58 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         }
 
         if (whole) pair_done();
-        if (!whole && p.by_cluster) {
+        if (!whole && p.by_cluster > 2) {
+            // ---- the cluster's blocks meet; the leading one fetches and merges ----------
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            uint32_t crank;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+            if (crank == 0) {
+                const int C = p.by_cluster;
+                for (int idx = tid; idx < rows_here * HD; idx += kThreads) {
+                    const int row = idx / HD, d = idx % HD;
+                    const uint32_t mine = smem_u32(&sm_pair[0][row][0]);
+                    // every block's three words of this value are asked for at once
+                    float mi[kClusterMax], li[kClusterMax], oi[kClusterMax];
+#pragma unroll
+                    for (int r = 0; r < kClusterMax; r++) {
+                        uint32_t there;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                                     : "=r"(there)
+                                     : "r"(mine), "r"((uint32_t)min(r, C - 1)));
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];"
+                                     : "=f"(mi[r])
+                                     : "r"(there + 4u * HD)
+                                     : "memory");
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];"
+                                     : "=f"(li[r])
+                                     : "r"(there + 4u * (HD + 1))
+                                     : "memory");
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];"
+                                     : "=f"(oi[r])
+                                     : "r"(there + 4u * d)
+                                     : "memory");
+                    }
+                    float M = -CUDART_INF_F;
+#pragma unroll
+                    for (int r = 0; r < kClusterMax; r++) M = fmaxf(M, mi[r]);   // repeats are harmless
+                    float O = 0.0f, L = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < kClusterMax; r++) {
+                        if (r < C) {
+                            const float f = (mi[r] == -CUDART_INF_F) ? 0.0f : ex2(mi[r] - M);
+                            O += f * oi[r];
+                            L += f * li[r];
+                        }
+                    }
+                    emit(row, d, O, M, L);
+                }
+                pair_done();
+            }
+            // nobody's slot is reused (or goes away with its block) before it was read
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        } else if (!whole && p.by_cluster) {
             // ---- the cluster's two blocks meet; the leading one merges -------------------
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -927,27 +989,75 @@ extern "C" llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size
     return LLMTIE_OK;
 }
 
-// Whether the launch goes pair by cluster: every sequence the same length,
-// two blocks a pair filling at least four fifths of the SMs, and runs short
-// enough (at most 256 units a block) for the launch's fixed costs to matter -
-// a long launch is bound by HBM either way and does better on every SM.
-static bool cluster_cut(DecodeStreamParams &p, int sm_count, int *grid)
+// How many clusters of `c` blocks of this kernel the device holds at once
+// (a cluster needs its SMs in one GPC, so this is less than SMs / c); asked of
+// the driver once per device, width and size.
+static int resident_clusters(int dev, int hd, int c)
+{
+    static int memo[64][2][kClusterMax + 1];   // 0: not asked yet
+    static std::mutex lock;
+    if (dev < 0 || dev >= 64 || c < 1 || c > kClusterMax) return 0;
+    std::lock_guard<std::mutex> hold(lock);
+    int &slot = memo[dev][hd == 128 ? 1 : 0][c];
+    if (slot == 0) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(c * 64);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = hd == 128 ? ring_bytes<128>() : ring_bytes<64>();
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = c;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        const cudaError_t e =
+            hd == 128 ? cudaOccupancyMaxActiveClusters(&n, decode_stream_kernel<128>, &cfg)
+                      : cudaOccupancyMaxActiveClusters(&n, decode_stream_kernel<64>, &cfg);
+        slot = (e == cudaSuccess && n > 0) ? n : -1;
+        if (e != cudaSuccess) cudaGetLastError();
+    }
+    return slot > 0 ? slot : 0;
+}
+
+// Whether the launch goes pair by cluster: every sequence the same length, and
+// either two blocks a pair filling at least four fifths of the SMs, with runs
+// short enough (at most 256 units a block) for the launch's fixed costs to
+// matter - a long launch is bound by HBM either way and does better on every
+// SM - or, for a few short pairs (a few sequences of a few thousand keys,
+// where the step is nothing but latency), as many blocks a pair - eight, four
+// or two - as leaves every block a unit and all clusters resident at once.
+static bool cluster_cut(DecodeStreamParams &p, int dev, int hd, int sm_count, int *grid)
 {
     static const bool never = getenv("LLMTIE_B200_DECODE_NO_CLUSTER") != nullptr;
     const long long pairs = (long long)p.nseq * p.kv_heads * p.row_chunks;
-    if (never || pairs * 2 > sm_count || pairs * 2 * 5 < (long long)sm_count * 4) return false;
+    if (never) return false;
     const int n = (p.seq[0].tk + 127) / 128;
     for (int b = 1; b < p.nseq; b++) {
         if ((p.seq[b].tk + 127) / 128 != n) return false;
     }
-    if (n < 16 || n > 512 || pairs * 2 > LLMTIE_STREAM_MAX_BLOCKS) return false;
-    for (long long q = 0; q < pairs; q++) {
-        p.ustart[2 * q] = (int)(q * n);
-        p.ustart[2 * q + 1] = (int)(q * n + (n + 1) / 2);
+    int C = 0;
+    if (pairs * 2 <= sm_count && pairs * 2 * 5 >= (long long)sm_count * 4 && n >= 16 && n <= 512) {
+        C = 2;
+    } else if (n <= 64) {
+        for (int c = kClusterMax; c >= 2 && C == 0; c >>= 1) {
+            if (n >= c && pairs * c >= 32 && pairs * c <= sm_count &&
+                pairs <= resident_clusters(dev, hd, c)) {
+                C = c;
+            }
+        }
     }
-    p.ustart[2 * pairs] = (int)(pairs * n);
-    p.by_cluster = 1;
-    *grid = (int)(2 * pairs);
+    if (C == 0 || pairs * C > LLMTIE_STREAM_MAX_BLOCKS) return false;
+    for (long long q = 0; q < pairs; q++) {
+        for (int i = 0; i < C; i++) {
+            p.ustart[C * q + i] = (int)(q * n + ((long long)i * n + C - 1) / C);
+        }
+    }
+    p.ustart[C * pairs] = (int)(pairs * n);
+    p.by_cluster = C;
+    *grid = (int)(C * pairs);
     return true;
 }
 
@@ -962,8 +1072,6 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (!cluster_cut(p, sms, &grid)) stream_partition(p, hd, grid);
-
     static bool configured[64] = {false};
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaFuncSetAttribute(decode_stream_kernel<128>,
@@ -972,6 +1080,7 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in
                              cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes<64>());
         configured[dev] = true;
     }
+    if (!cluster_cut(p, dev, hd, sms, &grid)) stream_partition(p, hd, grid);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(grid);
@@ -980,7 +1089,7 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.x = p.by_cluster ? p.by_cluster : 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
