@@ -1034,28 +1034,38 @@ static bool cluster_cut(DecodeStreamParams &p, int dev, int hd, int sm_count, in
     static const bool never = getenv("LLMTIE_B200_DECODE_NO_CLUSTER") != nullptr;
     const long long pairs = (long long)p.nseq * p.kv_heads * p.row_chunks;
     if (never) return false;
-    const int n = (p.seq[0].tk + 127) / 128;
+    int n = (p.seq[0].tk + 127) / 128, n_max = n;     // fewest and most units of a pair
     for (int b = 1; b < p.nseq; b++) {
-        if ((p.seq[b].tk + 127) / 128 != n) return false;
+        n = std::min(n, (p.seq[b].tk + 127) / 128);
+        n_max = std::max(n_max, (p.seq[b].tk + 127) / 128);
     }
+    const bool even = n == n_max;
     int C = 0;
-    if (pairs * 2 <= sm_count && pairs * 2 * 5 >= (long long)sm_count * 4 && n >= 16 && n <= 512) {
+    if (even && pairs * 2 <= sm_count && pairs * 2 * 5 >= (long long)sm_count * 4 && n >= 16 &&
+        n <= 512) {
         C = 2;
-    } else if (n <= 64) {
+    } else if (n_max <= 64) {
+        // (sequences of unequal length: only while the longest run stays
+        // short - eight units - since the clusters then end at different times)
         for (int c = kClusterMax; c >= 2 && C == 0; c >>= 1) {
             if (n >= c && pairs * c >= 32 && pairs * c <= sm_count &&
-                pairs <= resident_clusters(dev, hd, c)) {
+                pairs <= resident_clusters(dev, hd, c) && (even || (n_max + c - 1) / c <= 8)) {
                 C = c;
             }
         }
     }
     if (C == 0 || pairs * C > LLMTIE_STREAM_MAX_BLOCKS) return false;
-    for (long long q = 0; q < pairs; q++) {
-        for (int i = 0; i < C; i++) {
-            p.ustart[C * q + i] = (int)(q * n + ((long long)i * n + C - 1) / C);
+    const int inner = p.kv_heads * p.row_chunks;
+    for (int b = 0; b < p.nseq; b++) {
+        const long long nb = (p.seq[b].tk + 127) / 128;
+        for (int q = 0; q < inner; q++) {
+            const long long at = (long long)(p.pair0[b] + q) * C;
+            for (int i = 0; i < C; i++) {
+                p.ustart[at + i] = (int)(p.unit0[b] + q * nb + (i * nb + C - 1) / C);
+            }
         }
     }
-    p.ustart[C * pairs] = (int)(pairs * n);
+    p.ustart[C * pairs] = (int)p.total_units;
     p.by_cluster = C;
     *grid = (int)(C * pairs);
     return true;
