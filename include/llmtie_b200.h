@@ -399,7 +399,10 @@ llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_exchange *xch, s
  * grid_out = blocks launched on a device of sm_count SMs, ustart[c] = the
  * first 128-key unit of block c, ustart[grid] = all units. Units are laid end
  * to end, sequence after sequence, KV head after KV head. For tests and for
- * sizing scratch ahead of time (a launch uses 2*grid partial slots). */
+ * sizing scratch ahead of time (a launch uses 2*grid partial slots). This is
+ * the cut by work; a launch whose pairs are few and short, or all of one
+ * length and about half as many as the SMs, gives every pair a thread-block
+ * cluster of 2, 4 or 8 blocks instead, which writes no partials at all. */
 llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size_t kv_heads,
                                 size_t head_dim, int32_t sm_count, int32_t *ustart,
                                 size_t ustart_len, int32_t *grid_out);
