@@ -201,7 +201,7 @@ def test_partial_triples_merge_to_the_whole(gpu):
     assert_close_to("merged partials", want, merged, 2e-5)
 
 
-@pytest.mark.parametrize("mode", ["push", "pairs", "push-clusters"])
+@pytest.mark.parametrize("mode", ["push", "pairs", "push-clusters", "push-wide-clusters"])
 def test_peer_push_exchange_on_one_device(gpu, mode):
     """The fused multi-GPU exchange, with both "ranks" on one device: each rank
     decodes its slice of the keys and pushes its triples into every rank's
@@ -222,6 +222,9 @@ def test_peer_push_exchange_on_one_device(gpu, mode):
     if mode == "push-clusters":
         # 64 pairs of equal length a rank: the launch that goes pair by cluster
         batch, per, caps, mode = 8, [2048, 2304], [2048, 2304], "push"
+    if mode == "push-wide-clusters":
+        # 8 short pairs a rank: eight blocks a pair, the leading one fetches and pushes
+        batch, per, caps, mode = 1, [3000, 2944], [3008, 2944], "push"
     rows = batch * heads
     rng = np.random.default_rng(91)
     scale = float(np.float32(hd) ** np.float32(-0.5))
