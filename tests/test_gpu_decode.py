@@ -326,6 +326,9 @@ def test_fused_exchange_with_a_world_of_one(gpu, shape):
     # context cut over many blocks
     (8, 2, 128, 40, 64), (8, 2, 128, 1000, 1024), (4, 4, 64, 300, 512),
     (20, 20, 64, 1500, 1500), (32, 8, 128, 40000, 40960),
+    # few short pairs: clusters of eight blocks (and of four at head_dim 64), whose leading
+    # block writes the twin
+    (32, 8, 128, 3000, 3008), (20, 20, 64, 1500, 1504),
 ])
 def test_the_decode_twin_is_the_quantiser_over_its_output(gpu, shape):
     """attn_decode_f16_q: the context is bit for bit what attn_decode_f16
