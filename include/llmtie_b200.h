@@ -472,8 +472,7 @@ llmtie_status llmtie_cross_attn(llmtie_gpu *g, const float *q, size_t q_len,
  * all three unrotated and none of them written (the reference's chain rotates
  * q in place; here q is rotated on its way into the attention kernel, in two
  * launches where the caches are 16-byte aligned with capacities that are
- * multiples of 8 and every sequence holds 128 keys or more, and a copy of it
- * otherwise). cu_seqlens HOST int32 [batch+1], past/cap/k_ptrs/v_ptrs HOST
+ * multiples of 8, and a copy of it otherwise). cu_seqlens HOST int32 [batch+1], past/cap/k_ptrs/v_ptrs HOST
  * arrays; out f32 [total][heads*hd]. */
 llmtie_status llmtie_prefill_varlen(llmtie_gpu *g, const float *q, size_t q_len, const float *k,
                                     size_t k_len, const float *v, size_t v_len,

@@ -25,6 +25,11 @@ SIZED = [
     (8, 1, 128, True, 90, 17, 128, True),
     (4, 4, 128, True, 200, 40, 256, True),
     (4, 2, 128, True, 130, 5, 138, True),
+    # prompts shorter than a tile of the tensor-memory kernel (its boxes are wider than the caches)
+    (8, 2, 128, True, 8, 0, 64, True),
+    (8, 2, 128, True, 1, 0, 8, True),
+    (8, 2, 128, True, 30, 33, 64, True),
+    (8, 2, 128, False, 70, 0, 72, True),
     (4, 4, 64, False, 300, 0, 300, False),
     # crates/llmtie-cosy's callers, both off f32 caches: the speech LM's prefill
     # (14 / 2 heads, a group of 7; src/llm.rs:448-475) and the flow model's
@@ -167,6 +172,57 @@ def test_config2_ragged_batched_prefill(gpu):
     want64 = O.prefill(qr, gpu.download_u16(kcs[0]), gpu.download_u16(vcs[0]), n, 0, heads, kv,
                        hd, cap, scale, True)
     assert_parity("config 2 sequence 0 (f64 oracle)", want64, got[:n].reshape(-1))
+
+
+def test_ragged_prefill_of_short_prompts(gpu):
+    """Prompts of a few tokens, some onto a kept prefix: every sequence is
+    shorter than one 128-key tile, so every tensor map is narrower than its
+    box. Same chain, same bar as config 2; the caller's q is not written."""
+    heads, kv, hd = 32, 8, 128
+    lens = [1, 5, 40, 100, 127, 64]
+    pasts = [0, 0, 17, 0, 0, 60]
+    batch = len(lens)
+    rng = np.random.default_rng(77)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    total = int(cu[-1])
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, total * heads * hd)
+    k = normal_f16(rng, total * kv * hd)
+    v = normal_f16(rng, total * kv * hd)
+    cap = 128
+    olds = []
+    kcs, vcs = [], []
+    for b in range(batch):
+        # what the kept prefix holds (already rotated keys, transposed values)
+        kc = np.zeros(kv * cap * hd, np.uint16)
+        vc = np.zeros(kv * cap * hd, np.uint16)
+        if pasts[b]:
+            O.cache_append_f16(normal_f16(rng, pasts[b] * kv * hd), kc, pasts[b], kv, hd, cap, 0, False)
+            O.cache_append_f16(normal_f16(rng, pasts[b] * kv * hd), vc, pasts[b], kv, hd, cap, 0, True)
+        olds.append((kc, vc))
+        kcs.append(gpu.upload_u16(kc))
+        vcs.append(gpu.upload_u16(vc))
+    dq = gpu.upload(q)
+    out = gpu.prefill_varlen(dq, gpu.upload(k), gpu.upload(v), cu, kcs, vcs, pasts, [cap] * batch,
+                             None, heads, kv, hd, 10000.0, scale)
+    got = gpu.download(out).reshape(total, heads * hd)
+    assert np.array_equal(gpu.download(dq), q)
+    for b in range(batch):
+        n, r0, past = lens[b], int(cu[b]), pasts[b]
+        qb = q.reshape(total, -1)[r0:r0 + n].reshape(-1)
+        kb = k.reshape(total, -1)[r0:r0 + n].reshape(-1)
+        vb = v.reshape(total, -1)[r0:r0 + n].reshape(-1)
+        qr = O.rope(qb, n, heads, hd, 10000.0, past)
+        kr = O.rope(kb, n, kv, hd, 10000.0, past)
+        kc, vc = olds[b][0].copy(), olds[b][1].copy()
+        O.cache_append_f16(kr, kc, n, kv, hd, cap, past, False)
+        O.cache_append_f16(vb, vc, n, kv, hd, cap, past, True)
+        assert np.array_equal(gpu.download_u16(vcs[b]), vc)
+        # attention over the cache as the device left it (its sincosf and the
+        # host's differ in the last bit of a rotated key)
+        want = O.prefill(qr, gpu.download_u16(kcs[b]), vc, n, past, heads, kv, hd, cap, scale, True)
+        assert_parity(f"short prompt {b} ({n} tokens on {past})", want, got[r0:r0 + n].reshape(-1))
+        assert np.abs(O.widen_f16(gpu.download_u16(kcs[b])) - O.widen_f16(kc)).max() <= 4e-3
 
 
 def test_ragged_prefill_of_more_sequences_than_one_launch_maps(gpu):

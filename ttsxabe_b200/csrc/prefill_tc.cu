@@ -1064,8 +1064,8 @@ bool prefill_tc_eligible(const PrefillParams &p, int hd)
     if (((uintptr_t)p.out & 15u) != 0 || (p.out_stride & (p.out_f16 ? 7 : 3)) != 0) return false;
     for (int b = 0; b < p.nseq; b++) {
         if (p.seq[b].cap % 8 != 0) return false;
-        // short sequences stay with the general kernel (a box wider than the tensor)
-        if ((p.causal ? p.seq[b].past + p.seq[b].tq : p.seq[b].tk) < 128) return false;
+        // (a sequence shorter than a tile is fine: a box may be wider than its
+        // tensor, and what it reads past the live keys is zeros)
         if (((uintptr_t)p.seq[b].k & 15u) != 0 || ((uintptr_t)p.seq[b].v & 15u) != 0) return false;
     }
     return encode_fn() != nullptr;
