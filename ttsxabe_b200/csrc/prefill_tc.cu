@@ -220,6 +220,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32])
         : "r"(addr)
         : "memory");
 }
+// Sixteen lanes by 64 columns in the accumulator-fragment layout: lane i of
+// the warp gets, for each group j of eight columns, columns 8j + 2(i % 4) and
+// the next of tensor-memory lane i / 4 (r[4j], r[4j + 1]) and of lane
+// i / 4 + 8 (r[4j + 2], r[4j + 3]). Four lanes hold 32 consecutive bytes of a
+// row, which is what makes a store straight from these registers whole sectors.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t addr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32])
 {
     asm volatile(
@@ -688,71 +707,83 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                 const long long ptile =
                     ((long long)p.pslot[blockIdx.y] * gridDim.x + blockIdx.x) * 2 + t;
                 if (part) p.part_ml[ptile * BM + row] = make_float2(m_ref * sl2, l);
-                // A thread holds a row, and rows lie heads*hd elements apart: stored
-                // straight from the registers every 16-byte store of a warp would
-                // open its own line. So each warp turns its 32 rows through shared
-                // memory - its quarter of the
-                // tile's Q, which no MMA reads any more - and stores whole row
-                // segments of RB bytes, a row per LPR lanes. 16-byte chunks are
-                // swizzled by the row so that neither side has bank conflicts.
-                constexpr int RB = HD * 2;                 // bytes of a row a pass moves
-                constexpr int LPR = RB / 16;               // lanes to a row on the way out
-                constexpr int RPI = 32 / LPR;              // rows an instruction stores
-                const uint32_t scratch = q_smem(t) + (uint32_t)(warp & 3) * (32u * RB);
                 const bool out16 = p.out_f16 && !part;
+                const long long ostride = part ? HD : p.out_stride;      // elements
                 const int esize = out16 ? 2 : 4;
-                const int passes = HD * esize / RB;        // 1 for f16, 2 for f32
-                const long long ostride = part ? HD : p.out_stride;
                 unsigned char *obase =
                     part ? (unsigned char *)(p.part_o + (ptile * BM + 32 * (warp & 3)) * HD)
                          : (unsigned char *)p.out +
                                ((long long)(sq.row0 + me.r0 + 32 * (warp & 3)) * p.out_stride +
                                 me.head * HD) * esize;
-                for (int ps = 0; ps < passes; ps++) {
-                    // ---- registers -> shared: this lane's row, RB bytes of it ------------
-                    if (out16) {
+                if (!out16) {
+                    // f32 rows go out straight from the registers, read from tensor
+                    // memory in the fragment layout: four lanes write the 32 bytes
+                    // of a sector, a warp instruction eight rows of them. (A row's
+                    // 1 / l lives in the lane that owns the row in the softmax's
+                    // layout.)
+                    const int fr = lane >> 2, fc = 2 * (lane & 3);
 #pragma unroll
-                        for (int c = 0; c < HD / 32; c++) {
+                    for (int half = 0; half < 2; half++) {
+                        const int ra = 16 * half + fr, rb = ra + 8;      // rows within the warp's 32
+                        const float inv_a = __shfl_sync(0xffffffffu, inv, ra);
+                        const float inv_b = __shfl_sync(0xffffffffu, inv, rb);
+                        const bool live_a = part || me.r0 + 32 * (warp & 3) + ra < sq.tq;
+                        const bool live_b = part || me.r0 + 32 * (warp & 3) + rb < sq.tq;
+                        float *pa = (float *)(obase + (long long)ra * ostride * 4) + fc;
+                        float *pb = (float *)(obase + (long long)rb * ostride * 4) + fc;
+#pragma unroll
+                        for (int cg = 0; cg < HD / 64; cg++) {
                             uint32_t o[32];
-                            tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
+                            tmem_ld_16x256b_x8(lane_addr + ((uint32_t)(16 * half) << 16) + o_col(t) +
+                                                   64u * cg,
+                                               o);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                uint32_t v0 = pack_f16(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-                                uint32_t v1 = pack_f16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-                                uint32_t v2 = pack_f16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-                                uint32_t v3 = pack_f16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-                                const int k = 4 * c + i;   // 16-byte chunk of the row
-                                const uint32_t dst = scratch + (uint32_t)lane * RB +
-                                                     (uint32_t)((k ^ (lane & (LPR - 1))) << 4);
-                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
-                                             "r"(v0), "r"(v1), "r"(v2), "r"(v3)
-                                             : "memory");
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int cc = 0; cc < HD / 64; cc++) {
-                            const int c = ps * (HD / 64) + cc;
-                            uint32_t o[32];
-                            tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
-                            tmem_wait_ld();
-#pragma unroll
-                            for (int i = 0; i < 8; i++) {
-                                const int k = 8 * cc + i;
-                                const uint32_t dst = scratch + (uint32_t)lane * RB +
-                                                     (uint32_t)((k ^ (lane & (LPR - 1))) << 4);
-                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
-                                             "f"(__uint_as_float(o[4 * i]) * inv),
-                                             "f"(__uint_as_float(o[4 * i + 1]) * inv),
-                                             "f"(__uint_as_float(o[4 * i + 2]) * inv),
-                                             "f"(__uint_as_float(o[4 * i + 3]) * inv)
-                                             : "memory");
+                            for (int j = 0; j < 8; j++) {
+                                if (live_a) {
+                                    *(float2 *)(pa + 64 * cg + 8 * j) =
+                                        make_float2(__uint_as_float(o[4 * j]) * inv_a,
+                                                    __uint_as_float(o[4 * j + 1]) * inv_a);
+                                }
+                                if (live_b) {
+                                    *(float2 *)(pb + 64 * cg + 8 * j) =
+                                        make_float2(__uint_as_float(o[4 * j + 2]) * inv_b,
+                                                    __uint_as_float(o[4 * j + 3]) * inv_b);
+                                }
                             }
                         }
                     }
+                } else {
+                    // f16 rows: in that layout four lanes would write 16 bytes, half
+                    // a sector. Each warp turns its 32 rows through shared memory
+                    // instead - its quarter of the tile's Q, which no MMA reads any
+                    // more - a thread writing its own row, and stores whole rows
+                    // of RB bytes, a row per LPR lanes. 16-byte chunks are swizzled
+                    // by the row so that neither side has bank conflicts.
+                    constexpr int RB = HD * 2;                 // bytes of a row
+                    constexpr int LPR = RB / 16;               // lanes to a row on the way out
+                    constexpr int RPI = 32 / LPR;              // rows an instruction stores
+                    const uint32_t scratch = q_smem(t) + (uint32_t)(warp & 3) * (32u * RB);
+#pragma unroll
+                    for (int c = 0; c < HD / 32; c++) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_addr + o_col(t) + 32 * c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            uint32_t v0 = pack_f16(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+                            uint32_t v1 = pack_f16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+                            uint32_t v2 = pack_f16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+                            uint32_t v3 = pack_f16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+                            const int k = 4 * c + i;   // 16-byte chunk of the row
+                            const uint32_t dst = scratch + (uint32_t)lane * RB +
+                                                 (uint32_t)((k ^ (lane & (LPR - 1))) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                         "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                                         : "memory");
+                        }
+                    }
                     __syncwarp();
-                    // ---- shared -> global: whole row segments ----------------------------
                     const int k = lane % LPR;
 #pragma unroll
                     for (int it = 0; it < 32 / RPI; it++) {
@@ -763,8 +794,8 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
                         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                                      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                                      : "r"(src));
-                        if (part || me.r0 + 32 * (warp & 3) + r < sq.tq) {
-                            *(uint4 *)(obase + (long long)r * ostride * esize + ps * RB + k * 16) = v;
+                        if (me.r0 + 32 * (warp & 3) + r < sq.tq) {
+                            *(uint4 *)(obase + (long long)r * ostride * 2 + k * 16) = v;
                         }
                     }
                     __syncwarp();
