@@ -49,8 +49,8 @@ FALLBACK_TFLOPS = 1590.0
 FALLBACK_TFLOPS_SUSTAINED = 1400.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one prefill_tc_kernel<128>
 # launch at 8192 positions, from the capture summarised in
-# profiles/prefill_tc_kernel_seq8192.md (192.39 MB read + 94.12 MB written).
-PREFILL_DRAM_BYTES_8K = 192.388e6 + 94.125e6
+# profiles/prefill_tc_kernel_seq8192.md (194.05 MB read + 98.96 MB written).
+PREFILL_DRAM_BYTES_8K = 194.047e6 + 98.964e6
 
 # DRAM traffic of the dominant kernel from the ncu captures summarised under
 # profiles/. The decode entry is dram__bytes_read.sum + dram__bytes_write.sum
