@@ -446,7 +446,10 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     const int G = gridDim.x;
     const int u0 = p.ustart[blockIdx.x];
     const int u1 = p.ustart[blockIdx.x + 1];
-    for (int i = threadIdx.x; i <= G; i += kThreads) sm_ustart[i] = p.ustart[i];
+    // (only the merge of runs that share a pair looks the cut up; clusters do not)
+    if (!p.by_cluster) {
+        for (int i = threadIdx.x; i <= G; i += kThreads) sm_ustart[i] = p.ustart[i];
+    }
     // (the first segment's barriers order these stores before their first use)
 
     int u = u0;
