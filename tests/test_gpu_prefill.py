@@ -275,6 +275,35 @@ def test_whisper_encoder_rows(gpu):
     assert np.linalg.norm(want - got) / np.linalg.norm(want) <= 1e-3 + 2.0 ** -11
 
 
+@pytest.mark.parametrize("t,heads", [(150, 4), (1500, 20)])
+def test_the_encoder_attention_off_its_rows_is_the_split_path(gpu, t, heads):
+    """crates/llmtie-cuda/tests/kernels.rs:4040-4079: flash_attn_rows over the
+    packed [t][3d] product against the chain it replaces - q scaled,
+    split_heads, split_heads_t, flash_attn over the f32 caches with scale 1,
+    the context rounded to f16. The reference runs one kernel under both and
+    asserts equal bits; here the rows path is the tensor-memory kernel and the
+    chain the general one, whose sums associate differently, so the two are
+    held to the bar the reference sets between its f16-cache and f32-cache
+    readers (tests/kernels.rs:2561-2725: 2e-3), and most elements must still
+    come out as the same f16."""
+    hd = 64
+    d = heads * hd
+    scale = np.float32(hd) ** np.float32(-0.5)
+    qkv = (O.seq(t * 3 * d, 611) * np.float32(3.0)).reshape(t, 3 * d)
+    q = np.ascontiguousarray(qkv[:, :d]) * scale
+    k = gpu.split_heads(gpu.upload(np.ascontiguousarray(qkv[:, d:2 * d])), t, heads, hd)
+    v = gpu.split_heads_t(gpu.upload(np.ascontiguousarray(qkv[:, 2 * d:])), t, heads, hd)
+    ctx = gpu.download(gpu.flash_attn(gpu.upload(q), k, v, t, 0, heads, heads, hd, t, 1.0, False))
+    want = O.round_f16(ctx)
+    got = gpu.download_u16(gpu.flash_attn_rows(gpu.upload(qkv), t, heads, hd, float(scale)))
+    a, b = O.widen_f16(want), O.widen_f16(got)
+    # (the bar is relative to the contexts' size, which here reaches into the tens)
+    assert np.abs(a - b).max() <= 2e-3 * max(1.0, float(np.abs(a).max())), np.abs(a - b).max()
+    assert np.linalg.norm(a - b) / np.linalg.norm(a) <= 1e-3
+    differ = float((want != got).mean())
+    assert differ <= 0.10, f"{differ:.4f} of the elements round to another f16"
+
+
 @pytest.mark.parametrize("batch,t", [(3, 200), (8, 1500), (10, 130)])
 def test_batched_encoder_rows_equal_one_call_per_utterance(gpu, batch, t):
     """BASELINE config 4 at batch 8 in two launches: bit for bit what one
