@@ -248,7 +248,10 @@ llmtie_status llmtie_flash_attn_f16(llmtie_gpu *g, const float *q, size_t q_len,
                                     size_t head_dim, size_t cap, float scale,
                                     int32_t causal);
 /* Gpu::flash_attn (device.rs:5702-5745): the same off f32 caches, head_dim 64
- * or 128; K and V are rounded to f16 on their way into the products. */
+ * or 128; K and V are rounded to f16 on their way into the products: here
+ * once, the live keys into f16 caches that the handle keeps for the purpose
+ * (grown on the stream when a longer context comes), ahead of the attention
+ * kernel. */
 llmtie_status llmtie_flash_attn(llmtie_gpu *g, const float *q, size_t q_len,
                                 const float *k, size_t k_len, const float *v,
                                 size_t v_len, float *out, size_t out_len, size_t tq,

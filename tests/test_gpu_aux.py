@@ -98,6 +98,7 @@ def test_kprof_charges_each_launch_to_its_kernel(gpu):
     n2 = 130
     kc2, vc2 = lay_caches(O.seq(kv * n2 * hd, 4), O.seq(kv * n2 * hd, 5), kv, n2, hd, 138)
     dk2, dv2 = gpu.upload_f16(kc2), gpu.upload_f16(vc2)
+    d32k, d32v = gpu.upload(kc), gpu.upload(vc)
     gpu.synchronize()
     gpu.kprof_reset()
     gpu.kprof_enable(True)
@@ -106,12 +107,15 @@ def test_kprof_charges_each_launch_to_its_kernel(gpu):
         gpu.rope(dq, 0, tq, heads, hd, 10000.0, 0)
         gpu.flash_attn_f16(dq, dk, dv, tq, 0, heads, kv, hd, 256, scale, True)
         gpu.flash_attn_f16(dq, dk2, dv2, n2, 0, heads, kv, hd, 138, scale, True)
+        # f32 caches: rounded to f16 once, then the tensor-memory kernel
+        gpu.flash_attn(dq, d32k, d32v, tq, 0, heads, kv, hd, 256, scale, True)
         rep = gpu.kprof_report()
     finally:
         gpu.kprof_enable(False)
     assert rep["rope"][0] == 2
     assert rep["flash_attn_h_tc"][0] == 1
     assert rep["flash_attn_h"][0] == 1
+    assert rep["caches_to_f16"][0] == 1 and rep["flash_attn_tc"][0] == 1
     assert all(ms > 0.0 for _, ms in rep.values())
     assert list(rep.values()) == sorted(rep.values(), key=lambda e: -e[1])
     gpu.kprof_reset()

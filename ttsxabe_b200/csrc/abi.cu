@@ -193,6 +193,7 @@ extern "C" void llmtie_close(llmtie_gpu *g)
     if (g->stream) cudaStreamSynchronize(g->stream);
     if (g->ws_rope.ptr) cudaFreeAsync(g->ws_rope.ptr, g->stream);
     if (g->ws_part.ptr) cudaFreeAsync(g->ws_part.ptr, g->stream);
+    if (g->ws_kv16.ptr) cudaFreeAsync(g->ws_kv16.ptr, g->stream);
     if (g->stream) cudaStreamSynchronize(g->stream);
     if (g->abort_epoch) cudaFree(g->abort_epoch);
     if (g->timeout_host) cudaFreeHost(g->timeout_host);
@@ -837,10 +838,48 @@ static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q,
     p.out_f16 = 0;
     p.q_scale = 1.0f;
     p.sl2 = scale * kLog2e;
-    // kprof tells the two kernels apart: the tensor-memory one (f16 caches
-    // only, so `name` is "flash_attn_h" then) is charged to "flash_attn_h_tc"
-    const bool tc = use_tc(p, (int)hd);
-    LaunchScope ls(g, tc ? "flash_attn_h_tc" : name);
+    // f32 caches (Whisper's self-attention twins, the speech LM's prefill,
+    // the flow model's attention): the fused kernels round K and V to f16 as
+    // they read them (crates/llmtie-cuda/src/kernels.rs:3078-3269), so the
+    // live keys are rounded once, into f16 caches of the handle's own, and
+    // the tensor-memory kernel takes it from there - the same numbers through
+    // tcgen05 instead of mma.sync. (LLMTIE_B200_F32_GENERAL keeps such calls
+    // on the general kernel: an A/B switch.)
+    static const bool f32_general = getenv("LLMTIE_B200_F32_GENERAL") != nullptr;
+    bool staged = false;
+    if (kv_f32 && !f32_general && ((uintptr_t)v & 7u) == 0 && cap % 2 == 0) {
+        const size_t live = past + tq;
+        const size_t cap16 = (live + 7) / 8 * 8;
+        const size_t half = kv_heads * cap16 * hd * sizeof(uint16_t);
+        PrefillParams t = p;
+        t.kv_f32 = 0;
+        t.seq[0].cap = (int)cap16;
+        cudaError_t werr;
+        // (eligibility is a matter of shapes and alignments: asked with a
+        // stand-in pointer before anything is allocated)
+        t.seq[0].k = t.seq[0].v = (const void *)(uintptr_t)256;
+        if (use_tc(t, (int)hd)) {
+            void *work = workspace_reserve(g->ws_kv16, 2 * half + 256, g->stream, &werr);
+            if (!work) return driver_fail("allocating", werr);
+            uint16_t *k16 = (uint16_t *)work;
+            uint16_t *v16 = (uint16_t *)((char *)work + (half + 255) / 256 * 256);
+            {
+                LaunchScope ls(g, "caches_to_f16");
+                launch_caches_to_f16(g->stream, (const float *)k, (const float *)v, k16, v16,
+                                     (int)kv_heads, (int)hd, (int)cap, (int)cap16, (int)live);
+                const llmtie_status st = ls.done();
+                if (st != LLMTIE_OK) return st;
+            }
+            p = t;
+            p.seq[0].k = k16;
+            p.seq[0].v = v16;
+            staged = true;
+        }
+    }
+    // kprof tells the two kernels apart: the tensor-memory one is charged to
+    // "flash_attn_h_tc" (f16 caches) or "flash_attn_tc" (f32 caches, staged)
+    const bool tc = staged || use_tc(p, (int)hd);
+    LaunchScope ls(g, tc ? (staged ? "flash_attn_tc" : "flash_attn_h_tc") : name);
     const cudaError_t e = tc ? launch_prefill_tc(g->stream, p, (int)hd, next_wait_ctl(g))
                              : launch_prefill_mma(g->stream, p, (int)hd);
     if (e != cudaSuccess) return driver_fail(name, e);

@@ -272,6 +272,42 @@ __global__ void round_f16_kernel(const float *__restrict__ src, uint16_t *__rest
     if (i < n) dst[i] = f16_bits(src[i]);
 }
 
+// The live part of a pair of f32 caches as f16 caches of capacity `cap16`
+// (live rounded up to eight keys): K [kv][cap][hd] -> [kv][cap16][hd], V
+// [kv][hd][cap] -> [kv][hd][cap16], rounded to nearest as the attention
+// kernels round their operands, what lies past the live keys zero. A thread a
+// pair of neighbouring elements of either output.
+__global__ void caches_to_f16_kernel(const float *__restrict__ k32, const float *__restrict__ v32,
+                                     uint32_t *__restrict__ k16, uint32_t *__restrict__ v16,
+                                     int kv_heads, int hd, int cap, int cap16, int live)
+{
+    const long long nk = (long long)kv_heads * cap16 * hd / 2;     // pairs of the key cache
+    const long long nv = (long long)kv_heads * hd * cap16 / 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nk + nv;
+         i += (long long)gridDim.x * blockDim.x) {
+        if (i < nk) {
+            const long long e = 2 * i;                  // element of [kv][cap16][hd]
+            const int d = (int)(e % hd);
+            const long long row = e / hd;
+            const int r = (int)(row % cap16), h = (int)(row / cap16);
+            uint32_t w = 0u;
+            if (r < live) {
+                const float2 x = *(const float2 *)(k32 + ((long long)h * cap + r) * hd + d);
+                w = (uint32_t)f16_bits(x.x) | ((uint32_t)f16_bits(x.y) << 16);
+            }
+            k16[i] = w;
+        } else {
+            const long long e = 2 * (i - nk);           // element of [kv][hd][cap16]
+            const int c = (int)(e % cap16);
+            const long long row = e / cap16;            // h * hd + d
+            const float *src = v32 + row * cap + c;
+            const uint32_t lo = c < live ? f16_bits(src[0]) : 0u;
+            const uint32_t hi = c + 1 < live ? f16_bits(src[1]) : 0u;
+            v16[i - nk] = lo | (hi << 16);
+        }
+    }
+}
+
 // Whisper encoder staging (hd 64): the k and v column blocks of qkv f32
 // [t][3*heads*64] go to K f16 [heads][tp][64] and V f16 [heads][64][tp], zero
 // padded to tp. One block = one head x 64 frames: every global access is a
@@ -781,6 +817,14 @@ void launch_rope_gptj(cudaStream_t st, float *x, const float *inv_freq, int posi
     const int wide = dim % 2 == 0 && ((uintptr_t)x & 7u) == 0;
     rope_gptj_kernel<<<flat_blocks(n, 256), 256, 0, st>>>(x, inv_freq, positions, dim, rot_dim,
                                                          wide);
+}
+
+void launch_caches_to_f16(cudaStream_t st, const float *k32, const float *v32, uint16_t *k16,
+                          uint16_t *v16, int kv_heads, int hd, int cap, int cap16, int live)
+{
+    const size_t pairs = (size_t)kv_heads * cap16 * hd;      // half of each cache, twice
+    caches_to_f16_kernel<<<flat_blocks(pairs, 256), 256, 0, st>>>(
+        k32, v32, (uint32_t *)k16, (uint32_t *)v16, kv_heads, hd, cap, cap16, live);
 }
 
 void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n)
