@@ -24,7 +24,8 @@ def test_runs_are_contiguous_increasing_and_cover_every_unit(tk, kv, hd):
     cut = decode_cut(tk, kv, hd, 148)
     w = units(tk, kv)
     grid = len(cut) - 1
-    assert grid == min(148, max(1, w // 4))
+    # never fewer than four units a block - unless that is fewer blocks than pairs
+    assert grid == min(148, max(1, w // 4, len(tk) * kv))
     assert cut[0] == 0 and cut[-1] == w
     assert all(a < b for a, b in zip(cut, cut[1:])), "every block gets at least one unit"
 
@@ -50,7 +51,7 @@ def test_ragged_contexts_are_laid_end_to_end():
     tk, kv = [1000, 130, 4096], 2
     cut = decode_cut(tk, kv, 128, 148)
     assert cut[-1] == (8 + 2 + 32) * kv
-    # fewer SMs, fewer blocks; never more blocks than a quarter of the units
+    # fewer SMs, fewer blocks; never more blocks than a quarter of the units or the pairs
     assert len(decode_cut(tk, kv, 128, 8)) - 1 == 8
     assert len(decode_cut([128], 1, 128, 148)) - 1 == 1
 

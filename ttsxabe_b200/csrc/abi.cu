@@ -1191,7 +1191,9 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         }
         // One block per SM, but never fewer than four units (512 keys) a block:
         // a short context cut any finer spends longer merging partials than
-        // it saved streaming them.
+        // it saved streaming them. (Whole pairs are another matter: as many
+        // blocks as pairs cost no merge at all, and spare a block from walking
+        // several short pairs one after the other.)
         // (LLMTIE_B200_DECODE_GRID caps the block count: a tuning switch)
         static const int grid_cap = [] {
             const char *e = getenv("LLMTIE_B200_DECODE_GRID");
@@ -1200,7 +1202,7 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         }();
         const int grid = (int)std::min<long long>(
             std::min(std::min(g->sm_count, grid_cap), LLMTIE_STREAM_MAX_BLOCKS),
-            std::max<long long>(1, units / 4));
+            std::max<long long>(std::max<long long>(1, units / 4), (long long)p.nseq * inner));
         const size_t pairs = (size_t)p.nseq * inner;
         const llmtie_status s =
             scratch_reserve(g, scratch, pairs + 1, (size_t)grid * 2, (size_t)hd);
@@ -1368,7 +1370,6 @@ extern "C" llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_
                                             size_t out_len, size_t out_off)
 {
     NEED_HANDLE(g);
-    (void)scratch;   // the f32 cache is a few hundred keys: one block a head, no partials
     if (head_dim != 64) return unsupported(head_dim, heads, kv_heads);
     if (kv_heads == 0 || heads % kv_heads != 0 || heads / kv_heads > 8) {
         return unsupported(head_dim, heads, kv_heads);
@@ -1400,10 +1401,21 @@ extern "C" llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_
                            "a row of %zu does not divide into blocks of 32", out_off);
     }
     if (!fits_i32(cap)) return llmtie_fail(LLMTIE_ERR_INVALID, "capacity does not fit 32 bits");
+    if (((uintptr_t)k & 15u) != 0) return misaligned("the key cache", k, 16);
+    // A partial (o, m, l) per block and a counter per head live in the
+    // caller's scratch (sized there in slots of 8 rows of hd + 2 floats);
+    // without one the launch is one block a head.
+    if (scratch) {
+        const size_t splits = (size_t)decode_f32_splits((int)tk);
+        const llmtie_status rs =
+            scratch_reserve(g, scratch, heads, (heads * splits + 7) / 8, head_dim);
+        if (rs != LLMTIE_OK) return rs;
+    }
     LaunchScope ls(g, "attn_decode_f64");
     launch_decode_f32(g->stream, q, (long long)q_off, k, v, out, (long long)out_off, (int)heads,
                       (int)kv_heads, (int)head_dim, (int)tk, (int)cap, scale_q ? scale : 1.0f,
-                      scale_q ? 1.0f : scale);
+                      scale_q ? 1.0f : scale, scratch ? scratch->part : nullptr,
+                      scratch ? scratch->ctr : nullptr);
     return ls.done();
 }
 

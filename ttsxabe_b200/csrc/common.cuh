@@ -283,7 +283,9 @@ bool llmtie_encode_tiled_f16(CUtensorMap *map, int rank, const void *base, const
                              const uint64_t *strides_bytes, const uint32_t *box, int swizzle_bytes);
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
                        const float *v, float *out, long long out_off, int heads, int kv_heads,
-                       int hd, int tk, int cap, float q_scale, float s_scale);
+                       int hd, int tk, int cap, float q_scale, float s_scale, float *part,
+                       unsigned *ctr);
+int decode_f32_splits(int tk);   // blocks a head of that launch (partials a head it needs)
 void launch_lse_merge(cudaStream_t st, const float *parts_buf, int parts, int rows, int hd,
                       float *out);
 // Waits (bounded) until every rank's flag has reached this rank's step, then

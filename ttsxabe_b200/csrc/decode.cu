@@ -364,39 +364,56 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p)
 }
 
 // Decode off an f32 cache (the Whisper decoder's self-attention: 64-wide
-// heads, at most a few hundred keys). One block a query head; plain f32 FMA
-// as the reference's `attn_decode_f64` entry keeps it.
+// heads, at most a few hundred keys), plain f32 FMA as the reference's
+// `attn_decode_f64` entry keeps it. Every head's keys are cut over
+// `gridDim.y` blocks: one block a head would be twenty blocks on 148 SMs,
+// each walking its few hundred keys alone. A block takes `span` keys in
+// chunks of 64: four lanes a key for the scores (a warp reads eight whole key
+// rows, 2 KB on end), a thread a channel and a quarter of the chunk's keys
+// for the context. It leaves an un-normalised (o, m, l) in `part`; the last
+// block of a head to arrive (`ctr`, which it leaves at zero) merges them.
 template <int HD>
 __global__ void __launch_bounds__(256)
-decode_f32_kernel(const float *__restrict__ q, long long q_off, const float *__restrict__ k,
-                  const float *__restrict__ v, float *__restrict__ out, long long out_off,
-                  int group, int tk, int cap, float q_scale, float s_scale)
+decode_f32_split_kernel(const float *__restrict__ q, long long q_off, const float *__restrict__ k,
+                        const float *__restrict__ v, float *__restrict__ out, long long out_off,
+                        int group, int tk, int cap, float q_scale, float s_scale, int span,
+                        float *__restrict__ part, unsigned *__restrict__ ctr)
 {
-    constexpr int CH = 256;
+    constexpr int CH = 64;               // keys of a chunk
+    constexpr int QW = HD / 4;           // channels a lane of a key's four takes
     __shared__ float sq[HD];
     __shared__ float sp[CH];
     __shared__ float red[8];
     __shared__ float so[4][HD];
+    __shared__ int s_last;
     const int head = blockIdx.x;
     const int kh = head / group;
     const int tid = threadIdx.x;
+    const int k0 = blockIdx.y * span, k1 = min(tk, k0 + span);
     if (tid < HD) sq[tid] = q[q_off + (long long)head * HD + tid] * q_scale;
     __syncthreads();
-    const int d = tid % HD;      // output channel this thread accumulates
-    const int part = tid / HD;   // over keys part, part + 4, ... of a chunk
+    const int d = tid % HD, quarter = tid / HD;     // context: channel, and keys quarter, +4, ...
+    const int ki = tid >> 2, kq = tid & 3;          // scores: key of the chunk, which 16 channels
     float m = -CUDART_INF_F, l = 0.0f, acc = 0.0f;
-    for (int c0 = 0; c0 < tk; c0 += CH) {
-        const int key = c0 + tid;
-        float s = -CUDART_INF_F;
-        if (key < tk) {
-            const float *kr = k + ((size_t)kh * cap + key) * HD;
-            float dot = 0.0f;
-#pragma unroll 8
-            for (int e = 0; e < HD; e++) dot += sq[e] * kr[e];
-            s = dot * s_scale;
+    for (int c0 = k0; c0 < k1; c0 += CH) {
+        const int key = c0 + ki;
+        float dot = 0.0f;
+        if (key < k1) {
+            const float4 *kr = (const float4 *)(k + ((size_t)kh * cap + key) * HD + kq * QW);
+#pragma unroll
+            for (int e = 0; e < QW / 4; e++) {
+                const float4 x = __ldg(kr + e);
+                const float *qs = sq + kq * QW + 4 * e;
+                dot += qs[0] * x.x;
+                dot += qs[1] * x.y;
+                dot += qs[2] * x.z;
+                dot += qs[3] * x.w;
+            }
         }
-        // block maximum
-        float bm = s;
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        const float sc = key < k1 ? dot * s_scale : -CUDART_INF_F;
+        float bm = sc;
         for (int w = 16; w > 0; w >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, w));
         if ((tid & 31) == 0) red[tid >> 5] = bm;
         __syncthreads();
@@ -404,10 +421,10 @@ decode_f32_kernel(const float *__restrict__ q, long long q_off, const float *__r
         for (int w = 1; w < 8; w++) bm = fmaxf(bm, red[w]);
         const float m_new = fmaxf(m, bm);
         const float alpha = (m == -CUDART_INF_F) ? 0.0f : __expf(m - m_new);
-        const float pv = (key < tk) ? __expf(s - m_new) : 0.0f;
-        sp[tid] = pv;
-        __syncthreads();
-        float bs = pv;
+        const float pv = (key < k1) ? __expf(sc - m_new) : 0.0f;
+        if (kq == 0) sp[ki] = pv;
+        float bs = kq == 0 ? pv : 0.0f;
+        __syncthreads();                 // red was read; sp is written
         for (int w = 16; w > 0; w >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, w);
         if ((tid & 31) == 0) red[tid >> 5] = bs;
         __syncthreads();
@@ -416,19 +433,49 @@ decode_f32_kernel(const float *__restrict__ q, long long q_off, const float *__r
         l = l * alpha + bs;
         m = m_new;
         acc *= alpha;
-        const int n = min(CH, tk - c0);
+        const int n = min(CH, k1 - c0);
         const float *vr = v + ((size_t)kh * HD + d) * cap + c0;
-        for (int e = part; e < n; e += 256 / HD) acc += sp[e] * vr[e];
+        for (int e = quarter; e < n; e += 256 / HD) acc += sp[e] * vr[e];
         __syncthreads();
     }
-    so[part][d] = acc;
+    so[quarter][d] = acc;
     __syncthreads();
+    const int S = gridDim.y;
+    float a = 0.0f;
     if (tid < HD) {
-        float a = 0.0f;
 #pragma unroll
         for (int w = 0; w < 256 / HD; w++) a += so[w][tid];
-        out[out_off + (long long)head * HD + tid] = l > 0.0f ? a / l : 0.0f;
     }
+    if (S == 1) {
+        if (tid < HD) out[out_off + (long long)head * HD + tid] = l > 0.0f ? a / l : 0.0f;
+        return;
+    }
+    float *mine = part + ((size_t)head * S + blockIdx.y) * (HD + 2);
+    if (tid < HD) mine[tid] = a;
+    if (tid == 0) {
+        mine[HD] = m;
+        mine[HD + 1] = l;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(ctr + head, 1u) == (unsigned)(S - 1);
+    __syncthreads();
+    if (!s_last) return;
+    if (tid < HD) {
+        const float *all = part + (size_t)head * S * (HD + 2);
+        float M = -CUDART_INF_F;
+        for (int i = 0; i < S; i++) M = fmaxf(M, __ldcg(all + (size_t)i * (HD + 2) + HD));
+        float O = 0.0f, L = 0.0f;
+        for (int i = 0; i < S; i++) {
+            const float *pr = all + (size_t)i * (HD + 2);
+            const float mi = __ldcg(pr + HD);
+            const float f = (mi == -CUDART_INF_F) ? 0.0f : __expf(mi - M);
+            O += f * __ldcg(pr + tid);
+            L += f * __ldcg(pr + HD + 1);
+        }
+        out[out_off + (long long)head * HD + tid] = L > 0.0f ? O / L : 0.0f;
+    }
+    if (tid == 0) ctr[head] = 0u;        // at rest again for the next call
 }
 
 // out[row] = sum_i o_i exp(m_i - M) / sum_i l_i exp(m_i - M) over `parts`
@@ -463,7 +510,7 @@ const KernelReg reg_d64("attn_decode_h64", (const void *)decode_f16_kernel<64, t
 const KernelReg reg_d64w("attn_decode_h64_wide", (const void *)decode_f16_kernel<64, true, 4>);
 const KernelReg reg_d64u("attn_decode_h64_unaligned",
                          (const void *)decode_f16_kernel<64, false, 1>);
-const KernelReg reg_df32("attn_decode_f64", (const void *)decode_f32_kernel<64>);
+const KernelReg reg_df32("attn_decode_f64", (const void *)decode_f32_split_kernel<64>);
 const KernelReg reg_merge("lse_merge", (const void *)lse_merge_kernel);
 
 template <int HD, bool V16, int NB>
@@ -680,13 +727,24 @@ int decode_resident_blocks(int hd, int sm_count, int nb)
     return (hd == 128 ? resident<128>(nb) : resident<64>(nb)) * sm_count;
 }
 
+int decode_f32_splits(int tk)
+{
+    return std::max(1, std::min(8, (tk + 63) / 64));
+}
+
 void launch_decode_f32(cudaStream_t st, const float *q, long long q_off, const float *k,
                        const float *v, float *out, long long out_off, int heads, int kv_heads,
-                       int hd, int tk, int cap, float q_scale, float s_scale)
+                       int hd, int tk, int cap, float q_scale, float s_scale, float *part,
+                       unsigned *ctr)
 {
     (void)hd;   // 64: the only width the f32 cache is decoded at
-    decode_f32_kernel<64><<<heads, 256, 0, st>>>(q, q_off, k, v, out, out_off, heads / kv_heads,
-                                                tk, cap, q_scale, s_scale);
+    // up to eight blocks a head, each a whole number of 64-key chunks
+    const int splits = part ? decode_f32_splits(tk) : 1;
+    const int span = ((tk + splits - 1) / splits + 63) / 64 * 64;
+    const dim3 grid(heads, (tk + span - 1) / span);
+    decode_f32_split_kernel<64><<<grid, 256, 0, st>>>(q, q_off, k, v, out, out_off,
+                                                     heads / kv_heads, tk, cap, q_scale, s_scale,
+                                                     span, part, ctr);
 }
 
 void launch_lse_merge(cudaStream_t st, const float *parts_buf, int parts, int rows, int hd,

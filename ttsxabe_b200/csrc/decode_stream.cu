@@ -980,8 +980,9 @@ extern "C" llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size
     p.pair0[batch] = (int)(batch * kv_heads);
     p.total_units = units;
     if (units > 0x7fffffffLL) return llmtie_fail(LLMTIE_ERR_INVALID, "too many keys for one launch");
-    const int grid = (int)std::min<long long>(std::min(sm_count, LLMTIE_STREAM_MAX_BLOCKS),
-                                              std::max<long long>(1, units / 4));
+    const int grid = (int)std::min<long long>(
+        std::min(sm_count, LLMTIE_STREAM_MAX_BLOCKS),
+        std::max<long long>(std::max<long long>(1, units / 4), (long long)(batch * kv_heads)));
     if (ustart_len < (size_t)grid + 1) {
         return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %d in a buffer of %zu", grid + 1,
                            ustart_len);
