@@ -433,9 +433,18 @@ decode_f32_split_kernel(const float *__restrict__ q, long long q_off, const floa
         l = l * alpha + bs;
         m = m_new;
         acc *= alpha;
+        // (all of the chunk's loads of a thread in flight at once; past the
+        // slice's last key the probability is zero and nothing is read)
         const int n = min(CH, k1 - c0);
         const float *vr = v + ((size_t)kh * HD + d) * cap + c0;
-        for (int e = quarter; e < n; e += 256 / HD) acc += sp[e] * vr[e];
+        float x[CH * HD / 256];
+#pragma unroll
+        for (int i = 0; i < CH * HD / 256; i++) {
+            const int e = quarter + i * (256 / HD);
+            x[i] = e < n ? __ldg(vr + e) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < CH * HD / 256; i++) acc += sp[quarter + i * (256 / HD)] * x[i];
         __syncthreads();
     }
     so[quarter][d] = acc;
