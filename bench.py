@@ -751,6 +751,46 @@ def other_configs(args, world, rank, local):
             byts = 2 * wh * wt * whd * 2
             res["config4_cross_n%d_cap%d" % (n, wcap_i)] = {"us": t * 1e6, "gbs": byts / t / 1e9,
                                                             "frac_of_hbm_peak": byts / t / 1e9 / hbm}
+    # ---- the callers either side of the BASELINE configs ----------------------------
+    # the Whisper decoder's self-attention off f32 caches (20 heads x 64, at most 448 keys)
+    for tk in (224, 448):
+        q, k, v = randn(wh * whd), randn(wh * 448 * whd), randn(wh * 448 * whd)
+        fn = lambda: gpu.attn_decode(q, k, v, wh, wh, whd, tk, 448, 0.125, True, sc)
+        res["whisper_self_decode_f32_tk%d" % tk] = {"us": graph_time(gpu, fn) * 1e6}
+    # prefill off f32 caches: the flow model's 16 heads x 64 over 2000 frames, the speech
+    # LM's 14 / 2 heads x 64 (crates/llmtie-cosy), and the chat geometry at 2048 positions
+    for name, (h_, kv_, hd_, causal, tq, past) in (
+            ("flow_16x64_2000_frames_f32", (16, 16, 64, False, 2000, 0)),
+            ("speech_lm_14_2x64_300_on_20_f32", (14, 2, 64, True, 300, 20)),
+            ("prefill_32_8x128_2048_f32", (HEADS, KV_HEADS, HD, True, 2048, 0))):
+        cap = past + tq
+        q, k, v = randn(tq * h_ * hd_), randn(kv_ * cap * hd_), randn(kv_ * cap * hd_)
+        fn = lambda: gpu.flash_attn(q, k, v, tq, past, h_, kv_, hd_, cap, float(hd_) ** -0.5,
+                                    causal)
+        t = graph_time(gpu, fn, reps=5)
+        keys = tq * (tq + 1) / 2 + tq * past if causal else tq * cap
+        res[name] = {"us": t * 1e6, "tflops": 4.0 * hd_ * h_ * keys / t / 1e12}
+    # prompts shorter than a key tile; a few short sequences decoding together
+    for lens in ([16], [100], [100, 50, 30, 120]):
+        total = int(sum(lens))
+        cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        q, k, v = randn(total * HEADS * HD), randn(total * KV_HEADS * HD), randn(total * KV_HEADS * HD)
+        kcs2 = [gpu.zeros_f16(KV_HEADS * 512 * HD) for _ in lens]
+        vcs2 = [gpu.zeros_f16(KV_HEADS * 512 * HD) for _ in lens]
+        out = gpu.uninit(total * HEADS * HD)
+        fn = lambda: gpu.prefill_varlen(q, k, v, cu, kcs2, vcs2, [0] * len(lens), [512] * len(lens),
+                                        None, HEADS, KV_HEADS, HD, 10000.0, SCALE, out=out)
+        res["prefill_prompts_%s" % "_".join(str(x) for x in lens)] = {"us": graph_time(gpu, fn) * 1e6}
+    for batch, lo, hi in ((1, 1024, 1025), (4, 512, 1025), (8, 512, 1025)):
+        tks = [int(x) for x in rng.integers(lo, hi, size=batch)]
+        cap = 1024
+        ks = [device_normal_f16(gpu, KV_HEADS * cap * HD, 110 + b) for b in range(batch)]
+        vs = [device_normal_f16(gpu, KV_HEADS * cap * HD, 150 + b) for b in range(batch)]
+        q = randn(batch * HEADS * HD)
+        out = gpu.uninit(batch * HEADS * HD)
+        fn = lambda: gpu.decode_batched(q, ks, vs, tks, [cap] * batch, HEADS, KV_HEADS, HD, SCALE,
+                                        False, sc, out=out)
+        res["decode_batch%d_ctx%d_%d" % (batch, lo, hi - 1)] = {"us": graph_time(gpu, fn) * 1e6}
     line = {"metric": "per-config device time", "unit": "us", "n_gpus": 1, "data": "synthetic",
             "timing": "CUDA-graph replay, median of 5", "peaks": {"hbm_gbs": hbm, "tflops": tf,
                                                                   "source": which},
