@@ -21,6 +21,10 @@ SIZED = [
     (4, 4, 128, True, 70, 33, 160, False),
     (4, 4, 64, True, 70, 33, 160, False),
     (4, 2, 64, True, 70, 33, 160, False),
+    # f32 caches of odd capacity: the general kernel (even ones are rounded to f16 once and
+    # take the tensor-memory kernel)
+    (4, 2, 128, True, 70, 33, 161, False),
+    (4, 4, 64, False, 70, 33, 161, False),
     (8, 2, 128, True, 150, 0, 256, True),
     (8, 1, 128, True, 90, 17, 128, True),
     (4, 4, 128, True, 200, 40, 256, True),
