@@ -240,7 +240,10 @@ llmtie_status llmtie_rope_cache_batched(llmtie_gpu *g, float *q, size_t q_len, c
 int32_t llmtie_supports_flash(size_t head_dim, size_t heads, size_t kv_heads);
 /* Gpu::flash_attn_f16 (device.rs:5754-5799): q f32 [tq][heads*hd] (already
  * rotated), K f16 [kv][cap][hd], V f16 [kv][hd][cap] holding past+tq
- * positions; out f32 [tq][heads*hd]. head_dim 128 only, cap even. */
+ * positions; out f32 [tq][heads*hd]. head_dim 128 only, cap even. (Caches
+ * whose value rows are not 16-byte aligned - a capacity that is not a
+ * multiple of 8 - cost one more launch: their live keys are copied into
+ * aligned caches that the handle keeps for the purpose.) */
 llmtie_status llmtie_flash_attn_f16(llmtie_gpu *g, const float *q, size_t q_len,
                                     const uint16_t *k, size_t k_len, const uint16_t *v,
                                     size_t v_len, float *out, size_t out_len, size_t tq,

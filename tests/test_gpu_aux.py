@@ -92,7 +92,8 @@ def test_kprof_charges_each_launch_to_its_kernel(gpu):
     scale = float(np.float32(hd) ** np.float32(-0.5))
     q = O.seq(tq * heads * hd, 1)
     dq = gpu.upload(q)
-    # capacity 256: aligned rows, the tensor-memory kernel; 138: the general one
+    # capacity 256: aligned rows, the tensor-memory kernel as the caches lie; 138: after a
+    # copy of the live keys into aligned caches
     kc, vc = lay_caches(O.seq(kv * tq * hd, 2), O.seq(kv * tq * hd, 3), kv, tq, hd, 256)
     dk, dv = gpu.upload_f16(kc), gpu.upload_f16(vc)
     n2 = 130
@@ -114,8 +115,8 @@ def test_kprof_charges_each_launch_to_its_kernel(gpu):
         gpu.kprof_enable(False)
     assert rep["rope"][0] == 2
     assert rep["flash_attn_h_tc"][0] == 1
-    assert rep["flash_attn_h"][0] == 1
-    assert rep["caches_to_f16"][0] == 1 and rep["flash_attn_tc"][0] == 1
+    assert rep["caches_to_f16"][0] == 2 and rep["flash_attn_tc"][0] == 2
+    assert "flash_attn_h" not in rep and "flash_attn" not in rep
     assert all(ms > 0.0 for _, ms in rep.values())
     assert list(rep.values()) == sorted(rep.values(), key=lambda e: -e[1])
     gpu.kprof_reset()
@@ -123,6 +124,49 @@ def test_kprof_charges_each_launch_to_its_kernel(gpu):
     # off again: nothing is charged
     gpu.rope(dq, 0, tq, heads, hd, 10000.0, 0)
     assert gpu.kprof_report() == {}
+
+
+def test_the_general_prefill_kernel_behind_its_switch():
+    """With LLMTIE_B200_NO_TC the tensor-memory kernel is never taken (the
+    switch is read once a process, hence the child): the general kernel
+    serves f16 and f32 caches, aligned or not, at the same bar, and kprof
+    names it."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import numpy as np
+from oracle import oracle as O
+from tests.helpers import lay_caches, prefill_spread, assert_prefill_tolerance
+from ttsxabe_b200 import Gpu
+gpu = Gpu.open(0)
+gpu.kprof_enable(True)
+for heads, kv, hd, causal, tq, past, cap, half in [(8, 2, 128, True, 150, 0, 256, True),
+                                                   (4, 2, 128, True, 130, 5, 138, True),
+                                                   (4, 2, 64, True, 70, 33, 160, False),
+                                                   (16, 16, 64, False, 257, 0, 258, False)]:
+    tk = past + tq
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = O.seq(tq * heads * hd, 71) * np.float32(100.0)
+    kc, vc = lay_caches(O.seq(kv * tk * hd, 72), O.seq(kv * tk * hd, 73), kv, tk, hd, cap)
+    dq = gpu.upload(q)
+    if half:
+        out = gpu.flash_attn_f16(dq, gpu.upload_f16(kc), gpu.upload_f16(vc), tq, past, heads, kv, hd, cap, scale, causal)
+    else:
+        out = gpu.flash_attn(dq, gpu.upload(kc), gpu.upload(vc), tq, past, heads, kv, hd, cap, scale, causal)
+    want, spread = prefill_spread(q, kc, vc, tq, past, heads, kv, hd, cap, scale, causal)
+    assert_prefill_tolerance(str((heads, kv, hd, tq, cap)), want, spread, gpu.download(out))
+rep = gpu.kprof_report()
+assert not any(name.endswith("_tc") or name == "caches_to_f16" for name in rep), rep
+assert rep["flash_attn_h"][0] == 2 and sum(rep[n][0] for n in rep if n in ("flash_attn", "flash_attn_64")) == 2, rep
+print("general kernel ok")
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, LLMTIE_B200_NO_TC="1", PYTHONPATH=root)
+    done = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True,
+                          text=True, timeout=600)
+    assert done.returncode == 0 and "general kernel ok" in done.stdout, done.stdout + done.stderr
 
 
 def test_kernel_resources_are_what_the_compiler_gave(gpu):

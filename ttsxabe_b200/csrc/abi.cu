@@ -838,16 +838,20 @@ static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q,
     p.out_f16 = 0;
     p.q_scale = 1.0f;
     p.sl2 = scale * kLog2e;
-    // f32 caches (Whisper's self-attention twins, the speech LM's prefill,
-    // the flow model's attention): the fused kernels round K and V to f16 as
-    // they read them (crates/llmtie-cuda/src/kernels.rs:3078-3269), so the
-    // live keys are rounded once, into f16 caches of the handle's own, and
-    // the tensor-memory kernel takes it from there - the same numbers through
-    // tcgen05 instead of mma.sync. (LLMTIE_B200_F32_GENERAL keeps such calls
-    // on the general kernel: an A/B switch.)
-    static const bool f32_general = getenv("LLMTIE_B200_F32_GENERAL") != nullptr;
+    // Caches the tensor-memory kernel cannot lay its tiles over go through an
+    // f16 copy of their live keys, in caches of the handle's own, first:
+    // - f32 caches (Whisper's self-attention twins, the speech LM's prefill,
+    //   the flow model's attention): the fused kernels round K and V to f16 as
+    //   they read them (crates/llmtie-cuda/src/kernels.rs:3078-3269), so the
+    //   live keys are rounded once and the same numbers go through tcgen05
+    //   instead of mma.sync;
+    // - f16 caches whose value rows are not 16-byte aligned (a capacity that
+    //   is not a multiple of 8, an odd address): re-strided bit for bit.
+    // (LLMTIE_B200_NO_STAGING keeps such calls on the general kernel: an A/B
+    // switch.)
+    static const bool no_staging = getenv("LLMTIE_B200_NO_STAGING") != nullptr;
     bool staged = false;
-    if (kv_f32 && !f32_general && ((uintptr_t)v & 7u) == 0 && cap % 2 == 0) {
+    if (!no_staging && (kv_f32 || !use_tc(p, (int)hd))) {
         const size_t live = past + tq;
         const size_t cap16 = (live + 7) / 8 * 8;
         const size_t half = kv_heads * cap16 * hd * sizeof(uint16_t);
@@ -865,8 +869,8 @@ static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q,
             uint16_t *v16 = (uint16_t *)((char *)work + (half + 255) / 256 * 256);
             {
                 LaunchScope ls(g, "caches_to_f16");
-                launch_caches_to_f16(g->stream, (const float *)k, (const float *)v, k16, v16,
-                                     (int)kv_heads, (int)hd, (int)cap, (int)cap16, (int)live);
+                launch_caches_to_f16(g->stream, k, v, kv_f32, k16, v16, (int)kv_heads, (int)hd,
+                                     (int)cap, (int)cap16, (int)live);
                 const llmtie_status st = ls.done();
                 if (st != LLMTIE_OK) return st;
             }
@@ -877,7 +881,7 @@ static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q,
         }
     }
     // kprof tells the two kernels apart: the tensor-memory one is charged to
-    // "flash_attn_h_tc" (f16 caches) or "flash_attn_tc" (f32 caches, staged)
+    // "flash_attn_h_tc" (f16 caches as they lie) or "flash_attn_tc" (staged)
     const bool tc = staged || use_tc(p, (int)hd);
     LaunchScope ls(g, tc ? (staged ? "flash_attn_tc" : "flash_attn_h_tc") : name);
     const cudaError_t e = tc ? launch_prefill_tc(g->stream, p, (int)hd, next_wait_ctl(g))

@@ -57,7 +57,7 @@ struct llmtie_gpu {
     std::vector<llmtie_decode_scratch *> scratches;
     Workspace ws_rope;   // the ragged prefill's table of cosines and sines (or its copy of q)
     Workspace ws_part;   // partial results of a prefill whose long row blocks were cut
-    Workspace ws_kv16;   // f16 copies of the live keys of f32 caches, for the tensor-memory prefill
+    Workspace ws_kv16;   // f16 copies of the live keys of caches the tensor-memory prefill cannot map
 };
 
 // The caches a tensor map was made for: a map is made again only when one of
@@ -120,9 +120,11 @@ void launch_cache_append(cudaStream_t st, const float *src, long long src_off, v
 void launch_cache_grow(cudaStream_t st, const void *src, void *dst, long long rows,
                        long long len, long long src_stride, long long dst_stride, int esize);
 void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n);
-// the live keys of f32 caches as f16 caches of capacity cap16 (a multiple of 8)
-void launch_caches_to_f16(cudaStream_t st, const float *k32, const float *v32, uint16_t *k16,
-                          uint16_t *v16, int kv_heads, int hd, int cap, int cap16, int live);
+// the live keys of f32 (rounded) or f16 (re-strided) caches as f16 caches of
+// capacity cap16 (a multiple of 8)
+void launch_caches_to_f16(cudaStream_t st, const void *k, const void *v, bool src_f32,
+                          uint16_t *k16, uint16_t *v16, int kv_heads, int hd, int cap, int cap16,
+                          int live);
 void launch_rope_gptj(cudaStream_t st, float *x, const float *inv_freq, int positions, int dim,
                       int rot_dim);
 void launch_split_heads_f32(cudaStream_t st, const float *x, float *out, int t, int heads, int hd,

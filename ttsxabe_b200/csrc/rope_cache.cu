@@ -272,12 +272,18 @@ __global__ void round_f16_kernel(const float *__restrict__ src, uint16_t *__rest
     if (i < n) dst[i] = f16_bits(src[i]);
 }
 
-// The live part of a pair of f32 caches as f16 caches of capacity `cap16`
-// (live rounded up to eight keys): K [kv][cap][hd] -> [kv][cap16][hd], V
-// [kv][hd][cap] -> [kv][hd][cap16], rounded to nearest as the attention
-// kernels round their operands, what lies past the live keys zero. A thread a
+// The live part of a pair of caches as f16 caches of capacity `cap16` (live
+// rounded up to eight keys): K [kv][cap][hd] -> [kv][cap16][hd], V
+// [kv][hd][cap] -> [kv][hd][cap16], what lies past the live keys zero. f32
+// caches are rounded to nearest, as the attention kernels round their
+// operands; f16 caches (T = uint16_t: a capacity or an address the copy
+// engine's tiles cannot be laid over) are re-strided bit for bit. A thread a
 // pair of neighbouring elements of either output.
-__global__ void caches_to_f16_kernel(const float *__restrict__ k32, const float *__restrict__ v32,
+__device__ __forceinline__ uint32_t as_f16_bits(float x) { return f16_bits(x); }
+__device__ __forceinline__ uint32_t as_f16_bits(uint16_t x) { return x; }
+
+template <typename T>
+__global__ void caches_to_f16_kernel(const T *__restrict__ k32, const T *__restrict__ v32,
                                      uint32_t *__restrict__ k16, uint32_t *__restrict__ v16,
                                      int kv_heads, int hd, int cap, int cap16, int live)
 {
@@ -292,17 +298,17 @@ __global__ void caches_to_f16_kernel(const float *__restrict__ k32, const float 
             const int r = (int)(row % cap16), h = (int)(row / cap16);
             uint32_t w = 0u;
             if (r < live) {
-                const float2 x = *(const float2 *)(k32 + ((long long)h * cap + r) * hd + d);
-                w = (uint32_t)f16_bits(x.x) | ((uint32_t)f16_bits(x.y) << 16);
+                const T *src = k32 + ((long long)h * cap + r) * hd + d;
+                w = as_f16_bits(src[0]) | (as_f16_bits(src[1]) << 16);
             }
             k16[i] = w;
         } else {
             const long long e = 2 * (i - nk);           // element of [kv][hd][cap16]
             const int c = (int)(e % cap16);
             const long long row = e / cap16;            // h * hd + d
-            const float *src = v32 + row * cap + c;
-            const uint32_t lo = c < live ? f16_bits(src[0]) : 0u;
-            const uint32_t hi = c + 1 < live ? f16_bits(src[1]) : 0u;
+            const T *src = v32 + row * cap + c;
+            const uint32_t lo = c < live ? as_f16_bits(src[0]) : 0u;
+            const uint32_t hi = c + 1 < live ? as_f16_bits(src[1]) : 0u;
             v16[i - nk] = lo | (hi << 16);
         }
     }
@@ -819,12 +825,20 @@ void launch_rope_gptj(cudaStream_t st, float *x, const float *inv_freq, int posi
                                                          wide);
 }
 
-void launch_caches_to_f16(cudaStream_t st, const float *k32, const float *v32, uint16_t *k16,
-                          uint16_t *v16, int kv_heads, int hd, int cap, int cap16, int live)
+void launch_caches_to_f16(cudaStream_t st, const void *k, const void *v, bool src_f32,
+                          uint16_t *k16, uint16_t *v16, int kv_heads, int hd, int cap, int cap16,
+                          int live)
 {
     const size_t pairs = (size_t)kv_heads * cap16 * hd;      // half of each cache, twice
-    caches_to_f16_kernel<<<flat_blocks(pairs, 256), 256, 0, st>>>(
-        k32, v32, (uint32_t *)k16, (uint32_t *)v16, kv_heads, hd, cap, cap16, live);
+    if (src_f32) {
+        caches_to_f16_kernel<float><<<flat_blocks(pairs, 256), 256, 0, st>>>(
+            (const float *)k, (const float *)v, (uint32_t *)k16, (uint32_t *)v16, kv_heads, hd, cap,
+            cap16, live);
+    } else {
+        caches_to_f16_kernel<uint16_t><<<flat_blocks(pairs, 256), 256, 0, st>>>(
+            (const uint16_t *)k, (const uint16_t *)v, (uint32_t *)k16, (uint32_t *)v16, kv_heads,
+            hd, cap, cap16, live);
+    }
 }
 
 void launch_round_f16(cudaStream_t st, const float *src, uint16_t *dst, size_t n)
