@@ -1128,17 +1128,26 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
                                    const llmtie_exchange *xch = nullptr,
                                    const FusedMerge *fused = nullptr)
 {
-    bool aligned = true;
+    // `aligned`: a tensor map can be laid over the value rows too; `ring`: the
+    // ring kernel can take the launch (the keys by TMA; value rows that are
+    // only 8-byte aligned by cp.async from the lanes)
+    bool aligned = true, ring = true;
     for (int b = 0; b < p.nseq; b++) {
         if (p.seq[b].cap % 8 != 0 || ((uintptr_t)p.seq[b].v & 15u) != 0) aligned = false;
+        if (p.seq[b].cap % 4 != 0 || ((uintptr_t)p.seq[b].v & 7u) != 0 ||
+            ((uintptr_t)p.seq[b].k & 15u) != 0) {
+            ring = false;
+        }
     }
     static const bool no_stream = getenv("LLMTIE_B200_DECODE_NO_STREAM") != nullptr;
+    static const bool no_plain = getenv("LLMTIE_B200_DECODE_NO_PLAIN_V") != nullptr;
+    if (no_plain && !aligned) ring = false;
     if (xch && !aligned) {
         return llmtie_fail(LLMTIE_ERR_MISALIGNED,
                            "the exchanging decode wants 16-byte aligned caches and capacities "
                            "that are multiples of 8");
     }
-    if (aligned && (!no_stream || xch)) {
+    if (ring && (!no_stream || xch)) {
         // The ring kernel, cut by work: one block per SM, never more blocks
         // than 128-key units.
         DecodeStreamParams sp;
@@ -1173,14 +1182,15 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         sp.twin_s = p.twin_s;
         sp.status = g->timeout_site;
         sp.wait_cycles = g->wait_cycles;
+        sp.v_plain = aligned ? 0 : 1;
         // The tensor maps of the caches, kept with the scratch: they are made
         // again only when a cache has moved or changed shape.
         for (int b = 0; b < p.nseq; b++) {
             DecodeMapKey &key = scratch->map_key[b];
             if (key.k != p.seq[b].k || key.v != p.seq[b].v || key.cap != p.seq[b].cap ||
                 key.kv_heads != p.kv_heads || key.hd != hd) {
-                if (!decode_tensor_maps(&scratch->kmap[b], &scratch->vmap[b], p.seq[b].k,
-                                        p.seq[b].v, p.kv_heads, p.seq[b].cap, hd)) {
+                if (!decode_tensor_maps(&scratch->kmap[b], aligned ? &scratch->vmap[b] : nullptr,
+                                        p.seq[b].k, p.seq[b].v, p.kv_heads, p.seq[b].cap, hd)) {
                     key = DecodeMapKey();
                     return llmtie_fail(LLMTIE_ERR_DRIVER, "making the tensor maps of a cache");
                 }

@@ -271,6 +271,11 @@ struct DecodeStreamParams {
     // thread-block cluster, which merge through distributed shared memory; no
     // run crosses a pair, no partial goes through global memory.
     int by_cluster;
+    // Value rows that are only 8-byte aligned (a capacity that is a multiple of
+    // 4 but not of 8: no tensor map can be laid over them): the value blocks
+    // come by 8-byte cp.async from the lanes instead, into the same swizzled
+    // layout; the keys still come by TMA. vmap is not used then.
+    int v_plain;
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
 // The two tensor maps the ring kernel reads one sequence's caches through:
@@ -278,6 +283,7 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, i
 // swizzle), values [kv][hd][cap] seen as kv*hd rows of `cap` (boxes of hd rows
 // x 64 bytes, 64-byte swizzle): what ldmatrix reads without bank conflicts.
 // Reads past the end return zero.
+// (vmap may be null: the key map alone)
 bool decode_tensor_maps(CUtensorMap *kmap, CUtensorMap *vmap, const void *k, const void *v,
                         int kv_heads, int cap, int hd);
 // cuTensorMapEncodeTiled for f16 data, through the runtime's driver entry point.

@@ -424,8 +424,10 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     // segments of the block's run.
     const uint32_t bar0 = smem_u32(&sm_bar[warp][0]);
     if (lane == 0) {
+        // one arrival a stage (the lane that announces the bytes), and where the
+        // values come by cp.async one more of every lane, when its copies land
 #pragma unroll
-        for (int s = 0; s < kStages; s++) mbar_init(bar0 + 8u * s, 1);
+        for (int s = 0; s < kStages; s++) mbar_init(bar0 + 8u * s, p.v_plain ? 33u : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -490,16 +492,39 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
         const CUtensorMap *kmap = &p.kmap[b];
         const CUtensorMap *vmap = &p.vmap[b];
         const int krow0 = kh * cap, vrow0 = kh * HD;
+        const uint16_t *vsrc = (const uint16_t *)p.seq[b].v + (size_t)vrow0 * cap;
         auto issue = [&](int blk) {
+            const uint32_t dst = ring_s + st_put * STAGE;
+            const uint32_t bar = bar0 + 8u * st_put;
             if (lane == 0) {
-                const uint32_t dst = ring_s + st_put * STAGE;
-                const uint32_t bar = bar0 + 8u * st_put;
-                mbar_expect_tx(bar, STAGE);
+                mbar_expect_tx(bar, p.v_plain ? KBYTES : STAGE);
 #pragma unroll
                 for (int kt = 0; kt < HD / 64; kt++) {
                     tma_load_2d(dst + kt * KSUB, kmap, bar, 64 * kt, krow0 + blk);
                 }
-                tma_load_2d(dst + KBYTES, vmap, bar, blk, vrow0);
+                if (!p.v_plain) tma_load_2d(dst + KBYTES, vmap, bar, blk, vrow0);
+            }
+            if (p.v_plain) {
+                // Eight lanes a channel row, 8 bytes (four keys) a lane, into the
+                // layout the tensor map's 64-byte swizzle would have made: 16-byte
+                // chunk c of row d at chunk c ^ ((d >> 1) & 3). Four keys are inside
+                // the cache or outside it together (its capacity is a multiple of
+                // four); outside, nothing is read and zeros are written.
+                const int j = lane & 7;                          // which 8 bytes of the row
+                const uint32_t bytes = (blk + 4 * j < cap) ? 8u : 0u;
+#pragma unroll
+                for (int i = 0; i < HD / 4; i++) {
+                    const int d = 4 * i + (lane >> 3);
+                    const uint32_t to = dst + KBYTES + (uint32_t)d * 64u +
+                                        (uint32_t)(((j >> 1) ^ ((d >> 1) & 3)) << 4) +
+                                        (uint32_t)(j & 1) * 8u;
+                    const uint16_t *from = vsrc + (size_t)d * cap + blk + 4 * j;
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(to),
+                                 "l"(bytes ? from : vsrc), "r"(bytes)
+                                 : "memory");
+                }
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar)
+                             : "memory");
             }
             st_put = (st_put + 1 == kStages) ? 0u : st_put + 1;
         };
@@ -902,6 +927,7 @@ bool decode_tensor_maps(CUtensorMap *kmap, CUtensorMap *vmap, const void *k, con
     const uint64_t ks[1] = {(uint64_t)hd * 2};
     const uint32_t kb[2] = {64, 32};
     if (!llmtie_encode_tiled_f16(kmap, 2, k, kd, ks, kb, 128)) return false;
+    if (!vmap) return true;
     // values: a row of `cap` keys per (kv head, channel); a box is hd rows by 32 keys
     const uint64_t vd[2] = {(uint64_t)cap, (uint64_t)kv_heads * (uint64_t)hd};
     const uint64_t vs[1] = {(uint64_t)cap * 2};
