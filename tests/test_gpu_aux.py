@@ -169,6 +169,47 @@ print("general kernel ok")
     assert done.returncode == 0 and "general kernel ok" in done.stdout, done.stdout + done.stderr
 
 
+def test_the_register_fed_decode_kernel_behind_its_switch():
+    """With LLMTIE_B200_DECODE_NO_STREAM the ring kernel is never taken (read
+    once a process, hence the child): the register-fed kernel - otherwise only
+    reached by caches at addresses the ring cannot copy from - serves aligned
+    capacities and those that are multiples of 4 only, at the same bar, twice
+    through one scratch."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import numpy as np
+from oracle import oracle as O
+from tests.helpers import assert_close_to
+from ttsxabe_b200 import Gpu, DecodeScratch
+gpu = Gpu.open(0)
+gpu.kprof_enable(True)
+for i, (heads, kv, hd, tk, cap, scale_q) in enumerate([(8, 2, 128, 256, 256, False), (6, 6, 64, 1499, 1500, True),
+                                                      (32, 8, 128, 7777, 8192, False), (14, 2, 64, 700, 1024, False),
+                                                      (20, 20, 64, 1500, 1500, True)]):
+    q = O.seq(heads * hd, 300 + i)
+    k0, v0 = O.seq(kv * cap * hd, 400 + i), O.seq(kv * hd * cap, 500 + i)
+    scratch = DecodeScratch()
+    dq, dk, dv = gpu.upload(q), gpu.upload_f16(k0), gpu.upload_f16(v0)
+    a = gpu.download(gpu.attn_decode_f16(dq, dk, dv, heads, kv, hd, tk, cap, 0.11, scale_q, scratch))
+    b = gpu.download(gpu.attn_decode_f16(dq, dk, dv, heads, kv, hd, tk, cap, 0.11, scale_q, scratch))
+    assert np.array_equal(a, b)
+    want = O.decode_f64(q, O.round_f16(k0), O.round_f16(v0), heads, kv, hd, 0, tk, cap, 0.11, scale_q)
+    assert_close_to(str((heads, kv, hd, tk, cap)), want, a, 2e-5)
+rep = gpu.kprof_report()
+assert not any(name.endswith("_run") for name in rep), rep
+assert sum(c for name, (c, _) in rep.items() if name.startswith("attn_decode_h")) == 10, rep
+print("register-fed kernel ok")
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, LLMTIE_B200_DECODE_NO_STREAM="1", PYTHONPATH=root)
+    done = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True,
+                          text=True, timeout=600)
+    assert done.returncode == 0 and "register-fed kernel ok" in done.stdout, done.stdout + done.stderr
+
+
 def test_kernel_resources_are_what_the_compiler_gave(gpu):
     """(registers a thread, local bytes a thread, static shared bytes a block)
     per kernel name; None for a name that is not in the library."""
