@@ -1101,6 +1101,30 @@ static bool cluster_cut(DecodeStreamParams &p, int dev, int hd, int sm_count, in
     return true;
 }
 
+// Whether every pair simply gets a block of its own: pairs of one length,
+// more of them than half the SMs (two blocks a pair do not fit), and short
+// enough that a block walking its pair alone ends before the work cut's
+// blocks would - those share the bytes over every SM but end with a merge
+// through global memory (about 4 us of fence, arrival count and reload). A
+// block streams about 52 GB/s.
+static bool pair_cut(DecodeStreamParams &p, int hd, int sm_count, int *grid)
+{
+    static const bool never = getenv("LLMTIE_B200_DECODE_NO_CLUSTER") != nullptr;
+    const long long pairs = (long long)p.nseq * p.kv_heads * p.row_chunks;
+    if (never || pairs > sm_count || pairs * 2 <= sm_count || pairs > LLMTIE_STREAM_MAX_BLOCKS) {
+        return false;
+    }
+    const int n = (p.seq[0].tk + 127) / 128;
+    for (int b = 1; b < p.nseq; b++) {
+        if ((p.seq[b].tk + 127) / 128 != n) return false;
+    }
+    const double unit_us = (hd == 128 ? 65536.0 : 32768.0) / 52.0e3;     // a unit of one block
+    if (n * unit_us * (1.0 - (double)pairs / sm_count) >= 4.0) return false;
+    for (long long q = 0; q <= pairs; q++) p.ustart[q] = (int)(q * n);
+    *grid = (int)pairs;
+    return true;
+}
+
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in, int hd, int grid)
 {
     if (grid < 1 || grid > LLMTIE_STREAM_MAX_BLOCKS || p_in.total_units > 0x7fffffffLL ||
@@ -1120,7 +1144,9 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in
                              cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes<64>());
         configured[dev] = true;
     }
-    if (!cluster_cut(p, dev, hd, sms, &grid)) stream_partition(p, hd, grid);
+    if (!cluster_cut(p, dev, hd, sms, &grid) && !pair_cut(p, hd, sms, &grid)) {
+        stream_partition(p, hd, grid);
+    }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(grid);
