@@ -1104,9 +1104,11 @@ static bool cluster_cut(DecodeStreamParams &p, int dev, int hd, int sm_count, in
 // Whether every pair simply gets a block of its own: pairs of one length,
 // more of them than half the SMs (two blocks a pair do not fit), and short
 // enough that a block walking its pair alone ends before the work cut's
-// blocks would - those share the bytes over every SM but end with a merge
-// through global memory (about 4 us of fence, arrival count and reload). A
-// block streams about 52 GB/s.
+// blocks would - those share the bytes over every SM, but a run that crosses
+// from one pair into the next drains and refills its ring, and every pair
+// ends with a merge through global memory (fence, arrival count, reload):
+// about 8 us against a block a pair, measured on 128 pairs of 8 and 16 units.
+// A block streams about 52 GB/s.
 static bool pair_cut(DecodeStreamParams &p, int hd, int sm_count, int *grid)
 {
     static const bool never = getenv("LLMTIE_B200_DECODE_NO_CLUSTER") != nullptr;
@@ -1119,7 +1121,7 @@ static bool pair_cut(DecodeStreamParams &p, int hd, int sm_count, int *grid)
         if ((p.seq[b].tk + 127) / 128 != n) return false;
     }
     const double unit_us = (hd == 128 ? 65536.0 : 32768.0) / 52.0e3;     // a unit of one block
-    if (n * unit_us * (1.0 - (double)pairs / sm_count) >= 4.0) return false;
+    if (n * unit_us * (1.0 - (double)pairs / sm_count) >= 8.0) return false;
     for (long long q = 0; q <= pairs; q++) p.ustart[q] = (int)(q * n);
     *grid = (int)pairs;
     return true;
