@@ -229,6 +229,50 @@ def test_ragged_prefill_of_short_prompts(gpu):
         assert np.abs(O.widen_f16(gpu.download_u16(kcs[b])) - O.widen_f16(kc)).max() <= 4e-3
 
 
+def test_ragged_prefill_with_empty_sequences(gpu):
+    """A batch in which some sequences bring no new token (cu_seqlens repeats
+    an offset): they take no rows of q or out, their caches are not touched,
+    and the others come out as when prefilled alone. A batch of nothing but
+    empty sequences is a no-op."""
+    heads, kv, hd, cap = 32, 8, 128, 256
+    lens = [0, 37, 0, 130, 0]
+    pasts = [5, 0, 0, 9, 0]
+    batch = len(lens)
+    rng = np.random.default_rng(123)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    total = int(cu[-1])
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, total * heads * hd)
+    k = normal_f16(rng, total * kv * hd)
+    v = normal_f16(rng, total * kv * hd)
+    olds = [(O.round_f16(normal_f16(rng, kv * cap * hd)), O.round_f16(normal_f16(rng, kv * cap * hd)))
+            for _ in range(batch)]
+    kcs = [gpu.upload_u16(a) for a, _ in olds]
+    vcs = [gpu.upload_u16(b) for _, b in olds]
+    dq, dk, dv = gpu.upload(q), gpu.upload(k), gpu.upload(v)
+    got = gpu.download(gpu.prefill_varlen(dq, dk, dv, cu, kcs, vcs, pasts, [cap] * batch, None,
+                                          heads, kv, hd, 10000.0, scale)).reshape(total, -1)
+    for b in range(batch):
+        n, r0 = lens[b], int(cu[b])
+        if n == 0:
+            assert np.array_equal(gpu.download_u16(kcs[b]), olds[b][0])
+            assert np.array_equal(gpu.download_u16(vcs[b]), olds[b][1])
+            continue
+        kc1, vc1 = gpu.upload_u16(olds[b][0]), gpu.upload_u16(olds[b][1])
+        rows = lambda x, w: gpu.upload(x.reshape(total, w)[r0:r0 + n].reshape(-1))
+        alone = gpu.download(gpu.prefill_varlen(rows(q, heads * hd), rows(k, kv * hd), rows(v, kv * hd),
+                                                [0, n], [kc1], [vc1], [pasts[b]], [cap], None, heads,
+                                                kv, hd, 10000.0, scale))
+        assert np.array_equal(got[r0:r0 + n].reshape(-1), alone), f"sequence {b}"
+        assert np.array_equal(gpu.download_u16(kcs[b]), gpu.download_u16(kc1))
+        assert np.array_equal(gpu.download_u16(vcs[b]), gpu.download_u16(vc1))
+    # nothing but empty sequences
+    none = gpu.prefill_varlen(gpu.zeros(heads * hd), gpu.zeros(kv * hd), gpu.zeros(kv * hd), [0, 0, 0],
+                              kcs[:2], vcs[:2], [5, 0], [cap, cap], None, heads, kv, hd, 10000.0, scale)
+    gpu.synchronize()
+    assert np.array_equal(gpu.download_u16(kcs[0]), olds[0][0])
+
+
 def test_ragged_prefill_of_more_sequences_than_one_launch_maps(gpu):
     """Eleven sequences: the tensor-core kernel carries eight tensor maps a
     launch, so the batch goes in groups; the second group holds a 40-token

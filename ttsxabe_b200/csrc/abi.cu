@@ -1753,19 +1753,24 @@ extern "C" llmtie_status llmtie_prefill_varlen(
         memset(&vp, 0, sizeof(vp));
         memset(&pp, 0, sizeof(pp));
         const int base = cu_seqlens[b0];
-        vp.nseq = pp.nseq = (int)nb;
+        // (a sequence that brings no new token takes no part: it has no rows,
+        // its caches are not touched, and a tensor map of no keys cannot be made)
+        int m = 0;
         for (size_t b = 0; b < nb; b++) {
             const int row0 = cu_seqlens[b0 + b] - base;
             const int n = cu_seqlens[b0 + b + 1] - cu_seqlens[b0 + b];
-            vp.seq[b] = {k_ptrs[b0 + b], v_ptrs[b0 + b], row0, n, past[b0 + b], cap[b0 + b]};
-            pp.seq[b].k = k_ptrs[b0 + b];
-            pp.seq[b].v = v_ptrs[b0 + b];
-            pp.seq[b].row0 = row0;
-            pp.seq[b].tq = n;
-            pp.seq[b].past = past[b0 + b];
-            pp.seq[b].cap = cap[b0 + b];
-            pp.seq[b].tk = past[b0 + b] + n;
+            if (n == 0) continue;
+            vp.seq[m] = {k_ptrs[b0 + b], v_ptrs[b0 + b], row0, n, past[b0 + b], cap[b0 + b]};
+            pp.seq[m].k = k_ptrs[b0 + b];
+            pp.seq[m].v = v_ptrs[b0 + b];
+            pp.seq[m].row0 = row0;
+            pp.seq[m].tq = n;
+            pp.seq[m].past = past[b0 + b];
+            pp.seq[m].cap = cap[b0 + b];
+            pp.seq[m].tk = past[b0 + b] + n;
+            m++;
         }
+        vp.nseq = pp.nseq = m;
         vp.total = cu_seqlens[b0 + nb] - base;
         if (vp.total == 0) continue;
         const float *q0 = q + (size_t)base * heads * head_dim;
