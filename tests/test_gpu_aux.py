@@ -225,3 +225,36 @@ def test_kernel_resources_are_what_the_compiler_gave(gpu):
     # the key loop of the ring kernel must not spill
     assert seen["attn_decode_h128_run"][1] == 0
     assert gpu.kernel_resources("no_such_kernel") is None
+
+
+def test_calls_with_nothing_to_do_launch_nothing(gpu):
+    """Zero rows, zero new tokens, zero sequences, zero layers: every entry
+    answers OK, launches nothing and writes nothing (the reference's methods
+    return early on empty work, e.g. crates/llmtie-cuda/src/device.rs:5702-5745
+    on `tq == 0`)."""
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, kv, hd, cap = 8, 2, 128, 64
+    buf = O.seq(4 * heads * hd, 9)
+    x = gpu.upload(buf)
+    kc, vc = gpu.zeros_f16(kv * cap * hd), gpu.zeros_f16(kv * cap * hd)
+    k32, v32 = gpu.zeros(kv * cap * hd), gpu.zeros(kv * cap * hd)
+    ck, cv = gpu.zeros_f16(heads * cap * hd), gpu.zeros_f16(heads * cap * hd)   # a cache a query head
+    scratch = DecodeScratch()
+    gpu.synchronize()
+    before = gpu.launch_count()
+    gpu.rope(x, 0, 0, heads, hd, 10000.0, 0)
+    gpu.cache_append_f16(x, 0, kc, 0, kv, hd, cap, 3, False)
+    gpu.cache_append(x, 0, k32, 0, kv, hd, cap, 3, True)
+    gpu.flash_attn_f16(x, kc, vc, 0, 5, heads, kv, hd, cap, 0.1, True)
+    gpu.flash_attn(x, k32, v32, 0, 5, heads, kv, hd, cap, 0.1, True)
+    gpu.flash_attn_rows(gpu.upload(O.seq(3 * 20 * 64, 1)), 0, 20, 64, 0.125)
+    gpu.cross_attn(x, ck, cv, 0, heads, hd, 10, cap, 0.1, scratch)
+    gpu.split_heads(x, 0, heads, hd)
+    gpu.prefill_varlen(x, x, x, [0, 0], [kc], [vc], [0], [cap], None, heads, kv, hd, 10000.0, 0.1)
+    gpu.prefill_varlen(x, x, x, [0], [], [], [], [], None, heads, kv, hd, 10000.0, 0.1)
+    gpu.lse_merge(x, 0, 4, hd)
+    gpu.synchronize()
+    assert gpu.launch_count() == before
+    assert np.array_equal(gpu.download(x), buf)
+    assert not gpu.download_u16(kc).any() and not gpu.download(k32).any()
