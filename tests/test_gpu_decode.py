@@ -40,6 +40,14 @@ CASES = [
     (16, 2, 64, 333, 512, True, False),
     (12, 4, 128, 500, 512, True, False),
     (14, 2, 64, 9000, 9004, True, True),
+    # the first keys of a conversation: one key, and either side of a 32-key block
+    (32, 8, 128, 1, 256, True, False),
+    (32, 8, 128, 2, 256, True, False),
+    (32, 8, 128, 31, 256, True, False),
+    (32, 8, 128, 33, 256, True, False),
+    (20, 20, 64, 1, 448, True, True),
+    (20, 20, 64, 1, 448, False, True),
+    (20, 20, 64, 65, 448, False, True),
 ]
 
 

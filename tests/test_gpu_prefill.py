@@ -34,6 +34,10 @@ SIZED = [
     (8, 2, 128, True, 1, 0, 8, True),
     (8, 2, 128, True, 30, 33, 64, True),
     (8, 2, 128, False, 70, 0, 72, True),
+    # one new row on a long past; one row into a second row block
+    (8, 2, 128, True, 1, 200, 256, True),
+    (8, 2, 128, True, 129, 0, 136, True),
+    (8, 2, 128, True, 1, 1000, 1008, True),
     (4, 4, 64, False, 300, 0, 300, False),
     # crates/llmtie-cosy's callers, both off f32 caches: the speech LM's prefill
     # (14 / 2 heads, a group of 7; src/llm.rs:448-475) and the flow model's
