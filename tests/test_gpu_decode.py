@@ -391,6 +391,35 @@ def test_the_twin_row_variant_fills_one_row_and_refuses_short_buffers(gpu):
                                   short, 1)
 
 
+def test_one_scratch_through_aligned_and_unaligned_launches(gpu):
+    """A scratch keeps the tensor maps of the caches it has seen. A cache with
+    16-byte aligned value rows that is first decoded beside one whose rows are
+    only 8-byte aligned (no value map is made for that launch) must still get
+    its value map when it is decoded alone afterwards; and the other way
+    round."""
+    from ttsxabe_b200 import DecodeScratch
+
+    heads, kv, hd = 20, 20, 64
+    rng = np.random.default_rng(5)
+    caps, tks = [1504, 1500], [1400, 1500]
+    q = normal_f16(rng, 2 * heads * hd)
+    kb = [O.round_f16(normal_f16(rng, kv * c * hd)) for c in caps]
+    vb = [O.round_f16(normal_f16(rng, kv * c * hd)) for c in caps]
+    ks, vs = [gpu.upload_u16(x) for x in kb], [gpu.upload_u16(x) for x in vb]
+    want = [O.decode_f64(q.reshape(2, -1)[i], kb[i], vb[i], heads, kv, hd, 0, tks[i], caps[i], 0.125,
+                         True) for i in range(2)]
+    scratch = DecodeScratch()
+    dq = gpu.upload(q)
+    both = gpu.download(gpu.decode_batched(dq, ks, vs, tks, caps, heads, kv, hd, 0.125, True,
+                                           scratch)).reshape(2, -1)
+    for i in range(2):
+        assert_close_to(f"together, sequence {i}", want[i], both[i], 2e-5)
+    for i in (0, 1, 0):
+        one = gpu.download(gpu.decode_batched(gpu.upload(q.reshape(2, -1)[i]), [ks[i]], [vs[i]],
+                                              [tks[i]], [caps[i]], heads, kv, hd, 0.125, True, scratch))
+        assert_close_to(f"alone, sequence {i}", want[i], one, 2e-5)
+
+
 @pytest.mark.parametrize("shape", [
     # heads, kv, hd, batch, keys, capacity: 64 or 72 pairs of equal length
     (32, 8, 128, 8, 3000, 3072), (64, 64, 64, 1, 2500, 2560), (36, 9, 128, 8, 2049, 2056),

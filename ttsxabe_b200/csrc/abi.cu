@@ -1188,7 +1188,7 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
         for (int b = 0; b < p.nseq; b++) {
             DecodeMapKey &key = scratch->map_key[b];
             if (key.k != p.seq[b].k || key.v != p.seq[b].v || key.cap != p.seq[b].cap ||
-                key.kv_heads != p.kv_heads || key.hd != hd) {
+                key.kv_heads != p.kv_heads || key.hd != hd || (aligned && !key.has_v)) {
                 if (!decode_tensor_maps(&scratch->kmap[b], aligned ? &scratch->vmap[b] : nullptr,
                                         p.seq[b].k, p.seq[b].v, p.kv_heads, p.seq[b].cap, hd)) {
                     key = DecodeMapKey();
@@ -1199,6 +1199,7 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
                 key.cap = p.seq[b].cap;
                 key.kv_heads = p.kv_heads;
                 key.hd = hd;
+                key.has_v = aligned;
             }
             sp.kmap[b] = scratch->kmap[b];
             sp.vmap[b] = scratch->vmap[b];

@@ -66,6 +66,7 @@ struct DecodeMapKey {
     const void *k = nullptr;
     const void *v = nullptr;
     int cap = 0, kv_heads = 0, hd = 0;
+    bool has_v = false;   // the value map was made too (it is not where the values come by cp.async)
 };
 
 struct llmtie_decode_scratch {
