@@ -448,11 +448,6 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
     const int G = gridDim.x;
     const int u0 = p.ustart[blockIdx.x];
     const int u1 = p.ustart[blockIdx.x + 1];
-    // (only the merge of runs that share a pair looks the cut up; clusters do not)
-    if (!p.by_cluster) {
-        for (int i = threadIdx.x; i <= G; i += kThreads) sm_ustart[i] = p.ustart[i];
-    }
-    // (the first segment's barriers order these stores before their first use)
 
     int u = u0;
     while (u < u1) {
@@ -555,6 +550,13 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
 #pragma unroll
         for (int s = 0; s < kStages - 1; s++) {
             if (s < nblk) issue(first + s * kWarps * 32);
+        }
+        // The cut goes into shared memory now, under the first copies' flight:
+        // a lane an entry out of the parameter bank is a replay a lane. (Only
+        // the merge of runs that share a pair looks it up - clusters do not -
+        // and this segment's barriers order the stores before that.)
+        if (u == u0 && !p.by_cluster) {
+            for (int i = threadIdx.x; i <= G; i += kThreads) sm_ustart[i] = p.ustart[i];
         }
 
         // ---- query fragments, split hi / lo: a0 a2 carry the heads (rows 0-7 of
