@@ -101,3 +101,52 @@ def test_random_prefill_cases(gpu, seed):
     want = O.prefill(q, kc, vc, tq, past, heads, kv, hd, cap, scale, causal)
     assert_parity(f"prefill {heads}/{kv} hd {hd} tq {tq} past {past} cap {cap} causal {causal} "
                   f"f16 {half}", want, gpu.download(out))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_ragged_prefill_batches(gpu, seed):
+    """llmtie_prefill_varlen over a random batch - empty sequences, single
+    tokens, prompts on a kept prefix, more sequences than one attention launch
+    carries - gives every sequence the bits it gets when prefilled alone, in
+    the output and in both caches; one sequence is held to the oracle."""
+    rng = np.random.default_rng(4000 + seed)
+    heads, kv = GROUPS_128[int(rng.integers(0, 6))]
+    hd, cap = 128, 512
+    batch = int(rng.choice([1, 2, 3, 5, 9, 12]))
+    lens = [int(rng.choice([0, 1, 2, 17, 64, 127, 128, 129, 200, 300])) for _ in range(batch)]
+    pasts = [int(rng.choice([0, 0, 1, 33, 128, 200])) for _ in range(batch)]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    total = int(cu[-1])
+    scale = float(np.float32(hd) ** np.float32(-0.5))
+    q = normal_f16(rng, max(total, 1) * heads * hd)
+    k = normal_f16(rng, max(total, 1) * kv * hd)
+    v = normal_f16(rng, max(total, 1) * kv * hd)
+    olds = [(O.round_f16(normal_f16(rng, kv * cap * hd)), O.round_f16(normal_f16(rng, kv * cap * hd)))
+            for _ in range(batch)]
+    kcs = [gpu.upload_u16(a) for a, _ in olds]
+    vcs = [gpu.upload_u16(b) for _, b in olds]
+    got = gpu.download(gpu.prefill_varlen(gpu.upload(q), gpu.upload(k), gpu.upload(v), cu, kcs, vcs,
+                                          pasts, [cap] * batch, None, heads, kv, hd, 10000.0, scale))
+    got = got[:total * heads * hd].reshape(total, -1)
+    checked = False
+    for b in range(batch):
+        n, r0 = lens[b], int(cu[b])
+        if n == 0:
+            assert np.array_equal(gpu.download_u16(kcs[b]), olds[b][0]), f"seed {seed} sequence {b}"
+            continue
+        kc1, vc1 = gpu.upload_u16(olds[b][0]), gpu.upload_u16(olds[b][1])
+        rows = lambda x, w: gpu.upload(x[:total * w].reshape(total, w)[r0:r0 + n].reshape(-1))
+        alone = gpu.download(gpu.prefill_varlen(rows(q, heads * hd), rows(k, kv * hd), rows(v, kv * hd),
+                                                [0, n], [kc1], [vc1], [pasts[b]], [cap], None, heads,
+                                                kv, hd, 10000.0, scale))
+        name = f"seed {seed} lens {lens} pasts {pasts} sequence {b}"
+        assert np.array_equal(got[r0:r0 + n].reshape(-1), alone), name
+        assert np.array_equal(gpu.download_u16(kcs[b]), gpu.download_u16(kc1)), name
+        assert np.array_equal(gpu.download_u16(vcs[b]), gpu.download_u16(vc1)), name
+        if not checked:
+            checked = True
+            qr = O.rope(q[:total * heads * hd].reshape(total, -1)[r0:r0 + n].reshape(-1), n, heads, hd,
+                        10000.0, pasts[b])
+            want = O.prefill(qr, gpu.download_u16(kc1), gpu.download_u16(vc1), n, pasts[b], heads, kv,
+                             hd, cap, scale, True)
+            assert_parity(name + " (oracle)", want, alone)
