@@ -150,3 +150,40 @@ def test_random_ragged_prefill_batches(gpu, seed):
             want = O.prefill(qr, gpu.download_u16(kc1), gpu.download_u16(vc1), n, pasts[b], heads, kv,
                              hd, cap, scale, True)
             assert_parity(name + " (oracle)", want, alone)
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_encoder_rows_and_cross_attention(gpu, seed):
+    """The two Whisper entries at random sizes: flash_attn_rows over t frames
+    (one frame, either side of a 128-row tile, ragged last tiles) against the
+    oracle's non-causal prefill; cross-attention of n query rows over tk keys
+    in caches of a capacity whose value rows are 16- or only 8-byte aligned,
+    against the oracle's decode row by row."""
+    from ttsxabe_b200 import DecodeScratch
+
+    rng = np.random.default_rng(5000 + seed)
+    heads, hd = int(rng.choice([4, 6, 20])), 64
+    d = heads * hd
+    t = int(rng.choice([1, 7, 127, 128, 129, 300, 700]))
+    qkv = normal_f16(rng, t * 3 * d).reshape(t, 3 * d)
+    got = O.widen_f16(gpu.download_u16(gpu.flash_attn_rows(gpu.upload(qkv), t, heads, hd, 0.125)))
+    kc, vc = lay_caches(qkv[:, d:2 * d].reshape(t, heads, hd).transpose(1, 0, 2),
+                        qkv[:, 2 * d:].reshape(t, heads, hd).transpose(1, 0, 2), heads, t, hd, t)
+    want = O.prefill(np.ascontiguousarray(qkv[:, :d]), kc, vc, t, 0, heads, heads, hd, t, 0.125,
+                     False, scale_q=True, fast=True)
+    assert np.abs(want - got).max() <= 2e-3 + 2.0 ** -11 * np.abs(want).max(), f"rows t {t} heads {heads}"
+
+    n = int(rng.choice([1, 2, 5, 8, 13, 32]))
+    tk = int(rng.choice([1, 31, 130, 1000, 1500]))
+    cap = _capacity(rng, tk, int(rng.choice([4, 8])))
+    q = normal_f16(rng, n * d)
+    kc, vc = lay_caches(normal_f16(rng, heads * tk * hd), normal_f16(rng, heads * tk * hd), heads, tk,
+                        hd, cap)
+    kbits = poison_f16_bits(O.round_f16(kc), heads, tk, hd, cap, False)
+    vbits = poison_f16_bits(O.round_f16(vc), heads, tk, hd, cap, True)
+    out = gpu.download(gpu.cross_attn(gpu.upload(q), gpu.upload_u16(kbits), gpu.upload_u16(vbits), n,
+                                      heads, hd, tk, cap, 0.125, DecodeScratch())).reshape(n, -1)
+    for r in range(n):
+        want = O.decode_f64(q.reshape(n, -1)[r], O.round_f16(kc), O.round_f16(vc), heads, heads, hd, 0,
+                            tk, cap, 0.125, True)
+        assert_close_to(f"cross n {n} tk {tk} cap {cap} row {r}", want, out[r], 2e-5)
