@@ -187,3 +187,29 @@ def test_random_encoder_rows_and_cross_attention(gpu, seed):
         want = O.decode_f64(q.reshape(n, -1)[r], O.round_f16(kc), O.round_f16(vc), heads, heads, hd, 0,
                             tk, cap, 0.125, True)
         assert_close_to(f"cross n {n} tk {tk} cap {cap} row {r}", want, out[r], 2e-5)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_decode_off_f32_caches(gpu, seed):
+    """attn_decode over f32 caches (head_dim 64): one key to a few thousand,
+    so one block a head, a few, and eight of several chunks each; twice through
+    one scratch; NaN in the capacity past the live keys."""
+    from ttsxabe_b200 import DecodeScratch
+
+    rng = np.random.default_rng(6000 + seed)
+    heads, kv = GROUPS_64[int(rng.integers(0, 6))]
+    hd = 64
+    tk = int(rng.choice([1, 2, 63, 64, 65, 200, 448, 513, 1500, 4000])) + int(rng.integers(0, 2))
+    cap = _capacity(rng, tk, 2)
+    scale_q = bool(rng.integers(0, 2))
+    q = normal_f16(rng, heads * hd)
+    kc, vc = lay_caches(normal_f16(rng, kv * tk * hd), normal_f16(rng, kv * tk * hd), kv, tk, hd, cap,
+                        fill=np.nan)
+    want = O.decode_f32(q, np.nan_to_num(kc), np.nan_to_num(vc), heads, kv, hd, tk, cap, 0.125, scale_q)
+    dq, dk, dv = gpu.upload(q), gpu.upload(kc), gpu.upload(vc)
+    scratch = DecodeScratch()
+    a = gpu.download(gpu.attn_decode(dq, dk, dv, heads, kv, hd, tk, cap, 0.125, scale_q, scratch))
+    b = gpu.download(gpu.attn_decode(dq, dk, dv, heads, kv, hd, tk, cap, 0.125, scale_q, scratch))
+    name = f"f32 decode {heads}/{kv} tk {tk} cap {cap} scale_q {scale_q}"
+    assert np.array_equal(a, b), name
+    assert_close_to(name, want, a, 2e-5)
