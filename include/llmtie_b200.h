@@ -316,7 +316,9 @@ llmtie_status llmtie_attn_decode_f16_q(llmtie_gpu *g, const float *q, size_t q_l
                                        size_t out_len, size_t out_off, int8_t *codes,
                                        size_t codes_len, float *scales, size_t scales_len);
 /* Gpu::attn_decode (device.rs:6132-6168): the same off f32 caches, head_dim 64
- * (the Whisper decoder's self-attention). */
+ * (the Whisper decoder's self-attention). With a scratch every head's keys are
+ * cut over up to eight blocks whose partial results meet there; without one
+ * (NULL) the launch is one block a head. The key cache 16-byte aligned. */
 llmtie_status llmtie_attn_decode(llmtie_gpu *g, const float *q, size_t q_len, size_t q_off,
                                  const float *k, size_t k_len, const float *v,
                                  size_t v_len, size_t heads, size_t kv_heads,
