@@ -1834,6 +1834,10 @@ extern "C" llmtie_status llmtie_prefill_varlen(
             part.nseq = std::min(LLMTIE_TC_MAX_SEQ, pp.nseq - s0);
             for (int b = 0; b < part.nseq; b++) part.seq[b] = pp.seq[s0 + b];
             const bool tc = all_tc || use_tc(part, (int)head_dim);
+            // the first attention launch behind the one-launch pre-pass sets itself
+            // up under that kernel's tail (LLMTIE_B200_NO_PDL: an A/B switch)
+            static const bool no_pdl = getenv("LLMTIE_B200_NO_PDL") != nullptr;
+            part.after_prepass = (all_tc && s0 == 0 && !no_pdl && !g->kprof) ? 1 : 0;
             LaunchScope ls(g, tc ? "flash_attn_h_tc" : "flash_attn_h");
             const cudaError_t e =
                 tc ? launch_prefill_tc(g->stream, part, (int)head_dim, next_wait_ctl(g))

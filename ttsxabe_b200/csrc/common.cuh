@@ -340,6 +340,8 @@ struct PrefillParams {
     float q_scale;         // scale when it goes on q before rounding, else 1
     float sl2;             // (scale on the scores, else 1) * log2(e)
     const float *rope_tab; // tensor-memory kernel only: rotate q while staging it (see PrefillTcParams)
+    int after_prepass;     // tensor-memory kernel only: launch as the programmatic dependent of the
+                           // kernel before it in the stream (the pre-pass that writes rope_tab and the caches)
 };
 cudaError_t launch_prefill_mma(cudaStream_t st, const PrefillParams &p, int hd);
 

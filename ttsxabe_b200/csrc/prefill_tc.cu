@@ -448,6 +448,10 @@ prefill_tc_kernel(const __grid_constant__ PrefillTcParams p)
     const bool dead = abort_flag_s != 0;
     // a dependent kernel (the merge of cut row blocks) may be set up from here on
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // and where this launch is itself the dependent of the pre-pass that rotates
+    // the keys into the caches and leaves the cosines and sines, nothing of that
+    // kernel's is read before it has ended (a no-op in an ordinary launch)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // The register file is split by role: a warp scheduler holds one warp of
     // each warpgroup, and 208 + 208 + 88 registers are the 3 x 168 per lane the block was launched with (asking for more would wait forever).
@@ -1304,12 +1308,22 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, c
         tp.part_o = (float *)part;
         tp.part_ml = (float2 *)((char *)part + o_bytes);
     }
-    if (hd == 128) {
-        prefill_tc_kernel<128><<<grid, kThreads, Geo<128>::SMEM, st>>>(tp);
-    } else {
-        prefill_tc_kernel<64><<<grid, kThreads, Geo<64>::SMEM, st>>>(tp);
+    cudaError_t err;
+    {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = hd == 128 ? Geo<128>::SMEM : Geo<64>::SMEM;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = p.after_prepass ? 1 : 0;
+        err = hd == 128 ? cudaLaunchKernelEx(&cfg, prefill_tc_kernel<128>, tp)
+                        : cudaLaunchKernelEx(&cfg, prefill_tc_kernel<64>, tp);
     }
-    cudaError_t err = cudaGetLastError();
     if (part) {
         if (err == cudaSuccess) {
             // the row blocks that were cut: merge their pieces into the output

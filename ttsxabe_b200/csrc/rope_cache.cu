@@ -585,6 +585,10 @@ __global__ void varlen_append_v_kernel(const __grid_constant__ VarlenParams p)
 __global__ void __launch_bounds__(256)
 varlen_kv_kernel(const __grid_constant__ VarlenParams p, int rope_blocks, int ctiles, int ttiles)
 {
+    // The attention kernel that follows may be launched as this kernel's
+    // programmatic dependent: its blocks set themselves up meanwhile and wait
+    // for this kernel's end before they read what it writes.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int half = p.hd >> 1;
     if ((int)blockIdx.x < rope_blocks) {
         __shared__ float inv_s[kInvMax];
