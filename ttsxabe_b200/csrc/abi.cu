@@ -877,6 +877,8 @@ static llmtie_status flash_impl(llmtie_gpu *g, const char *name, const float *q,
             p = t;
             p.seq[0].k = k16;
             p.seq[0].v = v16;
+            static const bool no_pdl = getenv("LLMTIE_B200_NO_PDL") != nullptr;
+            p.after_prepass = (!no_pdl && !g->kprof) ? 1 : 0;   // under the copy's tail
             staged = true;
         }
     }
@@ -997,6 +999,9 @@ static llmtie_status flash_rows_impl(llmtie_gpu *g, const float *qkv, size_t qkv
         p.out_f16 = 1;
         p.q_scale = scale;   // on q before it is rounded, as the encoder does
         p.sl2 = kLog2e;
+        // (the first launch sets itself up under the staging kernel's tail)
+        static const bool no_pdl = getenv("LLMTIE_B200_NO_PDL") != nullptr;
+        p.after_prepass = (b0 == 0 && !no_pdl && !g->kprof) ? 1 : 0;
         const bool tc = use_tc(p, 64);
         LaunchScope ls(g, tc ? "flash_attn_64_rows_tc" : "flash_attn_64_rows");
         const cudaError_t e = tc ? launch_prefill_tc(g->stream, p, 64, next_wait_ctl(g))

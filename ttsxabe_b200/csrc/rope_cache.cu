@@ -287,6 +287,8 @@ __global__ void caches_to_f16_kernel(const T *__restrict__ k32, const T *__restr
                                      uint32_t *__restrict__ k16, uint32_t *__restrict__ v16,
                                      int kv_heads, int hd, int cap, int cap16, int live)
 {
+    // (the attention kernel behind this one may set itself up meanwhile)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const long long nk = (long long)kv_heads * cap16 * hd / 2;     // pairs of the key cache
     const long long nv = (long long)kv_heads * hd * cap16 / 2;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nk + nv;
@@ -324,6 +326,8 @@ __global__ void __launch_bounds__(256)
 rows_stage_kernel(const float *__restrict__ qkv, uint16_t *__restrict__ k,
                   uint16_t *__restrict__ v, int t, int tp, int heads, int hd)
 {
+    // (the attention kernel behind this one may set itself up meanwhile)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float tile[64][65];
     const int d = heads * hd;
     qkv += (size_t)blockIdx.z * t * 3 * d;
