@@ -708,8 +708,7 @@ cudaError_t launch_lse_merge_pairs(cudaStream_t st, const float *gather, const u
                                    unsigned *mstep, int world, int rows, int rows_per_pair, int hd,
                                    float *out, int *status, long long wait_cycles, bool early)
 {
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(rows);
     cfg.blockDim = dim3(hd < 32 ? 32 : (hd > 256 ? 256 : hd));
     cfg.stream = st;

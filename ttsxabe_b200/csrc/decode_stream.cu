@@ -1032,8 +1032,7 @@ static int resident_clusters(int dev, int hd, int c)
     std::lock_guard<std::mutex> hold(lock);
     int &slot = memo[dev][hd == 128 ? 1 : 0][c];
     if (slot == 0) {
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(c * 64);
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = hd == 128 ? ring_bytes<128>() : ring_bytes<64>();
@@ -1151,8 +1150,7 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in
     if (!cluster_cut(p, dev, hd, sms, &grid) && !pair_cut(p, hd, sms, &grid)) {
         stream_partition(p, hd, grid);
     }
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = hd == 128 ? ring_bytes<128>() : ring_bytes<64>();

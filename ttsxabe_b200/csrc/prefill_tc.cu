@@ -1310,8 +1310,7 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, c
     }
     cudaError_t err;
     {
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = hd == 128 ? Geo<128>::SMEM : Geo<64>::SMEM;
@@ -1347,8 +1346,7 @@ cudaError_t launch_prefill_tc(cudaStream_t st, const PrefillParams &p, int hd, c
                 // A programmatic dependent of the attention kernel: its blocks are
                 // set up while that kernel's last blocks still run, and wait for
                 // its end (griddepcontrol.wait) before they read anything.
-                cudaLaunchConfig_t cfg;
-                memset(&cfg, 0, sizeof(cfg));
+                cudaLaunchConfig_t cfg = {};
                 cfg.gridDim = mg;
                 cfg.blockDim = dim3(128);
                 cfg.stream = st;
