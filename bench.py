@@ -791,6 +791,22 @@ def other_configs(args, world, rank, local):
         fn = lambda: gpu.decode_batched(q, ks, vs, tks, [cap] * batch, HEADS, KV_HEADS, HD, SCALE,
                                         False, sc, out=out)
         res["decode_batch%d_ctx%d_%d" % (batch, lo, hi - 1)] = {"us": graph_time(gpu, fn) * 1e6}
+    # a layer's decode step as a model makes it: RoPE + cache write, then attention
+    for batch, tk in ((1, 3000), (8, 1024)):
+        cap = 4096
+        ks = [device_normal_f16(gpu, KV_HEADS * cap * HD, 210 + b) for b in range(batch)]
+        vs = [device_normal_f16(gpu, KV_HEADS * cap * HD, 250 + b) for b in range(batch)]
+        q, k, v = randn(batch * HEADS * HD), randn(batch * KV_HEADS * HD), randn(batch * KV_HEADS * HD)
+        out = gpu.uninit(batch * HEADS * HD)
+        pos_t, cap_t = gpu.i32_table([tk - 1] * batch), gpu.i32_table([cap] * batch)
+        tk_t, ks_t, vs_t = gpu.i32_table([tk] * batch), gpu.ptr_table(ks), gpu.ptr_table(vs)
+
+        def step():
+            gpu.rope_cache_batched(q, k, v, None, HEADS, KV_HEADS, HD, 10000.0, pos_t, ks_t, vs_t,
+                                   cap_t)
+            gpu.decode_batched(q, ks_t, vs_t, tk_t, cap_t, HEADS, KV_HEADS, HD, SCALE, False, sc,
+                               out=out)
+        res["decode_step_batch%d_ctx%d" % (batch, tk)] = {"us": graph_time(gpu, step) * 1e6}
     line = {"metric": "per-config device time", "unit": "us", "n_gpus": 1, "data": "synthetic",
             "timing": "CUDA-graph replay, median of 5", "peaks": {"hbm_gbs": hbm, "tflops": tf,
                                                                   "source": which},
