@@ -414,6 +414,24 @@ llmtie_status llmtie_lse_merge_wait(llmtie_gpu *g, const llmtie_exchange *xch, s
 llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size_t kv_heads,
                                 size_t head_dim, int32_t sm_count, int32_t *ustart,
                                 size_t ustart_len, int32_t *grid_out);
+/* The whole choice a launch makes (host only, no device needed; no counterpart
+ * in the reference): for `batch` sequences of tk[b] keys, `rows` query rows a
+ * KV head (the GQA group, or the rows of llmtie_cross_attn), on a device of
+ * sm_count SMs that holds resident2 / resident4 / resident8 clusters of 2 / 4 /
+ * 8 blocks of the decode kernel at once (the launch asks the driver; a B200
+ * answers 74 / 33 / 15 at head_dim 128 and 148 / 71 / 33 at 64). blocks_a_pair_out = 0: cut by work as
+ * llmtie_decode_cut describes; 1: every pair a block of its own; 2, 4, 8: every
+ * pair a thread-block cluster of that many blocks. grid_out and ustart as for
+ * llmtie_decode_cut. */
+/* How many thread-block clusters of `blocks` (2, 4 or 8) blocks of the decode
+ * kernel the handle's device holds at once, as the driver answers (0: none,
+ * or a bad argument): what llmtie_decode_plan takes as resident2 / 4 / 8. */
+int32_t llmtie_decode_resident_clusters(llmtie_gpu *g, size_t head_dim, int32_t blocks);
+llmtie_status llmtie_decode_plan(const int32_t *tk, size_t batch, size_t kv_heads, size_t rows,
+                                 size_t head_dim, int32_t sm_count, int32_t resident2,
+                                 int32_t resident4, int32_t resident8, int32_t *ustart,
+                                 size_t ustart_len, int32_t *grid_out,
+                                 int32_t *blocks_a_pair_out);
 /* The whole sharded step in ONE kernel (no counterpart in the reference):
  * llmtie_decode_batched_push with the merge fused in as well. The block that
  * finishes a (sequence, KV head) pair on this rank stores the pair's triple

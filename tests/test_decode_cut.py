@@ -63,3 +63,51 @@ def test_refusals():
         decode_cut([128], 8, 96)
     with pytest.raises(InvalidArgument):
         decode_cut([128] * 33, 8, 128)
+
+
+def test_the_plan_of_a_launch():
+    """Which cut a launch takes, on a B200's figures (148 SMs; 74 / 33 / 15
+    clusters of 2 / 4 / 8 blocks of the head_dim-128 kernel resident at once,
+    148 / 71 / 33 of the head_dim-64 one)."""
+    from ttsxabe_b200 import decode_plan
+
+    def plan(tk, kv=8, rows=4, hd=128, **kw):
+        return decode_plan(tk, kv, rows, hd, **kw)
+
+    # the benchmark's step: long pairs, cut by work over every SM
+    mode, cut = plan([131072] * 8)
+    assert mode == 0 and len(cut) - 1 == 148
+    # a rank of eight's share of it: 64 equal pairs of 128 units, two blocks a pair
+    mode, cut = plan([16384] * 8)
+    assert mode == 2 and len(cut) - 1 == 128
+    assert all(b - a == 64 for a, b in zip(cut, cut[1:]))
+    # one short sequence: eight blocks a pair, three units each
+    mode, cut = plan([3000])
+    assert mode == 8 and len(cut) - 1 == 64 and cut[-1] == 8 * 24
+    assert all(b - a == 3 for a, b in zip(cut, cut[1:]))
+    # sixteen pairs' clusters of eight are one too many to be resident at once: four a pair
+    assert plan([3000] * 2)[0] == 4
+    assert plan([3000] * 2, resident=(74, 36, 16))[0] == 8
+    assert plan([3000] * 4)[0] == 4 and plan([700] * 8)[0] == 2
+    # one unit a pair: nothing to cut, a block a pair by the cut by work
+    mode, cut = plan([100])
+    assert mode == 0 and cut == list(range(9))
+    # unequal lengths: a cluster a pair only while the longest run stays at eight units
+    assert plan([600, 1000, 800, 520])[0] == 4
+    assert plan([2048, 4096, 3000, 2500, 2100, 3900, 2300, 4000])[0] == 0
+    # Whisper cross-attention (20 heads of 64): 1 and 8 rows by clusters of four,
+    # 32 rows are 80 pairs - more than half the SMs, short: a block a pair
+    assert plan([1500], kv=20, rows=1, hd=64)[0] == 4
+    assert plan([1500], kv=20, rows=8, hd=64)[0] == 4
+    mode, cut = plan([1500], kv=20, rows=32, hd=64)
+    assert mode == 1 and len(cut) - 1 == 80 and all(b - a == 12 for a, b in zip(cut, cut[1:]))
+    # 128 equal pairs of 16 units: a block a pair; 96 pairs of 24 units leave too many SMs
+    # idle for too long that way: cut by work
+    assert plan([2048] * 16)[0] == 1 and plan([3072] * 12)[0] == 0
+    # every cut covers every unit once, in order
+    for tk, kw in (([3000], {}), ([600, 1000, 800, 520], {}), ([1500], dict(kv=20, rows=32, hd=64)),
+                   ([2048] * 16, {}), ([777, 5000, 31], {})):
+        mode, cut = plan(tk, **kw)
+        kv, rows = kw.get("kv", 8), kw.get("rows", 4)
+        assert cut[0] == 0 and cut[-1] == sum(-(-t // 128) for t in tk) * kv * -(-rows // 8)
+        assert all(a < b for a, b in zip(cut, cut[1:]))

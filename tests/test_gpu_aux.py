@@ -258,3 +258,15 @@ def test_calls_with_nothing_to_do_launch_nothing(gpu):
     assert gpu.launch_count() == before
     assert np.array_equal(gpu.download(x), buf)
     assert not gpu.download_u16(kc).any() and not gpu.download(k32).any()
+
+
+def test_resident_clusters_as_the_driver_answers(gpu):
+    """What the launch asks before it gives pairs a cluster each: more blocks
+    a cluster, fewer clusters; the narrower kernel's ring is half the size, so
+    twice as many fit. (The host-side plan in tests/test_decode_cut.py is
+    checked against a B200's answers: 74 / 33 / 15 and 148 / 71 / 33.)"""
+    for hd in (128, 64):
+        n = [gpu._lib.llmtie_decode_resident_clusters(gpu._h, hd, c) for c in (2, 4, 8)]
+        assert n[0] >= n[1] >= n[2] >= 1, (hd, n)
+        assert n[0] * 2 <= 2 * 148 and n[2] * 8 <= 2 * 148
+    assert gpu._lib.llmtie_decode_resident_clusters(gpu._h, 96, 2) == 0

@@ -23,5 +23,6 @@ from .gpu import (  # noqa: F401
     SliceOverrun,
     UnsupportedAttention,
     decode_cut,
+    decode_plan,
 )
 from .cache import KvCache, Prefix, shared_prefix, want_capacity  # noqa: F401

@@ -79,6 +79,8 @@ PROTOTYPES = {
     "llmtie_decode_batched_push": (
         i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp]),
     "llmtie_decode_cut": (i32, [pi32, sz, sz, sz, i32, pi32, sz, pi32]),
+    "llmtie_decode_resident_clusters": (i32, [vp, sz, i32]),
+    "llmtie_decode_plan": (i32, [pi32, sz, sz, sz, sz, i32, i32, i32, i32, pi32, sz, pi32, pi32]),
     "llmtie_decode_batched_fused": (
         i32, [vp, vp, sz, pvp, pvp, pi32, pi32, sz, sz, sz, sz, f32, i32, vp, vp, pvp, vp, sz]),
     "llmtie_lse_merge_wait": (i32, [vp, vp, sz, sz, vp, sz]),

@@ -1220,9 +1220,8 @@ static llmtie_status decode_launch(llmtie_gpu *g, const char *name, DecodeParams
             const int v = e ? atoi(e) : 0;
             return v > 0 ? v : LLMTIE_STREAM_MAX_BLOCKS;
         }();
-        const int grid = (int)std::min<long long>(
-            std::min(std::min(g->sm_count, grid_cap), LLMTIE_STREAM_MAX_BLOCKS),
-            std::max<long long>(std::max<long long>(1, units / 4), (long long)p.nseq * inner));
+        const int grid =
+            decode_work_grid(units, (long long)p.nseq * inner, std::min(g->sm_count, grid_cap));
         const size_t pairs = (size_t)p.nseq * inner;
         const llmtie_status s =
             scratch_reserve(g, scratch, pairs + 1, (size_t)grid * 2, (size_t)hd);

@@ -279,6 +279,9 @@ struct DecodeStreamParams {
     int v_plain;
 };
 cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p, int hd, int grid);
+// Blocks of the cut by work: one per SM, never fewer than four units a block
+// unless that is fewer blocks than pairs.
+int decode_work_grid(long long units, long long pairs, int sm_count);
 // The two tensor maps the ring kernel reads one sequence's caches through:
 // keys [kv][cap][hd] seen as kv*cap rows (boxes of 32 rows x 128 bytes, 128-byte
 // swizzle), values [kv][hd][cap] seen as kv*hd rows of `cap` (boxes of hd rows

@@ -946,6 +946,12 @@ bool decode_tensor_maps(CUtensorMap *kmap, CUtensorMap *vmap, const void *k, con
 // cut is even not in units but in units plus `ov` virtual ones at the head of
 // every pair: a run that crosses a pair boundary swallows that pair's virtual
 // units and carries that many fewer real ones.
+int decode_work_grid(long long units, long long pairs, int sm_count)
+{
+    return (int)std::min<long long>(std::min(sm_count, LLMTIE_STREAM_MAX_BLOCKS),
+                                    std::max<long long>(std::max<long long>(1, units / 4), pairs));
+}
+
 static void stream_partition(DecodeStreamParams &p, int hd, int grid)
 {
     // (LLMTIE_B200_DECODE_OV overrides the count: a tuning switch)
@@ -1008,9 +1014,7 @@ extern "C" llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size
     p.pair0[batch] = (int)(batch * kv_heads);
     p.total_units = units;
     if (units > 0x7fffffffLL) return llmtie_fail(LLMTIE_ERR_INVALID, "too many keys for one launch");
-    const int grid = (int)std::min<long long>(
-        std::min(sm_count, LLMTIE_STREAM_MAX_BLOCKS),
-        std::max<long long>(std::max<long long>(1, units / 4), (long long)(batch * kv_heads)));
+    const int grid = decode_work_grid(units, (long long)(batch * kv_heads), sm_count);
     if (ustart_len < (size_t)grid + 1) {
         return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %d in a buffer of %zu", grid + 1,
                            ustart_len);
@@ -1019,6 +1023,78 @@ extern "C" llmtie_status llmtie_decode_cut(const int32_t *tk, size_t batch, size
     for (int c = 0; c <= grid; c++) ustart[c] = p.ustart[c];
     *grid_out = grid;
     return LLMTIE_OK;
+}
+
+static bool cluster_cut(DecodeStreamParams &p, const int *resident, int sm_count, int *grid);
+static bool pair_cut(DecodeStreamParams &p, int hd, int sm_count, int *grid);
+
+// The whole choice a launch makes, on the host (no device): the cut by work,
+// a block a pair, or a cluster of 2, 4 or 8 blocks a pair. What the device
+// would be asked - how many clusters of each size it holds at once - is an
+// argument here.
+extern "C" llmtie_status llmtie_decode_plan(const int32_t *tk, size_t batch, size_t kv_heads,
+                                            size_t rows, size_t head_dim, int32_t sm_count,
+                                            int32_t resident2, int32_t resident4,
+                                            int32_t resident8, int32_t *ustart, size_t ustart_len,
+                                            int32_t *grid_out, int32_t *blocks_a_pair_out)
+{
+    if (!tk || !ustart || !grid_out || !blocks_a_pair_out || batch == 0 ||
+        batch > LLMTIE_DECODE_MAX_SEQ || kv_heads == 0 || rows == 0 || sm_count < 1 ||
+        (head_dim != 64 && head_dim != 128)) {
+        return llmtie_fail(LLMTIE_ERR_INVALID, "a malformed decode description");
+    }
+    DecodeStreamParams p;
+    memset(&p, 0, sizeof(p));
+    p.nseq = (int)batch;
+    p.kv_heads = (int)kv_heads;
+    p.row_chunks = (int)((rows + kRows - 1) / kRows);
+    const int inner = p.kv_heads * p.row_chunks;
+    long long units = 0;
+    for (size_t b = 0; b < batch; b++) {
+        if (tk[b] <= 0) return llmtie_fail(LLMTIE_ERR_INVALID, "an empty context");
+        p.seq[b].tk = tk[b];
+        p.unit0[b] = units;
+        p.pair0[b] = (int)b * inner;
+        units += (long long)((tk[b] + 127) / 128) * inner;
+    }
+    p.unit0[batch] = units;
+    p.pair0[batch] = (int)batch * inner;
+    p.total_units = units;
+    if (units > 0x7fffffffLL) return llmtie_fail(LLMTIE_ERR_INVALID, "too many keys for one launch");
+    int grid = decode_work_grid(units, (long long)batch * inner, sm_count);
+    int resident[kClusterMax + 1] = {0};
+    resident[2] = resident2;
+    resident[4] = resident4;
+    resident[8] = resident8;
+    int mode = 0;
+    if (cluster_cut(p, resident, sm_count, &grid)) {
+        mode = p.by_cluster;
+    } else if (pair_cut(p, (int)head_dim, sm_count, &grid)) {
+        mode = 1;
+    } else {
+        stream_partition(p, (int)head_dim, grid);
+    }
+    if (ustart_len < (size_t)grid + 1) {
+        return llmtie_fail(LLMTIE_ERR_SLICE_OVERRUN, "reading to %d in a buffer of %zu", grid + 1,
+                           ustart_len);
+    }
+    for (int c = 0; c <= grid; c++) ustart[c] = p.ustart[c];
+    *grid_out = grid;
+    *blocks_a_pair_out = mode;
+    return LLMTIE_OK;
+}
+
+// The ring needs more shared memory than a kernel gets unasked: once a device.
+static void configure_decode_stream(int dev)
+{
+    static bool configured[64] = {false};
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaFuncSetAttribute(decode_stream_kernel<128>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes<128>());
+        cudaFuncSetAttribute(decode_stream_kernel<64>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes<64>());
+        configured[dev] = true;
+    }
 }
 
 // How many clusters of `c` blocks of this kernel the device holds at once
@@ -1053,6 +1129,15 @@ static int resident_clusters(int dev, int hd, int c)
     return slot > 0 ? slot : 0;
 }
 
+extern "C" int32_t llmtie_decode_resident_clusters(llmtie_gpu *g, size_t head_dim, int32_t blocks)
+{
+    if (!g || (head_dim != 64 && head_dim != 128)) return 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    configure_decode_stream(dev);
+    return resident_clusters(dev, (int)head_dim, blocks);
+}
+
 // Whether the launch goes pair by cluster: every sequence the same length, and
 // either two blocks a pair filling at least four fifths of the SMs, with runs
 // short enough (at most 256 units a block) for the launch's fixed costs to
@@ -1060,7 +1145,7 @@ static int resident_clusters(int dev, int hd, int c)
 // SM - or, for a few short pairs (a few sequences of a few thousand keys,
 // where the step is nothing but latency), as many blocks a pair - eight, four
 // or two - as leaves every block a unit and all clusters resident at once.
-static bool cluster_cut(DecodeStreamParams &p, int dev, int hd, int sm_count, int *grid)
+static bool cluster_cut(DecodeStreamParams &p, const int *resident, int sm_count, int *grid)
 {
     static const bool never = getenv("LLMTIE_B200_DECODE_NO_CLUSTER") != nullptr;
     const long long pairs = (long long)p.nseq * p.kv_heads * p.row_chunks;
@@ -1080,7 +1165,7 @@ static bool cluster_cut(DecodeStreamParams &p, int dev, int hd, int sm_count, in
         // short - eight units - since the clusters then end at different times)
         for (int c = kClusterMax; c >= 2 && C == 0; c >>= 1) {
             if (n >= c && pairs * c >= 32 && pairs * c <= sm_count &&
-                pairs <= resident_clusters(dev, hd, c) && (even || (n_max + c - 1) / c <= 8)) {
+                pairs <= resident[c] && (even || (n_max + c - 1) / c <= 8)) {
                 C = c;
             }
         }
@@ -1139,15 +1224,10 @@ cudaError_t launch_decode_stream(cudaStream_t st, const DecodeStreamParams &p_in
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    static bool configured[64] = {false};
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaFuncSetAttribute(decode_stream_kernel<128>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes<128>());
-        cudaFuncSetAttribute(decode_stream_kernel<64>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes<64>());
-        configured[dev] = true;
-    }
-    if (!cluster_cut(p, dev, hd, sms, &grid) && !pair_cut(p, hd, sms, &grid)) {
+    configure_decode_stream(dev);
+    int resident[kClusterMax + 1] = {0};
+    for (int c = 2; c <= kClusterMax; c <<= 1) resident[c] = resident_clusters(dev, hd, c);
+    if (!cluster_cut(p, resident, sms, &grid) && !pair_cut(p, hd, sms, &grid)) {
         stream_partition(p, hd, grid);
     }
     cudaLaunchConfig_t cfg = {};

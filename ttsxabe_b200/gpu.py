@@ -158,6 +158,24 @@ def decode_cut(tk, kv_heads: int, head_dim: int, sm_count: int = 148) -> list[in
     return list(table[:grid.value + 1])
 
 
+def decode_plan(tk, kv_heads: int, rows: int, head_dim: int, sm_count: int = 148,
+                resident=None):
+    """The whole choice a decode launch makes (host only): returns
+    (blocks_a_pair, cut) - 0: cut by work, 1: a block a pair, 2 / 4 / 8: a
+    cluster of that many blocks a pair - for a device that holds `resident`
+    clusters of 2, 4 and 8 blocks at once (by default a B200's answers:
+    74 / 33 / 15 at head_dim 128, 148 / 71 / 33 at 64, where two blocks fit an SM)."""
+    if resident is None:
+        resident = (74, 33, 15) if head_dim == 128 else (148, 71, 33)
+    lib = _lib.load()
+    table = (C.c_int32 * 161)()
+    grid, mode = C.c_int32(0), C.c_int32(0)
+    _check(lib.llmtie_decode_plan((C.c_int32 * len(tk))(*tk), len(tk), kv_heads, rows, head_dim,
+                                  sm_count, resident[0], resident[1], resident[2], table,
+                                  len(table), C.byref(grid), C.byref(mode)))
+    return mode.value, list(table[:grid.value + 1])
+
+
 class Gpu:
     """One device handle with its own stream (device.rs:737-842)."""
 
