@@ -95,11 +95,15 @@ def test_the_plan_of_a_launch():
     # unequal lengths: a cluster a pair only while the longest run stays at eight units
     assert plan([600, 1000, 800, 520])[0] == 4
     assert plan([2048, 4096, 3000, 2500, 2100, 3900, 2300, 4000])[0] == 0
-    # Whisper cross-attention (20 heads of 64): 1 and 8 rows by clusters of four,
-    # 32 rows are 80 pairs - more than half the SMs, short: a block a pair
-    assert plan([1500], kv=20, rows=1, hd=64)[0] == 4
-    assert plan([1500], kv=20, rows=8, hd=64)[0] == 4
+    # Whisper cross-attention (20 heads of 64; two blocks of the narrower kernel fit an
+    # SM): 1 and 8 rows by clusters of eight, the 80 pairs of 32 rows by clusters of two
+    assert plan([1500], kv=20, rows=1, hd=64)[0] == 8
+    assert plan([1500], kv=20, rows=8, hd=64)[0] == 8
     mode, cut = plan([1500], kv=20, rows=32, hd=64)
+    assert mode == 2 and len(cut) - 1 == 160 and all(b - a == 6 for a, b in zip(cut, cut[1:]))
+    # on a device that held one such block an SM: 80 pairs outnumber half the SMs, and are
+    # short: a block a pair
+    mode, cut = plan([1500], kv=20, rows=32, hd=64, resident=(74, 33, 15))
     assert mode == 1 and len(cut) - 1 == 80 and all(b - a == 12 for a, b in zip(cut, cut[1:]))
     # 128 equal pairs of 16 units: a block a pair; 96 pairs of 24 units leave too many SMs
     # idle for too long that way: cut by work

@@ -1161,10 +1161,15 @@ static bool cluster_cut(DecodeStreamParams &p, const int *resident, int sm_count
         n <= 512) {
         C = 2;
     } else if (n_max <= 64) {
+        // As many blocks as the device holds at once: one an SM at head_dim
+        // 128, two at 64, where the ring is half the size (which shows in how
+        // many clusters of two are resident).
+        const long long room =
+            std::min<long long>(LLMTIE_STREAM_MAX_BLOCKS, std::max(sm_count, 2 * resident[2]));
         // (sequences of unequal length: only while the longest run stays
         // short - eight units - since the clusters then end at different times)
         for (int c = kClusterMax; c >= 2 && C == 0; c >>= 1) {
-            if (n >= c && pairs * c >= 32 && pairs * c <= sm_count &&
+            if (n >= c && pairs * c >= 32 && pairs * c <= room &&
                 pairs <= resident[c] && (even || (n_max + c - 1) / c <= 8)) {
                 C = c;
             }
