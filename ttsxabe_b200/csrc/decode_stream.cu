@@ -794,15 +794,18 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
 
         if (whole) pair_done();
         if (!whole && p.by_cluster > 2) {
-            // ---- the cluster's blocks meet; the leading one fetches and merges ----------
+            // ---- the cluster's blocks meet; each fetches and merges its share of the rows
+            // (row r goes to block r mod C: the fetches of a pair's rows are spread
+            // over the cluster instead of queueing in the leading block)
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
             uint32_t crank;
             asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
-            if (crank == 0) {
+            {
                 const int C = p.by_cluster;
-                for (int idx = tid; idx < rows_here * HD; idx += kThreads) {
-                    const int row = idx / HD, d = idx % HD;
+                const int mine_n = (rows_here - (int)crank + C - 1) / C;     // rows crank, crank + C, ...
+                for (int idx = tid; idx < mine_n * HD; idx += kThreads) {
+                    const int row = (int)crank + (idx / HD) * C, d = idx % HD;
                     const uint32_t mine = smem_u32(&sm_pair[0][row][0]);
                     // every block's three words of this value are asked for at once
                     float mi[kClusterMax], li[kClusterMax], oi[kClusterMax];
@@ -839,11 +842,12 @@ decode_stream_kernel(const __grid_constant__ DecodeStreamParams p)
                     }
                     emit(row, d, O, M, L);
                 }
-                pair_done();
             }
-            // nobody's slot is reused (or goes away with its block) before it was read
+            // nobody's slot is reused (or goes away with its block) before it was
+            // read; and every row of the pair is out before the pair is counted
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            if (crank == 0) pair_done();
         } else if (!whole && p.by_cluster) {
             // ---- the cluster's two blocks meet; the leading one merges -------------------
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
